@@ -1,0 +1,113 @@
+/*
+ * linquant_b200 — C ABI of the sm_100a INT8 chunk-prefill kernels.
+ *
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer unless it says "host". Nothing here allocates
+ * device memory: callers own inputs, outputs and the workspace. All launches go to the given stream and return
+ * without synchronising. Every entry returns an lq_status (0 = ok); lq_last_error_string() gives the detail of
+ * the most recent failure on the calling thread.
+ *
+ * The reference project has no C boundary on this path: its hot path is Python calling Triton JIT kernels.
+ * Each entry below therefore names the reference *Python* function (file:line in the reference tree) whose
+ * device work it replaces; the Python wrappers in linquant_b200/kernels keep those functions' signatures.
+ */
+#ifndef LINQUANT_B200_H
+#define LINQUANT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  LQ_OK = 0,
+  LQ_ERR_NULL = 1,        /* a required pointer is null */
+  LQ_ERR_SHAPE = 2,       /* T % chunk != 0, unsupported K/V/chunk, non-positive extent */
+  LQ_ERR_ALIGN = 3,       /* a pointer or stride breaks the 16-byte rule of the vector loads */
+  LQ_ERR_UNSUPPORTED = 4, /* valid request this build has no kernel for */
+  LQ_ERR_LAUNCH = 5,      /* cudaGetLastError() after the launch was not cudaSuccess */
+  LQ_ERR_TIMEOUT = 6,     /* a bounded device-side wait ran out (status word written by the kernel) */
+  LQ_ERR_WORKSPACE = 7    /* workspace too small */
+} lq_status;
+
+typedef enum { LQ_F16 = 0, LQ_BF16 = 1, LQ_F32 = 2 } lq_dtype;
+
+/* decay kinds of the recurrence (reference.py:107-122) */
+typedef enum { LQ_DECAY_NONE = 0, LQ_DECAY_SCALAR = 1, LQ_DECAY_DIAGONAL = 2 } lq_decay;
+
+typedef void* lq_stream; /* a cudaStream_t */
+
+int lq_version(void);
+const char* lq_last_error_string(void);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Problem descriptor shared by the zoo-lineage entries (linear attention / Simple GLA / GLA / DeltaNet /
+ * Gated DeltaNet / KDA). Layouts follow the reference: q,k [B,T,H,K], v,o [B,T,H,V] dense, act dtype f16/bf16;
+ * g [B,T,H] (scalar) or [B,T,H,K] (diagonal) fp32 log-decay or null; beta [B,T,H] fp32 or null.
+ * Scales are fp32: sq,sk,sw [H]; skw [H,K]; svl,svw,sel,sew,sstate [H,V]  (invariances.py:102-112).
+ * ------------------------------------------------------------------------------------------------------------ */
+typedef struct {
+  int B, T, H, K, V, chunk;
+  int act_dtype; /* lq_dtype of q,k,v */
+  int out_dtype; /* lq_dtype of o */
+  int decay;     /* lq_decay */
+  float scale;   /* multiplies q before quantisation (reference.py:47) */
+  float eta;     /* write-decay split: key gets Omega^(1-eta), value Omega^eta */
+  float sigma;   /* delta rule: Gram exponent (reference "rho") */
+  float tau;     /* delta rule: placement of the outer beta factor */
+  float qmax;    /* 127 (INT8) or 31 (INT6 codes in INT8 containers) */
+  const void* q;
+  const void* k;
+  const void* v;
+  const float* g;
+  const float* beta;
+  const float* rot_signs; /* [K] +-1: fused signed-Hadamard R_QK (persistent for none/scalar decay, local for
+                             diagonal decay); null = operands are used as given */
+  const float* dqk;       /* [H,K] diagonal rescale D_QK (q*D, k/D) applied before the rotation; null = off */
+  const float *sq, *sk, *skw, *svl, *svw, *sstate; /* linear-family scales */
+  const float *sw, *sel, *sew;                     /* delta-family extras (null for the linear family) */
+  void* o;                /* [B,T,H,V] */
+  float* final_state;     /* [B,H,K,V] fp32 carry after the last chunk, or null */
+} lq_zoo_problem;
+
+/* Bytes of workspace the zoo entries need for this problem (a host-side computation). */
+size_t lq_zoo_workspace_bytes(const lq_zoo_problem* p, int delta_family);
+
+/* Workspace carve-up, exposed so tests can read the recorded INT8 codes back. All tiles are per (b*H+h, chunk):
+ *   qq  [BH,NT,C,K]  q codes (read == local, invariances.py:54)      kl  [BH,NT,C,K]  k_local codes
+ *   kwT [BH,NT,K,C]  k_write codes, token index contiguous            vlT [BH,NT,V,C]  v_local / e_local codes
+ *   vwT [BH,NT,V,C]  v_write codes                                     hT  [BH,NT,V,K]  stored state entering the chunk
+ *   gc  [BH,NT,C]    chunk-local cumulative log-decay (fp32)           wq  [BH,NT,C,K]  w_read codes (delta)
+ *   u   [BH,NT,C,V]  WY right-hand side U in fp32 rounded to the act dtype grid (delta)
+ *   fw  [BH,NT,C]    value-side share of the outer beta factor (delta)
+ */
+typedef struct {
+  int8_t *qq, *kl, *kwT, *vlT, *vwT, *hT, *wq;
+  float *gc, *u, *fw, *amat, *genv;
+  int8_t* gk; /* unused padding slot kept for ABI stability */
+} lq_zoo_workspace;
+int lq_zoo_carve_workspace(const lq_zoo_problem* p, int delta_family, void* workspace, size_t workspace_bytes,
+                           lq_zoo_workspace* out);
+
+/* Fused prologue: [D_QK] -> [signed Hadamard R_QK] -> act-dtype rounding -> x scale -> per-role static INT8, plus
+ * the chunk-local cumulative log-decay. Replaces the torch-side cumsum (zoo/simple_gla.py:191), the bench-side
+ * rotation GEMMs (bench/zoo_kernels.py:135-140) and the per-tile _q8 calls inside the reference kernels
+ * (zoo/simple_gla.py:16-20,66-67,129-130,149). */
+int lq_zoo_prologue_linear(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq_stream stream);
+
+/* Inter-chunk state pass of the linear family: INT8 stored copy of the fp32 carry entering every chunk, INT8
+ * write product, fp32 carry update. Replaces _state_kernel (zoo/simple_gla.py:24-87). */
+int lq_zoo_state_linear(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq_stream stream);
+
+/* Intra-chunk output: INT8 q.S read, INT8 q.k^T with the decay mask, fp16 A.v on the value codes.
+ * Replaces _output_kernel (zoo/simple_gla.py:99-165). */
+int lq_zoo_output_scalar(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq_stream stream);
+
+/* Whole call of chunk_simple_gla_int8 (zoo/simple_gla.py:175-212): prologue + state pass + output. */
+int lq_simple_gla_fwd(const lq_zoo_problem* p, void* workspace, size_t workspace_bytes, lq_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LINQUANT_B200_H */
