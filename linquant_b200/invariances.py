@@ -1,0 +1,131 @@
+"""Scale policies of the INT8 chunk kernels and absmax calibration of their static scales (host logic, torch).
+
+Mirrors the policy surface of ``linquant/invariances.py``: the role list (``:8``), the three realizable policies
+``kernel_static`` / ``kernel_pt`` / ``kernel_ptk`` (``:13-25``), the q_local -> q_read tie (``:54``), absmax / qmax
+scales with the state always on the 8-bit range (``:132-135``) and the exported kernel scale dict
+(``:102-112`` plus the delta extras of ``tests/test_kernel_delta.py:23-33``).
+
+The observers run the *unquantised* recurrence with plain torch ops on whatever device the inputs live on; they
+are calibration plumbing, not the prefill hot path (that is ``linquant_b200.kernels``)."""
+
+from __future__ import annotations
+
+import torch
+
+ROLES = ("q_read", "q_local", "k_local", "w_read", "v_local", "e_local", "k_write", "v_write", "e_write", "state")
+POLICIES = {
+    "kernel_static": {"q_read": "ph_static", "q_local": "ph_static", "k_local": "ph_static", "w_read": "ph_static",
+                      "v_local": "pc_static", "e_local": "pc_static", "k_write": "pc_static", "v_write": "pc_static",
+                      "e_write": "pc_static", "state": "pc_static"},
+}
+POLICIES["kernel_pt"] = {r: ("pt_static" if r != "state" else s) for r, s in POLICIES["kernel_static"].items()}
+_KEY_ROLES = ("q_read", "q_local", "k_local", "k_write", "w_read")
+POLICIES["kernel_ptk"] = {**POLICIES["kernel_static"], **{r: "pt_static" for r in _KEY_ROLES}}
+TIES = {"q_local": "q_read"}
+
+
+class StaticScales:
+    """Running absmax per role at the granularity the policy names; ``kernel_scales`` exports fp32 tensors."""
+
+    def __init__(self, policy="kernel_static", bits=8, state_bits=8):
+        if policy not in POLICIES:
+            raise KeyError(f"unknown policy {policy!r}; choose from {sorted(POLICIES)}")
+        self.policy, self.bits, self.state_bits = policy, bits, state_bits
+        self.qmax = 2 ** (bits - 1) - 1
+        self.absmax: dict[str, torch.Tensor] = {}
+        self.scales: dict[str, torch.Tensor] = {}
+
+    def observe(self, role, x):
+        """x is [B,H,rows,D] (operands) or [B,H,K,V] (state)."""
+        slot = TIES.get(role, role)
+        scheme = POLICIES[self.policy][role]
+        a = x.detach().abs()
+        a = a.amax(dim=(0, 2)) if scheme == "pc_static" else a.amax(dim=(0, 2, 3)) if scheme == "ph_static" else a.amax()
+        self.absmax[slot] = torch.maximum(self.absmax[slot], a) if slot in self.absmax else a
+
+    def finalize(self):
+        smax = 2 ** (self.state_bits - 1) - 1
+        self.scales = {r: a / (smax if r == "state" else self.qmax) for r, a in self.absmax.items()}
+        return self
+
+    def kernel_scales(self, H, K, V, device=None):
+        def grab(role, shape, floor=True):
+            s = self.scales.get(TIES.get(role, role))
+            if s is None:
+                return torch.ones(shape, dtype=torch.float32, device=device)
+            s = s.float()
+            s = s.clamp_min(1e-6) if floor else s  # an all-zero channel must not export 1/0
+            s = s.reshape(shape) if s.numel() > 1 else s.expand(shape).contiguous()
+            return s.to(device) if device is not None else s
+
+        out = {"q": grab("q_read", (H,)), "k": grab("k_local", (H,)), "kw": grab("k_write", (H, K)),
+               "vw": grab("v_write", (H, V)), "vl": grab("v_local", (H, V)), "state": grab("state", (H, V))}
+        if "w_read" in self.scales:
+            out.update(w=grab("w_read", (H,), False), el=grab("e_local", (H, V), False), ew=grab("e_write", (H, V), False))
+        return out
+
+
+def hadamard_signs(n, seed):
+    """Sign pattern of ``linquant.reference.hadamard_rotation(n, seed)`` (reference.py:237-238)."""
+    gen = torch.Generator().manual_seed(seed)
+    return (torch.randint(0, 2, (n,), generator=gen).double() * 2 - 1).float()
+
+
+def signed_hadamard_matrix(signs):
+    n = signs.numel()
+    Hm = torch.ones(1, 1, dtype=torch.float64)
+    while Hm.shape[0] < n:
+        Hm = torch.cat([torch.cat([Hm, Hm], 1), torch.cat([Hm, -Hm], 1)], 0)
+    return Hm / n**0.5 * signs.double().cpu()
+
+
+def dqk_from_stats(q, k, alpha):
+    """D = (max|k| / max|q|)^alpha per (H,K): q*D, k/D (harness.py:68-79)."""
+    aq = q.detach().abs().amax(dim=(0, 1)).double().clamp_min(1e-8)
+    ak = k.detach().abs().amax(dim=(0, 1)).double().clamp_min(1e-8)
+    return ((ak / aq) ** alpha).float()
+
+
+def _prepare_qk(q, k, rot_signs, dqk, scale):
+    act = q.dtype
+    qf, kf = q.float(), k.float()
+    if dqk is not None:
+        qf, kf = qf * dqk.to(qf.device), kf / dqk.to(kf.device)
+    if rot_signs is not None:
+        R = signed_hadamard_matrix(rot_signs).float().to(qf.device)
+        qf, kf = (qf @ R).to(act).float(), (kf @ R).to(act).float()
+    return qf * scale, kf
+
+
+@torch.no_grad()
+def calibrate_linear(sc: StaticScales, q, k, v, g, *, eta=1.0, scale=None, chunk_size=64, rot_signs=None, dqk=None):
+    """Observe every role of the linear family with none / scalar decay on one batch (reference.py:190-199 with the
+    quantiser in calibration mode: operands pass through, the fp carry is observed as the state)."""
+    B, T, H, K = q.shape
+    V = v.shape[-1]
+    C = chunk_size
+    nc = T // C
+    scale = K**-0.5 if scale is None else scale
+    qf, kf = _prepare_qk(q, k, rot_signs, dqk, scale)
+    tile = lambda x: x.reshape(B, nc, C, H, x.shape[-1]).permute(0, 3, 1, 2, 4)  # noqa: E731
+    Q, Kt, Vt = tile(qf), tile(kf), tile(v.float())
+    sc.observe("q_read", Q.reshape(B, H, nc * C, K))
+    sc.observe("k_local", Kt.reshape(B, H, nc * C, K))
+    sc.observe("v_local", Vt.reshape(B, H, nc * C, V))
+    if g is not None:
+        gc = g.float().reshape(B, nc, C, H).permute(0, 3, 1, 2).cumsum(-1)  # [B,H,nc,C]
+        d = gc[..., -1:] - gc
+        wk, wv = ((1 - eta) * d).exp().unsqueeze(-1), (eta * d).exp().unsqueeze(-1)
+        gam = gc[..., -1].exp()
+    else:
+        wk = wv = 1.0
+        gam = None
+    Kw, Vw = Kt * wk, Vt * wv
+    sc.observe("k_write", Kw.reshape(B, H, nc * C, K))
+    sc.observe("v_write", Vw.reshape(B, H, nc * C, V))
+    carry = torch.zeros(B, H, K, V, dtype=torch.float32, device=q.device)
+    for c in range(nc):
+        local = Kw[:, :, c].transpose(-1, -2) @ Vw[:, :, c]
+        carry = carry * gam[:, :, c, None, None] + local if gam is not None else carry + local
+        sc.observe("state", carry)
+    return sc

@@ -73,3 +73,12 @@ def run(entry, P, delta, like, debug=None):
     if debug is not None:
         debug["workspace"] = ws
     return ws
+
+
+def run_stage(entry, P, ws, like):
+    """Launch one pipeline stage (``lq_zoo_prologue_linear`` ...) on an already carved workspace."""
+    L = _cabi.lib()
+    fn = getattr(L, entry)
+    fn.argtypes = [C.POINTER(_cabi.ZooProblem), C.POINTER(_cabi.ZooWorkspace), C.c_void_p]
+    with torch.cuda.device(like.device):
+        _cabi.check(fn(C.byref(P), C.byref(ws.desc), _cabi.stream_of(like)), entry)
