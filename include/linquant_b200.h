@@ -79,13 +79,15 @@ size_t lq_zoo_workspace_bytes(const lq_zoo_problem* p, int delta_family);
  *   kwT [BH,NT,K,C]  k_write codes, token index contiguous            vlT [BH,NT,V,C]  v_local / e_local codes
  *   vwT [BH,NT,V,C]  v_write codes                                     hT  [BH,NT,V,K]  stored state entering the chunk
  *   gc  [BH,NT,C]    chunk-local cumulative log-decay (fp32)           wq  [BH,NT,C,K]  w_read codes (delta)
- *   u   [BH,NT,C,V]  WY right-hand side U in fp32 rounded to the act dtype grid (delta)
+ *   u   [BH,NT,C,V]  WY right-hand side U in the activation dtype (delta)
  *   fw  [BH,NT,C]    value-side share of the outer beta factor (delta)
  */
 typedef struct {
   int8_t *qq, *kl, *kwT, *vlT, *vwT, *hT, *wq;
-  float *gc, *u, *fw, *amat, *genv;
-  int8_t* gk; /* unused padding slot kept for ABI stability */
+  float* gc;
+  void* u;
+  float *fw, *amat, *genv;
+  void* reserved;
 } lq_zoo_workspace;
 int lq_zoo_carve_workspace(const lq_zoo_problem* p, int delta_family, void* workspace, size_t workspace_bytes,
                            lq_zoo_workspace* out);
@@ -106,6 +108,19 @@ int lq_zoo_output_scalar(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq
 
 /* Whole call of chunk_simple_gla_int8 (zoo/simple_gla.py:175-212): prologue + state pass + output. */
 int lq_simple_gla_fwd(const lq_zoo_problem* p, void* workspace, size_t workspace_bytes, lq_stream stream);
+
+/* Delta-rule WY prologue: q/k rows as above plus Gram matrix, (I+G)^-1 by forward substitution and the W / U
+ * products, in fp32-grade arithmetic (TF32 tensor-core MMA on exactly representable operands, left factor split
+ * in three). Replaces the torch-side _prep (zoo/gated_delta_rule.py:20-47) and the FLA prep kernels it may call
+ * (zoo/gated_delta_rule.py:139-156). */
+int lq_zoo_prologue_delta(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq_stream stream);
+
+/* Delta-rule state pass: stored INT8 state, INT8 W.S read, pseudo-values E, INT8 write product, fp32 carry.
+ * Replaces _delta_state_kernel (zoo/gated_delta_rule.py:51-136). */
+int lq_zoo_state_delta(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq_stream stream);
+
+/* Whole call of chunk_delta_int8 (zoo/gated_delta_rule.py:159-203): WY prologue + state pass + output. */
+int lq_delta_fwd(const lq_zoo_problem* p, void* workspace, size_t workspace_bytes, lq_stream stream);
 
 #ifdef __cplusplus
 }

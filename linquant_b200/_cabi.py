@@ -33,7 +33,7 @@ class ZooProblem(C.Structure):
 
 
 class ZooWorkspace(C.Structure):
-    _fields_ = [(n, C.c_void_p) for n in ("qq", "kl", "kwT", "vlT", "vwT", "hT", "wq", "gc", "u", "fw", "amat", "genv", "gk")]
+    _fields_ = [(n, C.c_void_p) for n in ("qq", "kl", "kwT", "vlT", "vwT", "hT", "wq", "gc", "u", "fw", "amat", "genv", "reserved")]
 
 
 class LinQuantError(RuntimeError):
@@ -100,7 +100,7 @@ _WS_LAYOUT = {  # name -> (torch dtype, lambda(BH,NT,C,K,V) -> shape)
     "hT": (torch.int8, lambda BH, NT, Cc, K, V: (BH, NT, V, K)),
     "wq": (torch.int8, lambda BH, NT, Cc, K, V: (BH, NT, Cc, K)),
     "gc": (torch.float32, lambda BH, NT, Cc, K, V: (BH, NT, Cc)),
-    "u": (torch.float32, lambda BH, NT, Cc, K, V: (BH, NT, Cc, V)),
+    "u": (None, lambda BH, NT, Cc, K, V: (BH, NT, Cc, V)),  # activation dtype
     "fw": (torch.float32, lambda BH, NT, Cc, K, V: (BH, NT, Cc)),
     "amat": (torch.float32, lambda BH, NT, Cc, K, V: (BH, NT, Cc, Cc)),
     "genv": (torch.float32, lambda BH, NT, Cc, K, V: (BH, NT, Cc)),
@@ -128,6 +128,8 @@ class Workspace:
             return None
         dt, shp = _WS_LAYOUT[name]
         pr = self.prob
+        if dt is None:
+            dt = torch.float16 if pr.act_dtype == LQ_F16 else torch.bfloat16
         shape = shp(pr.B * pr.H, pr.T // pr.chunk, pr.chunk, pr.K, pr.V)
         if name == "gc" and pr.decay == DECAY_DIAGONAL:
             shape = shape + (pr.K,)

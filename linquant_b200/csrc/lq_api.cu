@@ -70,11 +70,11 @@ static size_t carve(const lq_zoo_problem* p, int delta, void* ws, lq_zoo_workspa
   w.hT = cv.take<int8_t>(BH * NT * V * K);
   w.gc = cv.take<float>(BH * NT * C * (p->decay == LQ_DECAY_DIAGONAL ? K : 1));
   w.wq = delta ? cv.take<int8_t>(BH * NT * C * K) : nullptr;
-  w.u = delta ? cv.take<float>(BH * NT * C * V) : nullptr;
+  w.u = delta ? cv.take<uint16_t>(BH * NT * C * V) : nullptr;
   w.fw = delta ? cv.take<float>(BH * NT * C) : nullptr;
   w.amat = p->decay == LQ_DECAY_DIAGONAL ? cv.take<float>(BH * NT * C * C) : nullptr;
   w.genv = p->decay == LQ_DECAY_DIAGONAL ? cv.take<float>(BH * NT * C) : nullptr;
-  w.gk = nullptr;
+  w.reserved = nullptr;
   if (out) *out = w;
   return (cv.off + 255) & ~size_t(255);
 }
@@ -82,6 +82,8 @@ static size_t carve(const lq_zoo_problem* p, int delta, void* ws, lq_zoo_workspa
 int run_prologue_linear(const lq_zoo_problem* p, const lq_zoo_workspace* ws, int skip_v, cudaStream_t st);
 int run_state_linear(const lq_zoo_problem* p, const lq_zoo_workspace* ws, cudaStream_t st);
 int run_output_scalar(const lq_zoo_problem* p, const lq_zoo_workspace* ws, const float* s_local_value, cudaStream_t st);
+int run_prologue_delta(const lq_zoo_problem* p, const lq_zoo_workspace* ws, cudaStream_t st);
+int run_state_delta(const lq_zoo_problem* p, const lq_zoo_workspace* ws, cudaStream_t st);
 
 }  // namespace lq
 
@@ -111,4 +113,14 @@ extern "C" int lq_simple_gla_fwd(const lq_zoo_problem* p, void* workspace, size_
   if (int e = lq::run_prologue_linear(p, &ws, 0, st)) return e;
   if (int e = lq::run_state_linear(p, &ws, st)) return e;
   return lq::run_output_scalar(p, &ws, p->svl, st);
+}
+
+extern "C" int lq_delta_fwd(const lq_zoo_problem* p, void* workspace, size_t workspace_bytes, lq_stream stream) {
+  if (int e = lq::validate_zoo_problem(p, true, false)) return e;
+  lq_zoo_workspace ws;
+  if (int e = lq_zoo_carve_workspace(p, 1, workspace, workspace_bytes, &ws)) return e;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (int e = lq::run_prologue_delta(p, &ws, st)) return e;
+  if (int e = lq::run_state_delta(p, &ws, st)) return e;
+  return lq::run_output_scalar(p, &ws, p->sel, st);
 }

@@ -1,0 +1,499 @@
+// Delta-rule family (DeltaNet / Gated DeltaNet, none or scalar decay): WY prologue and the chunk-serial state pass.
+//
+// Prologue (one CTA per (batch*head, chunk), parallel over chunks):
+//   q, k rows as in the linear prologue (rescale, Walsh-Hadamard rotation, rounding, codes); the readout/write
+//   key is Hw = round(beta^((1-sigma)tau) * k). Then the WY representation of the chunk in fp32-grade arithmetic:
+//     G = tril( (beta^sigma k)(beta^(1-sigma) k)^T * exp(gc_i - gc_j), -1 )      TF32 MMA on exact operands
+//     T = (I + G)^-1                                                             forward substitution in smem
+//     W = T diag(beta^sigma exp(gc)) k ,  U = T diag(beta^sigma) v              3xTF32 split MMA (A split in three)
+//   W is rounded to the activation dtype and quantised per head (w_read codes); U is stored in the activation dtype.
+//   Operands k, v are fp16/bf16 values, exactly representable in TF32, and the fp32 left factor is split into three
+//   TF32 pieces, so every product is exact and only the fp32 accumulation rounds.
+//
+// State pass (one CTA per (batch*head, 32 value channels), serial over chunks, fp32 carry [v,k] in registers):
+//   hq = q8(carry)  -> stored state (global + shared);  ws = wq . hq (INT8 MMA);  E = (U - deq(ws)) * fw
+//   e_local codes from the activation-rounded E, e_write codes from E * Omega^eta;  carry <- gamma carry + deq(ew^T kw)
+//
+// Reference arithmetic: zoo/gated_delta_rule.py:20-47 (_prep), :51-115 (_delta_state_body);
+// reference.py:202-229 (_chunk_delta).
+#include "lq_zoo_rows.cuh"
+
+namespace lq {
+
+struct DeltaPrepArgs {
+  PrologueArgs pro;
+  const float *beta, *sw;
+  int8_t* wq;
+  void* u;
+  float* fw;
+  float sigma, tau;
+};
+
+__device__ __forceinline__ uint32_t tf32_rna(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float pow_exact01(float x, float e) { return e == 0.f ? 1.f : (e == 1.f ? x : powf(x, e)); }
+
+// acc[NT][4] += (T .* cw[None,:])[16 rows of m-tile mt, tokens 0..16mt+15] . B[tokens, NT*8 columns from n0]
+template <int NT>
+__device__ __forceinline__ void wy_product(float (&acc)[NT][4], const float* s_T, const float* s_cw, const float* s_B,
+                                           int LDB, int mt, int n0, int g, int j) {
+  const int ia = 16 * mt + g, ib = ia + 8;
+  for (int kk = 0; kk < 2 * mt + 2; ++kk) {
+    const int c0 = 8 * kk + j, c1 = c0 + 4;
+    const float x[4] = {s_T[ia * 68 + c0] * s_cw[c0], s_T[ib * 68 + c0] * s_cw[c0], s_T[ia * 68 + c1] * s_cw[c1],
+                        s_T[ib * 68 + c1] * s_cw[c1]};
+    uint32_t hi[4], mi[4], lo[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      hi[i] = tf32_rna(x[i]);
+      const float r1 = x[i] - __uint_as_float(hi[i]);
+      mi[i] = tf32_rna(r1);
+      lo[i] = __float_as_uint(r1 - __uint_as_float(mi[i]));
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const uint32_t b0 = __float_as_uint(s_B[c0 * LDB + n0 + 8 * nt + g]);
+      const uint32_t b1 = __float_as_uint(s_B[c1 * LDB + n0 + 8 * nt + g]);
+      mma_tf32(acc[nt], lo[0], lo[1], lo[2], lo[3], b0, b1);
+      mma_tf32(acc[nt], mi[0], mi[1], mi[2], mi[3], b0, b1);
+      mma_tf32(acc[nt], hi[0], hi[1], hi[2], hi[3], b0, b1);
+    }
+  }
+}
+
+template <typename T, int K, int V>
+__global__ void __launch_bounds__(256) zoo_prologue_delta_kernel(DeltaPrepArgs d) {
+  constexpr int C = kChunk, LDK = K + 8, LDV = V + 8;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  float* s_gc = reinterpret_cast<float*>(smem_raw);
+  float* s_fk = s_gc + C;
+  float* s_bs = s_fk + C;
+  float* s_b1 = s_bs + C;
+  float* s_hw = s_b1 + C;
+  float* s_cwW = s_hw + C;  // beta^sigma * exp(gc)
+  float* s_kf = s_cwW + C;
+  float* s_vf = s_kf + C * LDK;
+  float* s_G = s_vf + C * LDV;
+  float* s_T = s_G + C * 68;
+  uint32_t(*s_kw)[17] = reinterpret_cast<uint32_t(*)[17]>(s_T + C * 68);
+
+  const PrologueArgs& a = d.pro;
+  const int c = blockIdx.x, bh = blockIdx.y;
+  const int b = bh / a.H, h = bh % a.H;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, j = lane & 3;
+  const size_t tile = (size_t)bh * a.NT + c;
+  const float e_hw = (1.f - d.sigma) * d.tau;
+
+  if (warp == 0) {
+    if (a.g != nullptr) {
+      chunk_decay_scan(a.g, b, c, h, a.T, a.H, s_gc);
+    } else {
+      s_gc[lane] = 0.f;
+      s_gc[lane + 32] = 0.f;
+    }
+  }
+  __syncthreads();
+  if (tid < C) {
+    const float dd = s_gc[C - 1] - s_gc[tid];
+    s_fk[tid] = a.g ? expf((1.0f - a.eta) * dd) : 1.0f;
+    a.gc[tile * C + tid] = s_gc[tid];
+    const float bt = d.beta[((size_t)b * a.T + (size_t)c * C + tid) * a.H + h];
+    const float bs = pow_exact01(bt, d.sigma);
+    s_bs[tid] = bs;
+    s_b1[tid] = pow_exact01(bt, 1.f - d.sigma);
+    s_hw[tid] = pow_exact01(bt, e_hw);
+    s_cwW[tid] = a.g ? bs * expf(s_gc[tid]) : bs;
+    d.fw[tile * C + tid] = pow_exact01(bt, (1.f - d.sigma) * (1.f - d.tau));
+  }
+  __syncthreads();
+
+  prologue_qk_rows<T, K>(a, b, c, h, tile, s_fk, e_hw != 0.f ? s_hw : nullptr, s_kf, LDK, s_kw);
+  {
+    const T* vp = reinterpret_cast<const T*>(a.v);
+    for (int i = tid; i < C * (V / 8); i += 256) {
+      const int t = i / (V / 8), seg = i % (V / 8);
+      float x[8];
+      Act<T>::unpack8(*reinterpret_cast<const uint4*>(vp + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * V + 8 * seg), x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s_vf[t * LDV + 8 * seg + e] = x[e];
+    }
+  }
+  __syncthreads();
+
+  const int mt = warp & 3, nh = warp >> 2;
+  // ---- Gram matrix (strictly lower triangle)
+  {
+    const int ia = 16 * mt + g, ib = ia + 8;
+#pragma unroll
+    for (int n4 = 0; n4 < 4; ++n4) {
+      const int nt = 4 * nh + n4;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      if (8 * nt <= 16 * mt + 15) {
+        for (int kk = 0; kk < K / 8; ++kk) {
+          const int c0 = 8 * kk + j;
+          mma_tf32(acc, __float_as_uint(s_kf[ia * LDK + c0]), __float_as_uint(s_kf[ib * LDK + c0]),
+                   __float_as_uint(s_kf[ia * LDK + c0 + 4]), __float_as_uint(s_kf[ib * LDK + c0 + 4]),
+                   __float_as_uint(s_kf[(8 * nt + g) * LDK + c0]), __float_as_uint(s_kf[(8 * nt + g) * LDK + c0 + 4]));
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int jj = 8 * nt + 2 * j + e;
+        s_G[ia * 68 + jj] = (ia > jj) ? s_bs[ia] * s_b1[jj] * acc[e] * expf(s_gc[ia] - s_gc[jj]) : 0.f;
+        s_G[ib * 68 + jj] = (ib > jj) ? s_bs[ib] * s_b1[jj] * acc[2 + e] * expf(s_gc[ib] - s_gc[jj]) : 0.f;
+      }
+    }
+  }
+  __syncthreads();
+  // ---- T = (I + G)^-1: column col by four lanes (r = share of the row dot product); the column lives in registers
+  {
+    const int col = tid >> 2, r = tid & 3;
+    float tc[16];
+#pragma unroll
+    for (int m = 0; m < 16; ++m) tc[m] = 0.f;
+#pragma unroll
+    for (int i = 0; i < C; ++i) {
+      float part = 0.f;
+#pragma unroll
+      for (int m = 0; m <= (i - 1) / 4 && i > 0; ++m) {
+        if (4 * m + r < i) part = fmaf(s_G[i * 68 + 4 * m + r], tc[m], part);
+      }
+      part += __shfl_xor_sync(0xffffffffu, part, 1);
+      part += __shfl_xor_sync(0xffffffffu, part, 2);
+      const float val = (i == col ? 1.f : 0.f) - part;
+      if ((i & 3) == r) tc[i >> 2] = val;
+      if (r == 0) s_T[i * 68 + col] = val;
+    }
+  }
+  __syncthreads();
+  // ---- W = T diag(beta^sigma exp(gc)) k  -> w_read codes
+  {
+    constexpr int NTW = K / 16;
+    float acc[NTW][4];
+#pragma unroll
+    for (int nt = 0; nt < NTW; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    const int n0 = nh * (K / 2);
+    wy_product<NTW>(acc, s_T, s_cwW, s_kf, LDK, mt, n0, g, j);
+    const float inv_sw = 1.0f / d.sw[h];
+    const int ia = 16 * mt + g, ib = ia + 8;
+#pragma unroll
+    for (int nt = 0; nt < NTW; ++nt) {
+      const int col = n0 + 8 * nt + 2 * j;
+      const int a0 = q8(Act<T>::round(acc[nt][0]), inv_sw, a.qmax), a1 = q8(Act<T>::round(acc[nt][1]), inv_sw, a.qmax);
+      const int b0 = q8(Act<T>::round(acc[nt][2]), inv_sw, a.qmax), b1 = q8(Act<T>::round(acc[nt][3]), inv_sw, a.qmax);
+      *reinterpret_cast<uint16_t*>(d.wq + (tile * C + ia) * K + col) = (uint16_t)((a0 & 0xff) | ((a1 & 0xff) << 8));
+      *reinterpret_cast<uint16_t*>(d.wq + (tile * C + ib) * K + col) = (uint16_t)((b0 & 0xff) | ((b1 & 0xff) << 8));
+    }
+  }
+  // ---- U = T diag(beta^sigma) v  -> activation dtype
+  {
+    constexpr int NTU = V / 16;
+    float acc[NTU][4];
+#pragma unroll
+    for (int nt = 0; nt < NTU; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    const int n0 = nh * (V / 2);
+    wy_product<NTU>(acc, s_T, s_bs, s_vf, LDV, mt, n0, g, j);
+    const int ia = 16 * mt + g, ib = ia + 8;
+    T* up = reinterpret_cast<T*>(d.u);
+#pragma unroll
+    for (int nt = 0; nt < NTU; ++nt) {
+      const int col = n0 + 8 * nt + 2 * j;
+      *reinterpret_cast<uint32_t*>(up + (tile * C + ia) * V + col) = Act<T>::pack2(acc[nt][0], acc[nt][1]);
+      *reinterpret_cast<uint32_t*>(up + (tile * C + ib) * V + col) = Act<T>::pack2(acc[nt][2], acc[nt][3]);
+    }
+  }
+  uint32_t* kw_out = reinterpret_cast<uint32_t*>(a.kwT + tile * (size_t)(K * C));
+  for (int i = tid; i < K * 16; i += 256) kw_out[i] = s_kw[i >> 4][i & 15];
+}
+
+// ------------------------------------------------------------------------------------------------ state pass
+struct DeltaStateArgs {
+  const int8_t *wq, *kwT;
+  const void* u;
+  const float *fw, *gc, *skw, *sw, *sel, *sew, *ss;
+  int8_t *hT, *elT;
+  float* final_state;
+  int H, NT, use_g;
+  float eta, qmax;
+};
+
+template <int ROWB>
+__device__ __forceinline__ int swz_row(int row, int chunk) {
+  if (ROWB == 128) return row * 128 + ((chunk ^ ((row & 1) << 2)) << 4);
+  return row * 64 + (chunk << 4);
+}
+
+template <typename T, int K, int V>
+__global__ void __launch_bounds__(128) zoo_state_delta_kernel(DeltaStateArgs a) {
+  constexpr int C = 64, BV = 32;
+  constexpr int NTK = K / 32;  // key n-tiles per warp in the carry layout
+  constexpr int KK = K / 64;
+  __shared__ __align__(128) uint8_t s_h[BV * K];
+  __shared__ __align__(128) uint8_t s_ew[BV * C];
+  __shared__ __align__(128) uint8_t s_el[BV * C];
+
+  const int v0 = blockIdx.x * BV;
+  const int bh = blockIdx.y, h = bh % a.H;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, j = lane & 3;
+  const int kw0 = warp * (K / 4);
+  const int kown = kw0 + 2 * NTK * j;  // first of the 2*NTK consecutive key channels this thread owns
+
+  // carry rows (value channels, local index) and their scales
+  float sew_r[4], iss_r[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int vl = 16 * (i >> 1) + g + 8 * (i & 1);
+    sew_r[i] = a.sew[h * V + v0 + vl];
+    iss_r[i] = 1.0f / a.ss[h * V + v0 + vl];
+  }
+  float skw[2 * NTK];
+#pragma unroll
+  for (int i = 0; i < 2 * NTK; ++i) skw[i] = a.skw[h * K + kown + i];
+  // E columns: eight consecutive value channels v0 + 8j .. + 7
+  float ss_c[8], isel_c[8], isew_c[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    ss_c[i] = a.ss[h * V + v0 + 8 * j + i];
+    isel_c[i] = 1.0f / a.sel[h * V + v0 + 8 * j + i];
+    isew_c[i] = 1.0f / a.sew[h * V + v0 + 8 * j + i];
+  }
+  const float sw = a.sw[h];
+
+  int krow[NTK];
+#pragma unroll
+  for (int nt = 0; nt < NTK; ++nt) krow[nt] = kw0 + 2 * NTK * (g >> 1) + 2 * nt + (g & 1);
+
+  const size_t base_tile = (size_t)bh * a.NT;
+  const int ta = 16 * warp + g, tb = ta + 8;
+  const T* up = reinterpret_cast<const T*>(a.u);
+
+  float carry[2][NTK][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NTK; ++nt) carry[mt][nt][0] = carry[mt][nt][1] = carry[mt][nt][2] = carry[mt][nt][3] = 0.f;
+
+  uint4 wa[KK], wb[KK], ua, ub, kb[NTK];
+  float fwa, fwb, gca, gcb, glast;
+  auto fetch = [&](int c, uint4 (&wa_)[KK], uint4 (&wb_)[KK], uint4& ua_, uint4& ub_, uint4 (&kb_)[NTK], float& fwa_,
+                   float& fwb_, float& gca_, float& gcb_, float& gl_) {
+    const size_t tile = base_tile + c;
+    const int8_t* wqc = a.wq + tile * (size_t)(C * K);
+#pragma unroll
+    for (int kk = 0; kk < KK; ++kk) {
+      wa_[kk] = __ldg(reinterpret_cast<const uint4*>(wqc + ta * K + 64 * kk + 16 * j));
+      wb_[kk] = __ldg(reinterpret_cast<const uint4*>(wqc + tb * K + 64 * kk + 16 * j));
+    }
+    ua_ = __ldg(reinterpret_cast<const uint4*>(up + (tile * C + ta) * V + v0 + 8 * j));
+    ub_ = __ldg(reinterpret_cast<const uint4*>(up + (tile * C + tb) * V + v0 + 8 * j));
+    const int8_t* kwc = a.kwT + tile * (size_t)(K * C);
+#pragma unroll
+    for (int nt = 0; nt < NTK; ++nt) kb_[nt] = __ldg(reinterpret_cast<const uint4*>(kwc + krow[nt] * C + 16 * j));
+    fwa_ = __ldg(a.fw + tile * C + ta);
+    fwb_ = __ldg(a.fw + tile * C + tb);
+    gca_ = a.use_g ? __ldg(a.gc + tile * C + ta) : 0.f;
+    gcb_ = a.use_g ? __ldg(a.gc + tile * C + tb) : 0.f;
+    gl_ = a.use_g ? __ldg(a.gc + tile * C + C - 1) : 0.f;
+  };
+  fetch(0, wa, wb, ua, ub, kb, fwa, fwb, gca, gcb, glast);
+
+  for (int c = 0; c < a.NT; ++c) {
+    const size_t tile = base_tile + c;
+    uint4 nwa[KK], nwb[KK], nua = ua, nub = ub, nkb[NTK];
+    float nfwa = 0.f, nfwb = 0.f, ngca = 0.f, ngcb = 0.f, ngl = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < KK; ++kk) { nwa[kk] = wa[kk]; nwb[kk] = wb[kk]; }
+#pragma unroll
+    for (int nt = 0; nt < NTK; ++nt) nkb[nt] = kb[nt];
+    if (c + 1 < a.NT) fetch(c + 1, nwa, nwb, nua, nub, nkb, nfwa, nfwb, ngca, ngcb, ngl);
+
+    // ---- 1. INT8 copy of the carry entering the chunk: global stored state + shared B operand
+    {
+      int8_t* hc = a.hT + tile * (size_t)(V * K);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int mt = i >> 1, hi = i & 1;
+        const int vl = 16 * mt + g + 8 * hi;
+        int cd[2 * NTK];
+#pragma unroll
+        for (int nt = 0; nt < NTK; ++nt) {
+          cd[2 * nt] = q8(carry[mt][nt][2 * hi], iss_r[i], 127.f);
+          cd[2 * nt + 1] = q8(carry[mt][nt][2 * hi + 1], iss_r[i], 127.f);
+        }
+        uint8_t* sdst = s_h + swz_row<K>(vl, kown >> 4) + (kown & 15);
+        int8_t* gdst = hc + (size_t)(v0 + vl) * K + kown;
+        if (NTK == 4) {
+          const uint2 w = make_uint2(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4 % (2 * NTK)], cd[5 % (2 * NTK)],
+                                                                            cd[6 % (2 * NTK)], cd[7 % (2 * NTK)]));
+          *reinterpret_cast<uint2*>(sdst) = w;
+          *reinterpret_cast<uint2*>(gdst) = w;
+        } else {
+          const uint32_t w = pack4(cd[0], cd[1], cd[2], cd[3]);
+          *reinterpret_cast<uint32_t*>(sdst) = w;
+          *reinterpret_cast<uint32_t*>(gdst) = w;
+        }
+      }
+    }
+    __syncthreads();
+
+    // ---- 2. ws = wq . hq ; E ; e_local / e_write codes
+    {
+      int acc[4][4];
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0;
+        const int vr = 8 * (g >> 1) + 2 * nt + (g & 1);
+#pragma unroll
+        for (int kk = 0; kk < KK; ++kk) {
+          const uint4 bs = *reinterpret_cast<const uint4*>(s_h + swz_row<K>(vr, 4 * kk + j));
+          mma_s8(acc[nt], wa[kk].x, wb[kk].x, wa[kk].y, wb[kk].y, bs.x, bs.y);
+          mma_s8(acc[nt], wa[kk].z, wb[kk].z, wa[kk].w, wb[kk].w, bs.z, bs.w);
+        }
+      }
+      float Ua[8], Ub[8];
+      Act<T>::unpack8(ua, Ua);
+      Act<T>::unpack8(ub, Ub);
+      const float fva = a.use_g ? expf(a.eta * (glast - gca)) : 1.f;
+      const float fvb = a.use_g ? expf(a.eta * (glast - gcb)) : 1.f;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int i = 2 * nt + e;
+          const int vl = 8 * j + i;
+          const float wsa = __fmul_rn(__fmul_rn((float)acc[nt][e], sw), ss_c[i]);
+          const float wsb = __fmul_rn(__fmul_rn((float)acc[nt][2 + e], sw), ss_c[i]);
+          const float Ea = __fmul_rn(__fsub_rn(Ua[i], wsa), fwa);
+          const float Eb = __fmul_rn(__fsub_rn(Ub[i], wsb), fwb);
+          s_el[vl * C + ta] = (uint8_t)q8(Act<T>::round(Ea), isel_c[i], a.qmax);
+          s_el[vl * C + tb] = (uint8_t)q8(Act<T>::round(Eb), isel_c[i], a.qmax);
+          s_ew[vl * C + ta] = (uint8_t)q8(__fmul_rn(Ea, fva), isew_c[i], a.qmax);
+          s_ew[vl * C + tb] = (uint8_t)q8(__fmul_rn(Eb, fvb), isew_c[i], a.qmax);
+        }
+      }
+    }
+    __syncthreads();
+
+    // ---- 3. write product and carry update; e_local tile out
+    {
+      reinterpret_cast<uint4*>(a.elT + tile * (size_t)(V * C) + (size_t)v0 * C)[tid] = reinterpret_cast<const uint4*>(s_el)[tid];
+      const float gam = a.use_g ? expf(glast) : 1.0f;
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        const uint4 ea = *reinterpret_cast<const uint4*>(s_ew + (16 * mt + g) * C + 16 * j);
+        const uint4 eb = *reinterpret_cast<const uint4*>(s_ew + (16 * mt + g + 8) * C + 16 * j);
+#pragma unroll
+        for (int nt = 0; nt < NTK; ++nt) {
+          int acc[4] = {0, 0, 0, 0};
+          mma_s8(acc, ea.x, eb.x, ea.y, eb.y, kb[nt].x, kb[nt].y);
+          mma_s8(acc, ea.z, eb.z, ea.w, eb.w, kb[nt].z, kb[nt].w);
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float ta_ = __fmul_rn(__fmul_rn((float)acc[e], skw[2 * nt + e]), sew_r[2 * mt]);
+            const float tb_ = __fmul_rn(__fmul_rn((float)acc[2 + e], skw[2 * nt + e]), sew_r[2 * mt + 1]);
+            carry[mt][nt][e] = fmaf(carry[mt][nt][e], gam, ta_);
+            carry[mt][nt][2 + e] = fmaf(carry[mt][nt][2 + e], gam, tb_);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int kk = 0; kk < KK; ++kk) { wa[kk] = nwa[kk]; wb[kk] = nwb[kk]; }
+#pragma unroll
+    for (int nt = 0; nt < NTK; ++nt) kb[nt] = nkb[nt];
+    ua = nua; ub = nub; fwa = nfwa; fwb = nfwb; gca = ngca; gcb = ngcb; glast = ngl;
+  }
+
+  if (a.final_state != nullptr) {
+    float* fs = a.final_state + (size_t)bh * K * V;
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < NTK; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int kk_ = kown + 2 * nt + e;
+          fs[(size_t)kk_ * V + v0 + 16 * mt + g] = carry[mt][nt][e];
+          fs[(size_t)kk_ * V + v0 + 16 * mt + g + 8] = carry[mt][nt][2 + e];
+        }
+  }
+}
+
+int validate_zoo_problem(const lq_zoo_problem* p, bool delta, bool diagonal);
+void fill_prologue_args(const lq_zoo_problem* p, const lq_zoo_workspace* ws, PrologueArgs& a);
+
+template <typename T, int K, int V>
+static int launch_delta_prep(const DeltaPrepArgs& d, int BH, cudaStream_t st) {
+  constexpr size_t smem = sizeof(float) * (6 * 64 + 64 * (K + 8) + 64 * (V + 8) + 2 * 64 * 68) + sizeof(uint32_t) * K * 17;
+  cudaError_t e = cudaFuncSetAttribute(zoo_prologue_delta_kernel<T, K, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return fail(LQ_ERR_LAUNCH, "delta prologue: cannot opt in to %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+  zoo_prologue_delta_kernel<T, K, V><<<dim3(d.pro.NT, BH), 256, smem, st>>>(d);
+  return check_launch("zoo_prologue_delta_kernel");
+}
+
+template <typename T>
+static int dispatch_delta_prep(const lq_zoo_problem* p, const DeltaPrepArgs& d, cudaStream_t st) {
+  const int BH = p->B * p->H;
+  if (p->K == 64 && p->V == 64) return launch_delta_prep<T, 64, 64>(d, BH, st);
+  if (p->K == 64 && p->V == 128) return launch_delta_prep<T, 64, 128>(d, BH, st);
+  if (p->K == 128 && p->V == 64) return launch_delta_prep<T, 128, 64>(d, BH, st);
+  if (p->K == 128 && p->V == 128) return launch_delta_prep<T, 128, 128>(d, BH, st);
+  return fail(LQ_ERR_UNSUPPORTED, "delta prologue: K and V must be 64 or 128");
+}
+
+int run_prologue_delta(const lq_zoo_problem* p, const lq_zoo_workspace* ws, cudaStream_t st) {
+  DeltaPrepArgs d;
+  fill_prologue_args(p, ws, d.pro);
+  d.beta = p->beta; d.sw = p->sw; d.wq = ws->wq; d.u = ws->u; d.fw = ws->fw; d.sigma = p->sigma; d.tau = p->tau;
+  if (p->act_dtype == LQ_F16) return dispatch_delta_prep<__half>(p, d, st);
+  if (p->act_dtype == LQ_BF16) return dispatch_delta_prep<__nv_bfloat16>(p, d, st);
+  return fail(LQ_ERR_UNSUPPORTED, "delta prologue: activation dtype must be f16 or bf16");
+}
+
+template <typename T>
+static int dispatch_delta_state(const lq_zoo_problem* p, const DeltaStateArgs& a, cudaStream_t st) {
+  dim3 grid(p->V / 32, p->B * p->H), block(128);
+  if (p->K == 64 && p->V == 64) zoo_state_delta_kernel<T, 64, 64><<<grid, block, 0, st>>>(a);
+  else if (p->K == 64 && p->V == 128) zoo_state_delta_kernel<T, 64, 128><<<grid, block, 0, st>>>(a);
+  else if (p->K == 128 && p->V == 64) zoo_state_delta_kernel<T, 128, 64><<<grid, block, 0, st>>>(a);
+  else if (p->K == 128 && p->V == 128) zoo_state_delta_kernel<T, 128, 128><<<grid, block, 0, st>>>(a);
+  else return fail(LQ_ERR_UNSUPPORTED, "delta state: K and V must be 64 or 128");
+  return check_launch("zoo_state_delta_kernel");
+}
+
+int run_state_delta(const lq_zoo_problem* p, const lq_zoo_workspace* ws, cudaStream_t st) {
+  DeltaStateArgs a;
+  a.wq = ws->wq; a.kwT = ws->kwT; a.u = ws->u; a.fw = ws->fw; a.gc = ws->gc;
+  a.skw = p->skw; a.sw = p->sw; a.sel = p->sel; a.sew = p->sew; a.ss = p->sstate;
+  a.hT = ws->hT; a.elT = ws->vlT; a.final_state = p->final_state;
+  a.H = p->H; a.NT = p->T / p->chunk; a.use_g = p->g != nullptr; a.eta = p->eta; a.qmax = p->qmax;
+  if (p->act_dtype == LQ_F16) return dispatch_delta_state<__half>(p, a, st);
+  if (p->act_dtype == LQ_BF16) return dispatch_delta_state<__nv_bfloat16>(p, a, st);
+  return fail(LQ_ERR_UNSUPPORTED, "delta state: activation dtype must be f16 or bf16");
+}
+
+}  // namespace lq
+
+extern "C" int lq_zoo_prologue_delta(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq_stream stream) {
+  if (int e = lq::validate_zoo_problem(p, true, false)) return e;
+  if (!ws) return lq::fail(LQ_ERR_NULL, "delta prologue: workspace descriptor is null");
+  return lq::run_prologue_delta(p, ws, (cudaStream_t)stream);
+}
+
+extern "C" int lq_zoo_state_delta(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq_stream stream) {
+  if (int e = lq::validate_zoo_problem(p, true, false)) return e;
+  if (!ws) return lq::fail(LQ_ERR_NULL, "delta state: workspace descriptor is null");
+  return lq::run_state_delta(p, ws, (cudaStream_t)stream);
+}

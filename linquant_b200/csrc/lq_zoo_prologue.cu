@@ -12,41 +12,9 @@
 // Reference arithmetic: zoo/simple_gla.py:16-20 (_q8), :57-67 (write gating and codes), :129-130,:149 (read /
 // local codes), :191 (chunk-local cumsum; torch accumulates a float cumsum in double on the CPU oracle, so the
 // scan here runs in double too), reference.py:41-47 (rotate -> round to activation dtype -> scale).
-#include "lq_common.cuh"
+#include "lq_zoo_rows.cuh"
 
 namespace lq {
-
-struct PrologueArgs {
-  const void *q, *k, *v;
-  const float *g, *signs, *dqk;
-  const float *sq, *sk, *skw, *svl, *svw;
-  int8_t *qq, *kl, *kwT, *vlT, *vwT;
-  float* gc;
-  int T, H, NT;
-  float scale, eta, qmax;
-  int skip_v;  // delta family: the value operand is produced by the WY kernel instead
-};
-
-constexpr int kChunk = 64;
-
-__device__ __forceinline__ void chunk_decay_scan(const float* g, int b, int c, int h, int T, int H, float* s_gc) {
-  // warp 0 only: inclusive prefix sum of 64 log-decays, accumulated in double
-  const int lane = threadIdx.x & 31;
-  double run = 0.0;
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int t = half * 32 + lane;
-    double x = (double)g[((size_t)b * T + (size_t)c * kChunk + t) * H + h];
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      double y = __shfl_up_sync(0xffffffffu, x, d);
-      if (lane >= d) x += y;
-    }
-    x += run;
-    s_gc[t] = (float)x;
-    run = __shfl_sync(0xffffffffu, x, 31);
-  }
-}
 
 template <typename T, int K, int V>
 __global__ void __launch_bounds__(256) zoo_prologue_linear_kernel(PrologueArgs a) {
@@ -78,74 +46,7 @@ __global__ void __launch_bounds__(256) zoo_prologue_linear_kernel(PrologueArgs a
   }
   __syncthreads();
 
-  const float inv_sq = 1.0f / a.sq[h], inv_sk = 1.0f / a.sk[h];
-  // ------------------------------------------------------------------ q and k rows (K channels)
-  {
-    constexpr int LPR = K / 8, G = 32 / LPR;
-    const int r = lane % LPR, grp = lane / LPR;
-    float sgn[8], dmul[8], dinv[8], inv_kw[8];
-    const bool rot = a.signs != nullptr;
-    const float norm = rsqrtf((float)K);  // K is a power of four times {1,2}: 1/8 for K=64, 2^-3.5 for K=128
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      sgn[j] = rot ? a.signs[8 * r + j] * (K == 64 ? 0.125f : 0.08838834764831845f) : 1.0f;
-      dmul[j] = a.dqk ? a.dqk[h * K + 8 * r + j] : 1.0f;
-      dinv[j] = 1.0f / dmul[j];
-      inv_kw[j] = 1.0f / a.skw[h * K + 8 * r + j];
-    }
-    (void)norm;
-    const T* qp = reinterpret_cast<const T*>(a.q);
-    const T* kp = reinterpret_cast<const T*>(a.k);
-    for (int tg = warp * G + grp; tg < C / 4; tg += 8 * G) {
-      uint32_t kwp[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) kwp[j] = 0u;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int t = 4 * tg + i;
-        const size_t row = (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K + 8 * r;
-        const size_t orow = (tile * C + t) * K + 8 * r;
-        float x[8];
-        int cd[8];
-        // q
-        Act<T>::unpack8(*reinterpret_cast<const uint4*>(qp + row), x);
-        if (a.dqk) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(x[j], dmul[j]);
-        }
-        if (rot) {
-          fwht8<LPR>(x, r);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) x[j] = Act<T>::round(__fmul_rn(x[j], sgn[j]));
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) cd[j] = q8(__fmul_rn(x[j], a.scale), inv_sq, a.qmax);
-        *reinterpret_cast<uint2*>(a.qq + orow) =
-            make_uint2(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4], cd[5], cd[6], cd[7]));
-        // k
-        Act<T>::unpack8(*reinterpret_cast<const uint4*>(kp + row), x);
-        if (a.dqk) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(x[j], dinv[j]);
-        }
-        if (rot) {
-          fwht8<LPR>(x, r);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) x[j] = Act<T>::round(__fmul_rn(x[j], sgn[j]));
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) cd[j] = q8(x[j], inv_sk, a.qmax);
-        *reinterpret_cast<uint2*>(a.kl + orow) =
-            make_uint2(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4], cd[5], cd[6], cd[7]));
-        const float fk = s_fk[t];
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          kwp[j] |= ((uint32_t)q8(__fmul_rn(x[j], fk), inv_kw[j], a.qmax) & 0xffu) << (8 * i);
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) s_kw[8 * r + j][tg] = kwp[j];
-    }
-  }
+  prologue_qk_rows<T, K>(a, b, c, h, tile, s_fk, nullptr, nullptr, 0, s_kw);
   // ------------------------------------------------------------------ v rows (V channels)
   if (!a.skip_v) {
     constexpr int LPR = V / 8, G = 32 / LPR;
@@ -208,13 +109,18 @@ static int launch_prologue(const lq_zoo_problem* p, const PrologueArgs& a, cudaS
 
 int validate_zoo_problem(const lq_zoo_problem* p, bool delta, bool diagonal);
 
-int run_prologue_linear(const lq_zoo_problem* p, const lq_zoo_workspace* ws, int skip_v, cudaStream_t st) {
-  PrologueArgs a;
+void fill_prologue_args(const lq_zoo_problem* p, const lq_zoo_workspace* ws, PrologueArgs& a) {
   a.q = p->q; a.k = p->k; a.v = p->v; a.g = p->g; a.signs = p->rot_signs; a.dqk = p->dqk;
   a.sq = p->sq; a.sk = p->sk; a.skw = p->skw; a.svl = p->svl; a.svw = p->svw;
   a.qq = ws->qq; a.kl = ws->kl; a.kwT = ws->kwT; a.vlT = ws->vlT; a.vwT = ws->vwT; a.gc = ws->gc;
   a.T = p->T; a.H = p->H; a.NT = p->T / p->chunk;
-  a.scale = p->scale; a.eta = p->eta; a.qmax = p->qmax; a.skip_v = skip_v;
+  a.scale = p->scale; a.eta = p->eta; a.qmax = p->qmax; a.skip_v = 0;
+}
+
+int run_prologue_linear(const lq_zoo_problem* p, const lq_zoo_workspace* ws, int skip_v, cudaStream_t st) {
+  PrologueArgs a;
+  fill_prologue_args(p, ws, a);
+  a.skip_v = skip_v;
   if (p->act_dtype == LQ_F16) return launch_prologue<__half>(p, a, st);
   if (p->act_dtype == LQ_BF16) return launch_prologue<__nv_bfloat16>(p, a, st);
   return fail(LQ_ERR_UNSUPPORTED, "prologue: activation dtype must be f16 or bf16");

@@ -1,3 +1,4 @@
 """INT8 chunk kernels of the zoo lineage (same names as ``linquant/kernels/zoo/__init__.py``)."""
 
+from .gated_delta_rule import chunk_delta_int8  # noqa: F401
 from .simple_gla import chunk_simple_gla_int8  # noqa: F401

@@ -1,0 +1,83 @@
+"""chunk_delta_int8 (CUDA, through the C ABI) against the CPU oracle. Mirrors tests/test_kernel_delta.py and the
+delta rows of tests/test_kernel_regimes.py of the reference."""
+
+import pytest
+import torch
+
+from tests.helpers import OracleRun, code_mismatch, reference_check, rel_l2, zoo_inputs
+
+pytestmark = pytest.mark.gpu
+B, T, H, K, V = 2, 512, 4, 64, 128
+
+
+def run_case(q, k, v, g, beta, *, policy="kernel_static", bits=8, eta=1.0, sigma=1.0, tau=1.0, rot=False, dqk=None,
+             label="", budget=1e-3):
+    from linquant_b200.kernels.zoo.gated_delta_rule import chunk_delta_int8
+    from oracle import zoo_oracle as zo
+
+    Kd = q.shape[-1]
+    R, signs = zo.signed_hadamard(Kd, 3) if rot else (None, None)
+    orc = OracleRun(q, k, v, g, beta, family="delta", decay="none" if g is None else "scalar", policy=policy, bits=bits,
+                    eta=eta, sigma=sigma, tau=tau, rot_qk=R, dqk=dqk)
+    ref, ref_state = orc.lineage()
+    exact = orc.exact()
+    dbg = {}
+    dev = "cuda"
+    out, ht = chunk_delta_int8(q.to(dev), k.to(dev), v.to(dev), None if g is None else g.to(dev), beta.to(dev),
+                               orc.scales(dev), sigma=sigma, tau=tau, eta=eta, scale=Kd**-0.5, chunk_size=64, bits=bits,
+                               output_final_state=True, rot=signs, dqk=None if dqk is None else dqk.to(dev), _debug=dbg)
+    torch.cuda.synchronize()
+    ws = dbg["workspace"]
+    Bq, Tq, Hq, _ = q.shape
+    NT = Tq // 64
+    tile = lambda name: ws.view(name).view(Bq, Hq, NT, *ws.view(name).shape[2:])  # noqa: E731
+    fr = {}
+    fr["q"] = code_mismatch(tile("qq"), orc.codes("q_read"), f"{label} q codes", budget)
+    fr["k_local"] = code_mismatch(tile("kl"), orc.codes("k_local"), f"{label} Hw local codes", budget)
+    fr["k_write"] = code_mismatch(tile("kwT").transpose(-1, -2), orc.codes("k_write"), f"{label} Hw write codes", budget)
+    fr["w_read"] = code_mismatch(tile("wq"), orc.codes("w_read"), f"{label} W codes", budget)
+    fr["e_local"] = code_mismatch(tile("vlT").transpose(-1, -2), orc.codes("e_local"), f"{label} E local codes", budget)
+    st = orc.codes("state")
+    hT = tile("hT").transpose(-1, -2)
+    assert int(hT[:, :, 0].abs().max()) == 0
+    if NT > 1:
+        fr["state"] = code_mismatch(hT[:, :, 1:], st[:, :, :-1], f"{label} stored state codes", budget)
+    err = rel_l2(out, ref)
+    print(f"{label}: tie fractions {fr} rel-L2 {err:.2e}")
+    assert err <= 2e-3, f"{label}: output rel-L2 {err:.3e} vs the quantised emulation"
+    reference_check(out, ref, exact, label)
+    assert rel_l2(ht, ref_state) <= 1e-3, f"{label}: final fp32 carry {rel_l2(ht, ref_state):.2e}"
+    return out
+
+
+@pytest.mark.parametrize("decay", [False, True])
+@pytest.mark.parametrize("sigma,tau,eta", [(1.0, 1.0, 1.0), (0.0, 1.0, 1.0), (0.5, 0.5, 1.0), (1.0, 1.0, 0.0), (0.0, 1.0, 0.5)])
+def test_delta_kernel_matches_oracle(decay, sigma, tau, eta):
+    if not decay and eta != 1.0:
+        pytest.skip("eta needs a decay")
+    q, k, v, g, beta = zoo_inputs(B, T, H, K, V, decay="scalar" if decay else "none", delta=True)
+    run_case(q, k, v, g, beta, sigma=sigma, tau=tau, eta=eta, label=f"decay={decay} sigma={sigma} tau={tau} eta={eta}")
+
+
+@pytest.mark.parametrize("policy,bits", [("kernel_pt", 8), ("kernel_pt", 6), ("kernel_ptk", 8), ("kernel_static", 6)])
+def test_regime_and_bits(policy, bits):
+    q, k, v, g, beta = zoo_inputs(B, T, H, K, V, decay="scalar", delta=True)
+    run_case(q, k, v, g, beta, policy=policy, bits=bits, label=f"delta {policy} bits={bits}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("Kd,Vd", [(128, 128), (64, 64), (128, 64)])
+def test_shapes_dtypes_fused_rotation(dtype, Kd, Vd):
+    q, k, v, g, beta = zoo_inputs(2, 256, 3, Kd, Vd, decay="scalar", delta=True, dtype=dtype, seed=1)
+    run_case(q, k, v, g, beta, policy="kernel_ptk", sigma=0.5, rot=True, label=f"delta rot {dtype} K={Kd} V={Vd}")
+
+
+def test_gated_deltanet_config_slice():
+    """The Gated DeltaNet benchmark configuration on a slice: bf16, kernel_ptk, D_QK with alpha 0.5, sigma 0.5."""
+    from linquant_b200 import invariances as inv
+    from linquant_b200.synthetic import make_inputs
+
+    x = make_inputs("gated_deltanet", seed=4, B=1, T=512)
+    q, k, v, g, beta = (x[n][:, :, :4].contiguous() for n in ("q", "k", "v", "g", "beta"))
+    dqk = inv.dqk_from_stats(q, k, 0.5)
+    run_case(q, k, v, g, beta, policy="kernel_ptk", sigma=0.5, rot=True, dqk=dqk, label="gated deltanet slice")
