@@ -81,13 +81,16 @@ size_t lq_zoo_workspace_bytes(const lq_zoo_problem* p, int delta_family);
  *   gc  [BH,NT,C]    chunk-local cumulative log-decay (fp32)           wq  [BH,NT,C,K]  w_read codes (delta)
  *   u   [BH,NT,C,V]  WY right-hand side U in the activation dtype (delta)
  *   fw  [BH,NT,C]    value-side share of the outer beta factor (delta)
+ * Diagonal decay adds gc [BH,NT,C,K], amat, genv, gcl (see the fields below).
  */
 typedef struct {
   int8_t *qq, *kl, *kwT, *vlT, *vwT, *hT, *wq;
   float* gc;
   void* u;
-  float *fw, *amat, *genv;
-  void* reserved;
+  float* fw;
+  void* amat;  /* [BH,NT,C,C] fp16 intra-chunk matrix (diagonal decay) */
+  float* genv; /* [BH,NT,C]   log of the scalar write envelope (diagonal decay) */
+  float* gcl;  /* [BH,NT,K]   cumulative log-decay at the chunk end (diagonal decay) */
 } lq_zoo_workspace;
 int lq_zoo_carve_workspace(const lq_zoo_problem* p, int delta_family, void* workspace, size_t workspace_bytes,
                            lq_zoo_workspace* out);
@@ -121,6 +124,25 @@ int lq_zoo_state_delta(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq_s
 
 /* Whole call of chunk_delta_int8 (zoo/gated_delta_rule.py:159-203): WY prologue + state pass + output. */
 int lq_delta_fwd(const lq_zoo_problem* p, void* workspace, size_t workspace_bytes, lq_stream stream);
+
+/* Diagonal (per-channel) decay, row pass: chunk-local cumulative log-decay per channel, log envelope, pre-decayed
+ * q_read codes, gated k_write codes, and for the linear family the value codes. Replaces the torch-side cumsum /
+ * amax (zoo/gla.py:249-250, zoo/kda.py:168-170) and the operand quantisation inside _gla_state_body /
+ * _gla_output_body (zoo/gla.py:137-140,201). */
+int lq_zoo_diag_rows(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq_stream stream);
+
+/* Diagonal decay, intra-chunk matrix A in 16-token secondary chunks. Replaces _gla_A_inter and _gla_A_intra
+ * (zoo/gla.py:27-99). */
+int lq_zoo_diag_amat(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq_stream stream);
+
+/* KDA WY prep with per-channel Gram weights. Replaces _prep / _prep_fla (zoo/kda.py:22-65). */
+int lq_zoo_kda_wy(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq_stream stream);
+
+/* Whole call of chunk_gla_int8 (zoo/gla.py:235-279). */
+int lq_gla_fwd(const lq_zoo_problem* p, void* workspace, size_t workspace_bytes, lq_stream stream);
+
+/* Whole call of chunk_kda_int8 (zoo/kda.py:154-203). */
+int lq_kda_fwd(const lq_zoo_problem* p, void* workspace, size_t workspace_bytes, lq_stream stream);
 
 #ifdef __cplusplus
 }

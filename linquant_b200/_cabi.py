@@ -33,7 +33,7 @@ class ZooProblem(C.Structure):
 
 
 class ZooWorkspace(C.Structure):
-    _fields_ = [(n, C.c_void_p) for n in ("qq", "kl", "kwT", "vlT", "vwT", "hT", "wq", "gc", "u", "fw", "amat", "genv", "reserved")]
+    _fields_ = [(n, C.c_void_p) for n in ("qq", "kl", "kwT", "vlT", "vwT", "hT", "wq", "gc", "u", "fw", "amat", "genv", "gcl")]
 
 
 class LinQuantError(RuntimeError):
@@ -102,7 +102,8 @@ _WS_LAYOUT = {  # name -> (torch dtype, lambda(BH,NT,C,K,V) -> shape)
     "gc": (torch.float32, lambda BH, NT, Cc, K, V: (BH, NT, Cc)),
     "u": (None, lambda BH, NT, Cc, K, V: (BH, NT, Cc, V)),  # activation dtype
     "fw": (torch.float32, lambda BH, NT, Cc, K, V: (BH, NT, Cc)),
-    "amat": (torch.float32, lambda BH, NT, Cc, K, V: (BH, NT, Cc, Cc)),
+    "amat": (torch.float16, lambda BH, NT, Cc, K, V: (BH, NT, Cc, Cc)),
+    "gcl": (torch.float32, lambda BH, NT, Cc, K, V: (BH, NT, K)),
     "genv": (torch.float32, lambda BH, NT, Cc, K, V: (BH, NT, Cc)),
 }
 

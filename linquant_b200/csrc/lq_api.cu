@@ -72,9 +72,9 @@ static size_t carve(const lq_zoo_problem* p, int delta, void* ws, lq_zoo_workspa
   w.wq = delta ? cv.take<int8_t>(BH * NT * C * K) : nullptr;
   w.u = delta ? cv.take<uint16_t>(BH * NT * C * V) : nullptr;
   w.fw = delta ? cv.take<float>(BH * NT * C) : nullptr;
-  w.amat = p->decay == LQ_DECAY_DIAGONAL ? cv.take<float>(BH * NT * C * C) : nullptr;
+  w.amat = p->decay == LQ_DECAY_DIAGONAL ? cv.take<uint16_t>(BH * NT * C * C) : nullptr;
   w.genv = p->decay == LQ_DECAY_DIAGONAL ? cv.take<float>(BH * NT * C) : nullptr;
-  w.reserved = nullptr;
+  w.gcl = p->decay == LQ_DECAY_DIAGONAL ? cv.take<float>(BH * NT * K) : nullptr;
   if (out) *out = w;
   return (cv.off + 255) & ~size_t(255);
 }
@@ -84,6 +84,7 @@ int run_state_linear(const lq_zoo_problem* p, const lq_zoo_workspace* ws, cudaSt
 int run_output_scalar(const lq_zoo_problem* p, const lq_zoo_workspace* ws, const float* s_local_value, cudaStream_t st);
 int run_prologue_delta(const lq_zoo_problem* p, const lq_zoo_workspace* ws, cudaStream_t st);
 int run_state_delta(const lq_zoo_problem* p, const lq_zoo_workspace* ws, cudaStream_t st);
+int run_diag_stage(const lq_zoo_problem* p, const lq_zoo_workspace* ws, bool delta, int stage, cudaStream_t st);
 
 }  // namespace lq
 
@@ -121,6 +122,29 @@ extern "C" int lq_delta_fwd(const lq_zoo_problem* p, void* workspace, size_t wor
   if (int e = lq_zoo_carve_workspace(p, 1, workspace, workspace_bytes, &ws)) return e;
   cudaStream_t st = (cudaStream_t)stream;
   if (int e = lq::run_prologue_delta(p, &ws, st)) return e;
+  if (int e = lq::run_state_delta(p, &ws, st)) return e;
+  return lq::run_output_scalar(p, &ws, p->sel, st);
+}
+
+extern "C" int lq_gla_fwd(const lq_zoo_problem* p, void* workspace, size_t workspace_bytes, lq_stream stream) {
+  if (int e = lq::validate_zoo_problem(p, false, true)) return e;
+  lq_zoo_workspace ws;
+  if (int e = lq_zoo_carve_workspace(p, 0, workspace, workspace_bytes, &ws)) return e;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (int e = lq::run_diag_stage(p, &ws, false, 0, st)) return e;
+  if (int e = lq::run_diag_stage(p, &ws, false, 1, st)) return e;
+  if (int e = lq::run_state_linear(p, &ws, st)) return e;
+  return lq::run_output_scalar(p, &ws, p->svl, st);
+}
+
+extern "C" int lq_kda_fwd(const lq_zoo_problem* p, void* workspace, size_t workspace_bytes, lq_stream stream) {
+  if (int e = lq::validate_zoo_problem(p, true, true)) return e;
+  lq_zoo_workspace ws;
+  if (int e = lq_zoo_carve_workspace(p, 1, workspace, workspace_bytes, &ws)) return e;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (int e = lq::run_diag_stage(p, &ws, true, 0, st)) return e;
+  if (int e = lq::run_diag_stage(p, &ws, true, 1, st)) return e;
+  if (int e = lq::run_diag_stage(p, &ws, true, 2, st)) return e;
   if (int e = lq::run_state_delta(p, &ws, st)) return e;
   return lq::run_output_scalar(p, &ws, p->sel, st);
 }

@@ -16,6 +16,7 @@
 //
 // Reference arithmetic: zoo/gated_delta_rule.py:20-47 (_prep), :51-115 (_delta_state_body);
 // reference.py:202-229 (_chunk_delta).
+#include "lq_wy.cuh"
 #include "lq_zoo_rows.cuh"
 
 namespace lq {
@@ -28,48 +29,6 @@ struct DeltaPrepArgs {
   float* fw;
   float sigma, tau;
 };
-
-__device__ __forceinline__ uint32_t tf32_rna(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(r) : "f"(x));
-  return r;
-}
-__device__ __forceinline__ void mma_tf32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ float pow_exact01(float x, float e) { return e == 0.f ? 1.f : (e == 1.f ? x : powf(x, e)); }
-
-// acc[NT][4] += (T .* cw[None,:])[16 rows of m-tile mt, tokens 0..16mt+15] . B[tokens, NT*8 columns from n0]
-template <int NT>
-__device__ __forceinline__ void wy_product(float (&acc)[NT][4], const float* s_T, const float* s_cw, const float* s_B,
-                                           int LDB, int mt, int n0, int g, int j) {
-  const int ia = 16 * mt + g, ib = ia + 8;
-  for (int kk = 0; kk < 2 * mt + 2; ++kk) {
-    const int c0 = 8 * kk + j, c1 = c0 + 4;
-    const float x[4] = {s_T[ia * 68 + c0] * s_cw[c0], s_T[ib * 68 + c0] * s_cw[c0], s_T[ia * 68 + c1] * s_cw[c1],
-                        s_T[ib * 68 + c1] * s_cw[c1]};
-    uint32_t hi[4], mi[4], lo[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      hi[i] = tf32_rna(x[i]);
-      const float r1 = x[i] - __uint_as_float(hi[i]);
-      mi[i] = tf32_rna(r1);
-      lo[i] = __float_as_uint(r1 - __uint_as_float(mi[i]));
-    }
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      const uint32_t b0 = __float_as_uint(s_B[c0 * LDB + n0 + 8 * nt + g]);
-      const uint32_t b1 = __float_as_uint(s_B[c1 * LDB + n0 + 8 * nt + g]);
-      mma_tf32(acc[nt], lo[0], lo[1], lo[2], lo[3], b0, b1);
-      mma_tf32(acc[nt], mi[0], mi[1], mi[2], mi[3], b0, b1);
-      mma_tf32(acc[nt], hi[0], hi[1], hi[2], hi[3], b0, b1);
-    }
-  }
-}
 
 template <typename T, int K, int V>
 __global__ void __launch_bounds__(256) zoo_prologue_delta_kernel(DeltaPrepArgs d) {
@@ -156,26 +115,7 @@ __global__ void __launch_bounds__(256) zoo_prologue_delta_kernel(DeltaPrepArgs d
     }
   }
   __syncthreads();
-  // ---- T = (I + G)^-1: column col by four lanes (r = share of the row dot product); the column lives in registers
-  {
-    const int col = tid >> 2, r = tid & 3;
-    float tc[16];
-#pragma unroll
-    for (int m = 0; m < 16; ++m) tc[m] = 0.f;
-#pragma unroll
-    for (int i = 0; i < C; ++i) {
-      float part = 0.f;
-#pragma unroll
-      for (int m = 0; m <= (i - 1) / 4 && i > 0; ++m) {
-        if (4 * m + r < i) part = fmaf(s_G[i * 68 + 4 * m + r], tc[m], part);
-      }
-      part += __shfl_xor_sync(0xffffffffu, part, 1);
-      part += __shfl_xor_sync(0xffffffffu, part, 2);
-      const float val = (i == col ? 1.f : 0.f) - part;
-      if ((i & 3) == r) tc[i >> 2] = val;
-      if (r == 0) s_T[i * 68 + col] = val;
-    }
-  }
+  wy_solve(s_G, s_T);
   __syncthreads();
   // ---- W = T diag(beta^sigma exp(gc)) k  -> w_read codes
   {
@@ -222,6 +162,7 @@ struct DeltaStateArgs {
   const int8_t *wq, *kwT;
   const void* u;
   const float *fw, *gc, *skw, *sw, *sel, *sew, *ss;
+  const float *gcl, *genv;  // diagonal decay: [BH,NT,K] end-of-chunk log-decay, [BH,NT,C] log envelope
   int8_t *hT, *elT;
   float* final_state;
   int H, NT, use_g;
@@ -234,7 +175,7 @@ __device__ __forceinline__ int swz_row(int row, int chunk) {
   return row * 64 + (chunk << 4);
 }
 
-template <typename T, int K, int V>
+template <typename T, int K, int V, bool DIAG>
 __global__ void __launch_bounds__(128) zoo_state_delta_kernel(DeltaStateArgs a) {
   constexpr int C = 64, BV = 32;
   constexpr int NTK = K / 32;  // key n-tiles per warp in the carry layout
@@ -303,9 +244,15 @@ __global__ void __launch_bounds__(128) zoo_state_delta_kernel(DeltaStateArgs a) 
     for (int nt = 0; nt < NTK; ++nt) kb_[nt] = __ldg(reinterpret_cast<const uint4*>(kwc + krow[nt] * C + 16 * j));
     fwa_ = __ldg(a.fw + tile * C + ta);
     fwb_ = __ldg(a.fw + tile * C + tb);
-    gca_ = a.use_g ? __ldg(a.gc + tile * C + ta) : 0.f;
-    gcb_ = a.use_g ? __ldg(a.gc + tile * C + tb) : 0.f;
-    gl_ = a.use_g ? __ldg(a.gc + tile * C + C - 1) : 0.f;
+    if (DIAG) {  // gca/gcb carry the log envelope of the two token rows; the carry decay is per key channel
+      gca_ = __ldg(a.genv + tile * C + ta);
+      gcb_ = __ldg(a.genv + tile * C + tb);
+      gl_ = 0.f;
+    } else {
+      gca_ = a.use_g ? __ldg(a.gc + tile * C + ta) : 0.f;
+      gcb_ = a.use_g ? __ldg(a.gc + tile * C + tb) : 0.f;
+      gl_ = a.use_g ? __ldg(a.gc + tile * C + C - 1) : 0.f;
+    }
   };
   fetch(0, wa, wb, ua, ub, kb, fwa, fwb, gca, gcb, glast);
 
@@ -365,8 +312,8 @@ __global__ void __launch_bounds__(128) zoo_state_delta_kernel(DeltaStateArgs a) 
       float Ua[8], Ub[8];
       Act<T>::unpack8(ua, Ua);
       Act<T>::unpack8(ub, Ub);
-      const float fva = a.use_g ? expf(a.eta * (glast - gca)) : 1.f;
-      const float fvb = a.use_g ? expf(a.eta * (glast - gcb)) : 1.f;
+      const float fva = DIAG ? expf(a.eta * gca) : (a.use_g ? expf(a.eta * (glast - gca)) : 1.f);
+      const float fvb = DIAG ? expf(a.eta * gcb) : (a.use_g ? expf(a.eta * (glast - gcb)) : 1.f);
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
@@ -389,7 +336,15 @@ __global__ void __launch_bounds__(128) zoo_state_delta_kernel(DeltaStateArgs a) 
     // ---- 3. write product and carry update; e_local tile out
     {
       reinterpret_cast<uint4*>(a.elT + tile * (size_t)(V * C) + (size_t)v0 * C)[tid] = reinterpret_cast<const uint4*>(s_el)[tid];
-      const float gam = a.use_g ? expf(glast) : 1.0f;
+      float gamv[2 * NTK];
+      if (DIAG) {
+#pragma unroll
+        for (int i = 0; i < 2 * NTK; ++i) gamv[i] = expf(__ldg(a.gcl + tile * K + kown + i));
+      } else {
+        const float gs = a.use_g ? expf(glast) : 1.0f;
+#pragma unroll
+        for (int i = 0; i < 2 * NTK; ++i) gamv[i] = gs;
+      }
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
         const uint4 ea = *reinterpret_cast<const uint4*>(s_ew + (16 * mt + g) * C + 16 * j);
@@ -403,8 +358,8 @@ __global__ void __launch_bounds__(128) zoo_state_delta_kernel(DeltaStateArgs a) 
           for (int e = 0; e < 2; ++e) {
             const float ta_ = __fmul_rn(__fmul_rn((float)acc[e], skw[2 * nt + e]), sew_r[2 * mt]);
             const float tb_ = __fmul_rn(__fmul_rn((float)acc[2 + e], skw[2 * nt + e]), sew_r[2 * mt + 1]);
-            carry[mt][nt][e] = fmaf(carry[mt][nt][e], gam, ta_);
-            carry[mt][nt][2 + e] = fmaf(carry[mt][nt][2 + e], gam, tb_);
+            carry[mt][nt][e] = fmaf(carry[mt][nt][e], gamv[2 * nt + e], ta_);
+            carry[mt][nt][2 + e] = fmaf(carry[mt][nt][2 + e], gamv[2 * nt + e], tb_);
           }
         }
       }
@@ -465,11 +420,16 @@ int run_prologue_delta(const lq_zoo_problem* p, const lq_zoo_workspace* ws, cuda
 template <typename T>
 static int dispatch_delta_state(const lq_zoo_problem* p, const DeltaStateArgs& a, cudaStream_t st) {
   dim3 grid(p->V / 32, p->B * p->H), block(128);
-  if (p->K == 64 && p->V == 64) zoo_state_delta_kernel<T, 64, 64><<<grid, block, 0, st>>>(a);
-  else if (p->K == 64 && p->V == 128) zoo_state_delta_kernel<T, 64, 128><<<grid, block, 0, st>>>(a);
-  else if (p->K == 128 && p->V == 64) zoo_state_delta_kernel<T, 128, 64><<<grid, block, 0, st>>>(a);
-  else if (p->K == 128 && p->V == 128) zoo_state_delta_kernel<T, 128, 128><<<grid, block, 0, st>>>(a);
+  const bool diag = p->decay == LQ_DECAY_DIAGONAL;
+#define LQ_LAUNCH_DSTATE(KK_, VV_)                                                         \
+  if (diag) zoo_state_delta_kernel<T, KK_, VV_, true><<<grid, block, 0, st>>>(a);          \
+  else zoo_state_delta_kernel<T, KK_, VV_, false><<<grid, block, 0, st>>>(a)
+  if (p->K == 64 && p->V == 64) { LQ_LAUNCH_DSTATE(64, 64); }
+  else if (p->K == 64 && p->V == 128) { LQ_LAUNCH_DSTATE(64, 128); }
+  else if (p->K == 128 && p->V == 64) { LQ_LAUNCH_DSTATE(128, 64); }
+  else if (p->K == 128 && p->V == 128) { LQ_LAUNCH_DSTATE(128, 128); }
   else return fail(LQ_ERR_UNSUPPORTED, "delta state: K and V must be 64 or 128");
+#undef LQ_LAUNCH_DSTATE
   return check_launch("zoo_state_delta_kernel");
 }
 
@@ -477,7 +437,7 @@ int run_state_delta(const lq_zoo_problem* p, const lq_zoo_workspace* ws, cudaStr
   DeltaStateArgs a;
   a.wq = ws->wq; a.kwT = ws->kwT; a.u = ws->u; a.fw = ws->fw; a.gc = ws->gc;
   a.skw = p->skw; a.sw = p->sw; a.sel = p->sel; a.sew = p->sew; a.ss = p->sstate;
-  a.hT = ws->hT; a.elT = ws->vlT; a.final_state = p->final_state;
+  a.hT = ws->hT; a.elT = ws->vlT; a.final_state = p->final_state; a.gcl = ws->gcl; a.genv = ws->genv;
   a.H = p->H; a.NT = p->T / p->chunk; a.use_g = p->g != nullptr; a.eta = p->eta; a.qmax = p->qmax;
   if (p->act_dtype == LQ_F16) return dispatch_delta_state<__half>(p, a, st);
   if (p->act_dtype == LQ_BF16) return dispatch_delta_state<__nv_bfloat16>(p, a, st);
@@ -493,7 +453,7 @@ extern "C" int lq_zoo_prologue_delta(const lq_zoo_problem* p, const lq_zoo_works
 }
 
 extern "C" int lq_zoo_state_delta(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq_stream stream) {
-  if (int e = lq::validate_zoo_problem(p, true, false)) return e;
+  if (int e = lq::validate_zoo_problem(p, true, p && p->decay == LQ_DECAY_DIAGONAL)) return e;
   if (!ws) return lq::fail(LQ_ERR_NULL, "delta state: workspace descriptor is null");
   return lq::run_state_delta(p, ws, (cudaStream_t)stream);
 }

@@ -1,0 +1,504 @@
+// Diagonal (per-channel) decay cells: GLA (linear family) and KDA (delta family).
+//
+// Three chunk-parallel kernels, one CTA per (batch*head, chunk):
+//   rows   chunk-local cumulative log-decay per channel (double accumulate), log envelope, pre-decayed q_read codes,
+//          gated k_write codes (Omega * s^-eta), and for the linear family the v_local / v_write codes
+//   amat   the intra-chunk matrix A in 16-token secondary chunks: off-diagonal blocks as INT8 MMAs on operands
+//          re-scaled around the block's anchor row (optionally rotated by a signed Hadamard on fp16-rounded values),
+//          diagonal blocks as an fp32 reduction with the exact per-channel weights on the dequantised codes
+//   kda_wy KDA only: unquantised Gram matrix with per-channel weights, (I+G)^-1, W codes, U
+// The state pass and the output kernel are the scalar-decay kernels instantiated with per-channel carry decay
+// and a precomputed A.
+//
+// Reference arithmetic: zoo/gla.py:27-63 (_gla_A_inter), :66-99 (_gla_A_intra), :103-148 (state), :171-213 (output),
+// :249-250 (cumsum, envelope); zoo/kda.py:22-53 (_prep); reference.py:125-152, :155-163.
+#include "lq_wy.cuh"
+#include "lq_zoo_rows.cuh"
+
+namespace lq {
+
+struct DiagArgs {
+  const void *q, *k, *v;
+  const float *g, *beta, *signs;
+  const float *sq, *sk, *skw, *svl, *svw, *sw;
+  int8_t *qq, *kwT, *vlT, *vwT, *wq;
+  float *gc, *genv, *gcl, *fw;
+  void* u;
+  __half* amat;
+  int T, H, NT;
+  float scale, eta, sigma, tau, qmax;
+};
+
+template <int K>
+__device__ __forceinline__ void load_gc_tile(const float* gc_tile, float* s_gc) {
+  for (int i = threadIdx.x; i < 64 * K / 4; i += blockDim.x) {
+    const int t = i / (K / 4), c4 = i % (K / 4);
+    const float4 v = reinterpret_cast<const float4*>(gc_tile)[i];
+    *reinterpret_cast<float4*>(s_gc + t * (K + 4) + 4 * c4) = v;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ rows
+template <typename T, int K, int V, bool DELTA>
+__global__ void __launch_bounds__(256) zoo_diag_rows_kernel(DiagArgs a) {
+  constexpr int C = 64, LD = K + 4;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  float* s_gc = reinterpret_cast<float*>(smem_raw);
+  float* s_le = s_gc + C * LD;
+  float* s_hw = s_le + C;
+  uint32_t(*s_kw)[17] = reinterpret_cast<uint32_t(*)[17]>(s_hw + C);
+  uint32_t(*s_vl)[17] = s_kw + K;
+  uint32_t(*s_vw)[17] = s_vl + V;
+
+  const int c = blockIdx.x, bh = blockIdx.y;
+  const int b = bh / a.H, h = bh % a.H;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const size_t tile = (size_t)bh * a.NT + c;
+  const float e_hw = (1.f - a.sigma) * a.tau;
+
+  if (tid < K) {
+    double acc = 0.0;
+    float f = 0.f;
+    for (int t = 0; t < C; ++t) {
+      acc += (double)a.g[(((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K + tid];
+      f = (float)acc;
+      s_gc[t * LD + tid] = f;
+      a.gc[(tile * C + t) * K + tid] = f;
+    }
+    a.gcl[tile * K + tid] = f;
+  } else if (DELTA && tid >= 128 && tid < 128 + C) {
+    const int t = tid - 128;
+    const float bt = a.beta[((size_t)b * a.T + (size_t)c * C + t) * a.H + h];
+    s_hw[t] = pow_exact01(bt, e_hw);
+  }
+  __syncthreads();
+  for (int tt = 0; tt < 8; ++tt) {
+    const int t = 8 * warp + tt;
+    float m = -INFINITY;
+    for (int n = lane; n < K; n += 32) m = fmaxf(m, s_gc[(C - 1) * LD + n] - s_gc[t * LD + n]);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+    if (lane == 0) {
+      s_le[t] = m;
+      a.genv[tile * C + t] = m;
+    }
+  }
+  __syncthreads();
+
+  {
+    constexpr int LPR = K / 8, G = 32 / LPR;
+    const int r = lane % LPR, grp = lane / LPR;
+    const float inv_sq = 1.0f / a.sq[h];
+    float inv_kw[8], gl[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      inv_kw[j] = 1.0f / a.skw[h * K + 8 * r + j];
+      gl[j] = s_gc[(C - 1) * LD + 8 * r + j];
+    }
+    const T* qp = reinterpret_cast<const T*>(a.q);
+    const T* kp = reinterpret_cast<const T*>(a.k);
+    for (int tg = warp * G + grp; tg < C / 4; tg += 8 * G) {
+      uint32_t kwp[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) kwp[j] = 0u;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int t = 4 * tg + i;
+        const size_t row = (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K + 8 * r;
+        float x[8], gv[8];
+        int cd[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) gv[j] = s_gc[t * LD + 8 * r + j];
+        Act<T>::unpack8(*reinterpret_cast<const uint4*>(qp + row), x);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) cd[j] = q8(__fmul_rn(__fmul_rn(x[j], expf(gv[j])), a.scale), inv_sq, a.qmax);
+        *reinterpret_cast<uint2*>(a.qq + (tile * C + t) * K + 8 * r) =
+            make_uint2(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4], cd[5], cd[6], cd[7]));
+        Act<T>::unpack8(*reinterpret_cast<const uint4*>(kp + row), x);
+        if (DELTA && e_hw != 0.f) {
+          const float hw = s_hw[t];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) x[j] = Act<T>::round(__fmul_rn(x[j], hw));
+        }
+        const float ele = a.eta * s_le[t];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float w = expf(__fsub_rn(__fsub_rn(gl[j], gv[j]), ele));
+          kwp[j] |= ((uint32_t)q8(__fmul_rn(x[j], w), inv_kw[j], a.qmax) & 0xffu) << (8 * i);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s_kw[8 * r + j][tg] = kwp[j];
+    }
+  }
+  if (!DELTA) {
+    constexpr int LPR = V / 8, G = 32 / LPR;
+    const int r = lane % LPR, grp = lane / LPR;
+    float inv_vl[8], inv_vw[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      inv_vl[j] = 1.0f / a.svl[h * V + 8 * r + j];
+      inv_vw[j] = 1.0f / a.svw[h * V + 8 * r + j];
+    }
+    const T* vp = reinterpret_cast<const T*>(a.v);
+    for (int tg = warp * G + grp; tg < C / 4; tg += 8 * G) {
+      uint32_t vlp[8], vwp[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) vlp[j] = vwp[j] = 0u;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int t = 4 * tg + i;
+        float x[8];
+        Act<T>::unpack8(*reinterpret_cast<const uint4*>(vp + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * V + 8 * r), x);
+        const float fv = expf(a.eta * s_le[t]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          vlp[j] |= ((uint32_t)q8(x[j], inv_vl[j], a.qmax) & 0xffu) << (8 * i);
+          vwp[j] |= ((uint32_t)q8(__fmul_rn(x[j], fv), inv_vw[j], a.qmax) & 0xffu) << (8 * i);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        s_vl[8 * r + j][tg] = vlp[j];
+        s_vw[8 * r + j][tg] = vwp[j];
+      }
+    }
+  }
+  __syncthreads();
+  uint32_t* kw_out = reinterpret_cast<uint32_t*>(a.kwT + tile * (size_t)(K * C));
+  for (int i = tid; i < K * 16; i += 256) kw_out[i] = s_kw[i >> 4][i & 15];
+  if (!DELTA) {
+    uint32_t* vl_out = reinterpret_cast<uint32_t*>(a.vlT + tile * (size_t)(V * C));
+    uint32_t* vw_out = reinterpret_cast<uint32_t*>(a.vwT + tile * (size_t)(V * C));
+    for (int i = tid; i < V * 16; i += 256) {
+      vl_out[i] = s_vl[i >> 4][i & 15];
+      vw_out[i] = s_vw[i >> 4][i & 15];
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ A matrix
+template <typename T, int K>
+__global__ void __launch_bounds__(256) zoo_diag_amat_kernel(DiagArgs a) {
+  constexpr int C = 64, LD = K + 4, SUB = 16;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  float* s_gc = reinterpret_cast<float*>(smem_raw);
+  float* s_A = s_gc + C * LD;
+  float* s_hw = s_A + C * 65;
+  int8_t* s_qc = reinterpret_cast<int8_t*>(s_hw + C);
+  int8_t* s_kc = s_qc + C * K;
+  int8_t* s_qa = s_kc + C * K;
+  int8_t* s_ka = s_qa + SUB * K;
+
+  const int c = blockIdx.x, bh = blockIdx.y;
+  const int b = bh / a.H, h = bh % a.H;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, j4 = lane & 3;
+  const size_t tile = (size_t)bh * a.NT + c;
+  const float e_hw = (1.f - a.sigma) * a.tau;
+  const bool use_hw = a.beta != nullptr && e_hw != 0.f;
+  const bool rot = a.signs != nullptr;
+
+  load_gc_tile<K>(a.gc + tile * (size_t)(C * K), s_gc);
+  for (int i = tid; i < C * 65; i += 256) s_A[i] = 0.f;
+  if (tid < C) {
+    s_hw[tid] = use_hw ? pow_exact01(a.beta[((size_t)b * a.T + (size_t)c * C + tid) * a.H + h], e_hw) : 1.f;
+  }
+  __syncthreads();
+
+  constexpr int LPR = K / 8, G = 32 / LPR;
+  const int r = lane % LPR, grp = lane / LPR;
+  const float inv_sq = 1.0f / a.sq[h], inv_sk = 1.0f / a.sk[h];
+  const float sqk = __fmul_rn(a.sq[h], a.sk[h]);
+  const T* qp = reinterpret_cast<const T*>(a.q);
+  const T* kp = reinterpret_cast<const T*>(a.k);
+  auto grow = [&](int t) { return (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K + 8 * r; };
+
+  // codes of the bare operands (diagonal blocks)
+  for (int t = warp * G + grp; t < C; t += 8 * G) {
+    float x[8];
+    int cd[8];
+    Act<T>::unpack8(*reinterpret_cast<const uint4*>(qp + grow(t)), x);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cd[j] = q8(__fmul_rn(x[j], a.scale), inv_sq, a.qmax);
+    *reinterpret_cast<uint2*>(s_qc + t * K + 8 * r) = make_uint2(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4], cd[5], cd[6], cd[7]));
+    Act<T>::unpack8(*reinterpret_cast<const uint4*>(kp + grow(t)), x);
+    if (use_hw) {
+      const float hw = s_hw[t];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = Act<T>::round(__fmul_rn(x[j], hw));
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cd[j] = q8(x[j], inv_sk, a.qmax);
+    *reinterpret_cast<uint2*>(s_kc + t * K + 8 * r) = make_uint2(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4], cd[5], cd[6], cd[7]));
+  }
+
+  // off-diagonal blocks: rows [16I, 16I+16) against columns [0, 16I), operands re-scaled around the anchor row 16I
+  float sgn[8];
+  {
+    const float n16 = __half2float(__float2half_rn(K == 64 ? 0.125f : 0.08838834764831845f));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sgn[j] = rot ? a.signs[8 * r + j] * n16 : 1.f;
+  }
+  for (int I = 1; I < C / SUB; ++I) {
+    float anc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) anc[j] = s_gc[(SUB * I) * LD + 8 * r + j];
+    const int R = SUB + SUB * I;
+    for (int rr = warp * G + grp; rr < R; rr += 8 * G) {
+      const bool isq = rr < SUB;
+      const int t = isq ? SUB * I + rr : rr - SUB;
+      float x[8];
+      int cd[8];
+      Act<T>::unpack8(*reinterpret_cast<const uint4*>((isq ? qp : kp) + grow(t)), x);
+      if (isq) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(__fmul_rn(x[j], expf(__fsub_rn(s_gc[t * LD + 8 * r + j], anc[j]))), a.scale);
+      } else {
+        if (use_hw) {
+          const float hw = s_hw[t];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) x[j] = Act<T>::round(__fmul_rn(x[j], hw));
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(x[j], expf(__fsub_rn(anc[j], s_gc[t * LD + 8 * r + j])));
+      }
+      if (rot) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = __half2float(__float2half_rn(x[j]));
+        fwht8<LPR>(x, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(x[j], sgn[j]);
+      }
+      const float inv = isq ? inv_sq : inv_sk;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) cd[j] = q8(x[j], inv, a.qmax);
+      int8_t* dst = isq ? (s_qa + rr * K) : (s_ka + (rr - SUB) * K);
+      *reinterpret_cast<uint2*>(dst + 8 * r) = make_uint2(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4], cd[5], cd[6], cd[7]));
+    }
+    __syncthreads();
+    if (warp < 2 * I) {
+      int acc[4] = {0, 0, 0, 0};
+#pragma unroll
+      for (int kk = 0; kk < K / 64; ++kk) {
+        const uint4 qa = *reinterpret_cast<const uint4*>(s_qa + g * K + 64 * kk + 16 * j4);
+        const uint4 qb = *reinterpret_cast<const uint4*>(s_qa + (g + 8) * K + 64 * kk + 16 * j4);
+        const uint4 kb = *reinterpret_cast<const uint4*>(s_ka + (8 * warp + g) * K + 64 * kk + 16 * j4);
+        mma_s8(acc, qa.x, qb.x, qa.y, qb.y, kb.x, kb.y);
+        mma_s8(acc, qa.z, qb.z, qa.w, qb.w, kb.z, kb.w);
+      }
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        s_A[(SUB * I + g) * 65 + 8 * warp + 2 * j4 + e] = __fmul_rn((float)acc[e], sqk);
+        s_A[(SUB * I + g + 8) * 65 + 8 * warp + 2 * j4 + e] = __fmul_rn((float)acc[2 + e], sqk);
+      }
+    }
+    __syncthreads();
+  }
+
+  // diagonal blocks: 4 x 136 (i >= j) pairs, eight lanes per pair
+  for (int pass = 0; pass < 17; ++pass) {
+    const int p = pass * 32 + (tid >> 3);
+    const int I = p / 136, rem = p % 136;
+    int i = (int)((sqrtf(8.f * rem + 1.f) - 1.f) * 0.5f);
+    while ((i + 1) * (i + 2) / 2 <= rem) ++i;
+    while (i * (i + 1) / 2 > rem) --i;
+    const int jj = rem - i * (i + 1) / 2;
+    const int ti = SUB * I + i, tj = SUB * I + jj;
+    const int l8 = tid & 7;
+    float sum = 0.f;
+    for (int n = l8; n < K; n += 8) {
+      const float w = __expf(s_gc[ti * LD + n] - s_gc[tj * LD + n]);
+      sum = fmaf((float)((int)s_qc[ti * K + n] * (int)s_kc[tj * K + n]), w, sum);
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    if (l8 == 0) s_A[ti * 65 + tj] = __fmul_rn(sum, sqk);
+  }
+  __syncthreads();
+  uint32_t* out = reinterpret_cast<uint32_t*>(a.amat + tile * (size_t)(C * C));
+  for (int i = tid; i < C * 32; i += 256) {
+    const int row = i >> 5, cp = i & 31;
+    out[i] = Act<__half>::pack2(s_A[row * 65 + 2 * cp], s_A[row * 65 + 2 * cp + 1]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ KDA WY prep
+template <typename T, int K, int V>
+__global__ void __launch_bounds__(256) zoo_kda_wy_kernel(DiagArgs a) {
+  constexpr int C = 64, LD = K + 4, LDV = V + 8;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  float* s_gc = reinterpret_cast<float*>(smem_raw);  // later: gc * log2(e)
+  float* s_kf = s_gc + C * LD;
+  float* s_vf = s_kf + C * LD;
+  float* s_G = s_vf + C * LDV;
+  float* s_T = s_G + C * 68;
+  float* s_bs = s_T + C * 68;
+  float* s_b1 = s_bs + C;
+
+  const int c = blockIdx.x, bh = blockIdx.y;
+  const int b = bh / a.H, h = bh % a.H;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, j4 = lane & 3;
+  const size_t tile = (size_t)bh * a.NT + c;
+
+  load_gc_tile<K>(a.gc + tile * (size_t)(C * K), s_gc);
+  {
+    const T* kp = reinterpret_cast<const T*>(a.k);
+    const T* vp = reinterpret_cast<const T*>(a.v);
+    for (int i = tid; i < C * (K / 8); i += 256) {
+      const int t = i / (K / 8), seg = i % (K / 8);
+      float x[8];
+      Act<T>::unpack8(*reinterpret_cast<const uint4*>(kp + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K + 8 * seg), x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s_kf[t * LD + 8 * seg + e] = x[e];
+    }
+    for (int i = tid; i < C * (V / 8); i += 256) {
+      const int t = i / (V / 8), seg = i % (V / 8);
+      float x[8];
+      Act<T>::unpack8(*reinterpret_cast<const uint4*>(vp + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * V + 8 * seg), x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s_vf[t * LDV + 8 * seg + e] = x[e];
+    }
+  }
+  if (tid < C) {
+    const float bt = a.beta[((size_t)b * a.T + (size_t)c * C + tid) * a.H + h];
+    s_bs[tid] = pow_exact01(bt, a.sigma);
+    s_b1[tid] = pow_exact01(bt, 1.f - a.sigma);
+    a.fw[tile * C + tid] = pow_exact01(bt, (1.f - a.sigma) * (1.f - a.tau));
+  }
+  for (int i = tid; i < C * 68; i += 256) s_G[i] = 0.f;
+  __syncthreads();
+
+  // Gram matrix with exact per-channel weights, strictly lower triangle: 2016 pairs, eight lanes per pair
+  for (int pass = 0; pass < 63; ++pass) {
+    const int p = pass * 32 + (tid >> 3);
+    int i = (int)((sqrtf(8.f * p + 1.f) + 1.f) * 0.5f);
+    while (i * (i + 1) / 2 <= p) ++i;
+    while (i * (i - 1) / 2 > p) --i;
+    const int jj = p - i * (i - 1) / 2;
+    const int l8 = tid & 7;
+    float sum = 0.f;
+    for (int n = l8; n < K; n += 8) {
+      const float w = expf(s_gc[i * LD + n] - s_gc[jj * LD + n]);
+      sum = fmaf(s_kf[i * LD + n] * s_kf[jj * LD + n], w, sum);
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    if (l8 == 0) s_G[i * 68 + jj] = s_bs[i] * s_b1[jj] * sum;
+  }
+  __syncthreads();
+  wy_solve(s_G, s_T);
+  // decayed keys k * exp(gc) in place (the Gram pass is done with the bare keys)
+  for (int i = tid; i < C * K; i += 256) {
+    const int t = i / K, n = i % K;
+    s_kf[t * LD + n] = s_kf[t * LD + n] * expf(s_gc[t * LD + n]);
+  }
+  __syncthreads();
+  // W = T diag(beta^sigma) (k * exp(gc)): fp32 FMA, one channel per thread, rows interleaved over the groups
+  {
+    constexpr int GR = 256 / K;
+    const int n = tid % K, rg = tid / K;
+    const float inv_sw = 1.0f / a.sw[h];
+    for (int i = rg; i < C; i += GR) {
+      float acc = 0.f;
+      for (int jj = 0; jj <= i; ++jj) acc = fmaf(s_T[i * 68 + jj] * s_bs[jj], s_kf[jj * LD + n], acc);
+      a.wq[(tile * C + i) * K + n] = (int8_t)q8(Act<T>::round(acc), inv_sw, a.qmax);
+    }
+  }
+  // U = T diag(beta^sigma) v on the tensor cores (v is exact in TF32)
+  {
+    constexpr int NTU = V / 16;
+    const int mt = warp & 3, nh = warp >> 2;
+    float acc[NTU][4];
+#pragma unroll
+    for (int nt = 0; nt < NTU; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    const int n0 = nh * (V / 2);
+    wy_product<NTU>(acc, s_T, s_bs, s_vf, LDV, mt, n0, g, j4);
+    const int ia = 16 * mt + g, ib = ia + 8;
+    T* up = reinterpret_cast<T*>(a.u);
+#pragma unroll
+    for (int nt = 0; nt < NTU; ++nt) {
+      const int col = n0 + 8 * nt + 2 * j4;
+      *reinterpret_cast<uint32_t*>(up + (tile * C + ia) * V + col) = Act<T>::pack2(acc[nt][0], acc[nt][1]);
+      *reinterpret_cast<uint32_t*>(up + (tile * C + ib) * V + col) = Act<T>::pack2(acc[nt][2], acc[nt][3]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ launchers
+int validate_zoo_problem(const lq_zoo_problem* p, bool delta, bool diagonal);
+
+static void fill_diag_args(const lq_zoo_problem* p, const lq_zoo_workspace* ws, DiagArgs& a) {
+  a.q = p->q; a.k = p->k; a.v = p->v; a.g = p->g; a.beta = p->beta; a.signs = p->rot_signs;
+  a.sq = p->sq; a.sk = p->sk; a.skw = p->skw; a.svl = p->svl; a.svw = p->svw; a.sw = p->sw;
+  a.qq = ws->qq; a.kwT = ws->kwT; a.vlT = ws->vlT; a.vwT = ws->vwT; a.wq = ws->wq;
+  a.gc = ws->gc; a.genv = ws->genv; a.gcl = ws->gcl; a.fw = ws->fw; a.u = ws->u;
+  a.amat = reinterpret_cast<__half*>(ws->amat);
+  a.T = p->T; a.H = p->H; a.NT = p->T / p->chunk;
+  a.scale = p->scale; a.eta = p->eta; a.sigma = p->sigma; a.tau = p->tau; a.qmax = p->qmax;
+}
+
+template <typename KernelT>
+static int launch_big_smem(KernelT kern, const char* name, dim3 grid, size_t smem, const DiagArgs& a, cudaStream_t st) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return fail(LQ_ERR_LAUNCH, "%s: cannot opt in to %zu bytes of shared memory: %s", name, smem, cudaGetErrorString(e));
+  kern<<<grid, 256, smem, st>>>(a);
+  return check_launch(name);
+}
+
+template <typename T, int K, int V>
+static int run_diag_T(const lq_zoo_problem* p, const DiagArgs& a, bool delta, int stage, cudaStream_t st) {
+  dim3 grid(a.NT, p->B * p->H);
+  if (stage == 0) {
+    const size_t smem = sizeof(float) * (64 * (K + 4) + 128) + sizeof(uint32_t) * 17 * (K + 2 * V);
+    if (delta) return launch_big_smem(zoo_diag_rows_kernel<T, K, V, true>, "zoo_diag_rows_kernel", grid, smem, a, st);
+    return launch_big_smem(zoo_diag_rows_kernel<T, K, V, false>, "zoo_diag_rows_kernel", grid, smem, a, st);
+  }
+  if (stage == 1) {
+    const size_t smem = sizeof(float) * (64 * (K + 4) + 64 * 65 + 64) + (size_t)(64 * K * 2 + 16 * K + 48 * K);
+    return launch_big_smem(zoo_diag_amat_kernel<T, K>, "zoo_diag_amat_kernel", grid, smem, a, st);
+  }
+  const size_t smem = sizeof(float) * (2 * 64 * (K + 4) + 64 * (V + 8) + 2 * 64 * 68 + 128);
+  return launch_big_smem(zoo_kda_wy_kernel<T, K, V>, "zoo_kda_wy_kernel", grid, smem, a, st);
+}
+
+template <typename T>
+static int run_diag_KV(const lq_zoo_problem* p, const DiagArgs& a, bool delta, int stage, cudaStream_t st) {
+  if (p->K == 64 && p->V == 64) return run_diag_T<T, 64, 64>(p, a, delta, stage, st);
+  if (p->K == 64 && p->V == 128) return run_diag_T<T, 64, 128>(p, a, delta, stage, st);
+  if (p->K == 128 && p->V == 64) return run_diag_T<T, 128, 64>(p, a, delta, stage, st);
+  if (p->K == 128 && p->V == 128) return run_diag_T<T, 128, 128>(p, a, delta, stage, st);
+  return fail(LQ_ERR_UNSUPPORTED, "diagonal decay: K and V must be 64 or 128");
+}
+
+// stage 0 = rows, 1 = A matrix, 2 = KDA WY prep
+int run_diag_stage(const lq_zoo_problem* p, const lq_zoo_workspace* ws, bool delta, int stage, cudaStream_t st) {
+  DiagArgs a;
+  fill_diag_args(p, ws, a);
+  if (p->act_dtype == LQ_F16) return run_diag_KV<__half>(p, a, delta, stage, st);
+  if (p->act_dtype == LQ_BF16) return run_diag_KV<__nv_bfloat16>(p, a, delta, stage, st);
+  return fail(LQ_ERR_UNSUPPORTED, "diagonal decay: activation dtype must be f16 or bf16");
+}
+
+}  // namespace lq
+
+extern "C" int lq_zoo_diag_rows(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq_stream stream) {
+  const bool delta = p && p->beta != nullptr;
+  if (int e = lq::validate_zoo_problem(p, delta, true)) return e;
+  if (!ws) return lq::fail(LQ_ERR_NULL, "diag rows: workspace descriptor is null");
+  return lq::run_diag_stage(p, ws, delta, 0, (cudaStream_t)stream);
+}
+extern "C" int lq_zoo_diag_amat(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq_stream stream) {
+  const bool delta = p && p->beta != nullptr;
+  if (int e = lq::validate_zoo_problem(p, delta, true)) return e;
+  if (!ws) return lq::fail(LQ_ERR_NULL, "diag amat: workspace descriptor is null");
+  return lq::run_diag_stage(p, ws, delta, 1, (cudaStream_t)stream);
+}
+extern "C" int lq_zoo_kda_wy(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq_stream stream) {
+  if (int e = lq::validate_zoo_problem(p, true, true)) return e;
+  if (!ws) return lq::fail(LQ_ERR_NULL, "kda wy: workspace descriptor is null");
+  return lq::run_diag_stage(p, ws, true, 2, (cudaStream_t)stream);
+}

@@ -19,6 +19,7 @@ namespace lq {
 struct OutputArgs {
   const int8_t *qq, *kl, *vlT, *hT;
   const float *gc, *sq, *sk, *svl, *ss;
+  const __half* amat;  // diagonal decay: [BH,NT,C,C] intra-chunk matrix A, already masked and in fp16
   void* o;
   int T, H, NT;
 };
@@ -49,7 +50,7 @@ __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* dst, const 
                  Act<__nv_bfloat16>::pack2(x[4], x[5]), Act<__nv_bfloat16>::pack2(x[6], x[7]));
 }
 
-template <int K, int V, typename OT>
+template <int K, int V, typename OT, bool DIAG>
 __global__ void __launch_bounds__(128) zoo_output_scalar_kernel(OutputArgs a) {
   constexpr int C = 64;
   constexpr int KK = K / 64;  // 64-byte reduction blocks per row
@@ -78,7 +79,7 @@ __global__ void __launch_bounds__(128) zoo_output_scalar_kernel(OutputArgs a) {
     for (int i = tid; i < C * CPR; i += 128) {
       const int row = i / CPR, ch = i % CPR;
       cp_async16(s_q + swz_k<K>(row, ch), gq + (size_t)i * 16);
-      cp_async16(s_k + swz_k<K>(row, ch), gk + (size_t)i * 16);
+      if (!DIAG) cp_async16(s_k + swz_k<K>(row, ch), gk + (size_t)i * 16);
     }
     for (int i = tid; i < V * CPR; i += 128) {
       const int row = i / CPR, ch = i % CPR;
@@ -89,7 +90,7 @@ __global__ void __launch_bounds__(128) zoo_output_scalar_kernel(OutputArgs a) {
       cp_async16(s_v + swz_v(row, ch), gv + (size_t)i * 16);
     }
     cp_async_commit();
-    if (tid < C) s_gc[tid] = a.gc[tile * C + tid];
+    if (tid < C) s_gc[tid] = DIAG ? 0.f : a.gc[tile * C + tid];
     for (int i = tid; i < V; i += 128) {
       s_ss[i] = a.ss[h * V + i];
       s_svl[i] = a.svl[h * V + i];
@@ -114,7 +115,17 @@ __global__ void __launch_bounds__(128) zoo_output_scalar_kernel(OutputArgs a) {
   uint32_t P[4][4];
 #pragma unroll
   for (int ks = 0; ks < 4; ++ks) {
-    if (ks <= warp) {
+    if (DIAG) {
+      // A operand straight from the precomputed matrix: slots (2j,2j+1 | 8+2j,8+2j+1) of k-step ks are the
+      // tokens 16ks + 4j + {0,1 | 2,3}
+      if (ks <= warp) {
+        const uint2 ra = *reinterpret_cast<const uint2*>(a.amat + (tile * C + ia) * C + 16 * ks + 4 * j);
+        const uint2 rb = *reinterpret_cast<const uint2*>(a.amat + (tile * C + ib) * C + 16 * ks + 4 * j);
+        P[ks][0] = ra.x; P[ks][1] = rb.x; P[ks][2] = ra.y; P[ks][3] = rb.y;
+      } else {
+        P[ks][0] = P[ks][1] = P[ks][2] = P[ks][3] = 0u;
+      }
+    } else if (ks <= warp) {
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         int acc[4] = {0, 0, 0, 0};
@@ -160,7 +171,7 @@ __global__ void __launch_bounds__(128) zoo_output_scalar_kernel(OutputArgs a) {
   }
 
   // ---- S1 against the stored state, combine, store
-  const float ega = __expf(gia), egb = __expf(gib);
+  const float ega = DIAG ? 1.f : __expf(gia), egb = DIAG ? 1.f : __expf(gib);
   OT* op = reinterpret_cast<OT*>(a.o);
   const size_t rowa = (((size_t)b * a.T + (size_t)c * C + ia) * a.H + h) * V;
   const size_t rowb = (((size_t)b * a.T + (size_t)c * C + ib) * a.H + h) * V;
@@ -197,10 +208,15 @@ template <int K, int V>
 static int launch_output(const lq_zoo_problem* p, const OutputArgs& a, cudaStream_t st) {
   dim3 grid(a.NT, p->B * p->H), block(128);
   const size_t smem = (size_t)64 * K * 2 + (size_t)V * K + (size_t)V * 64 + sizeof(float) * (64 + 2 * V);
-  if (p->out_dtype == LQ_F16) zoo_output_scalar_kernel<K, V, __half><<<grid, block, smem, st>>>(a);
-  else if (p->out_dtype == LQ_BF16) zoo_output_scalar_kernel<K, V, __nv_bfloat16><<<grid, block, smem, st>>>(a);
-  else if (p->out_dtype == LQ_F32) zoo_output_scalar_kernel<K, V, float><<<grid, block, smem, st>>>(a);
+  const bool diag = p->decay == LQ_DECAY_DIAGONAL;
+#define LQ_LAUNCH_OUT(OT_)                                                                 \
+  if (diag) zoo_output_scalar_kernel<K, V, OT_, true><<<grid, block, smem, st>>>(a);       \
+  else zoo_output_scalar_kernel<K, V, OT_, false><<<grid, block, smem, st>>>(a)
+  if (p->out_dtype == LQ_F16) { LQ_LAUNCH_OUT(__half); }
+  else if (p->out_dtype == LQ_BF16) { LQ_LAUNCH_OUT(__nv_bfloat16); }
+  else if (p->out_dtype == LQ_F32) { LQ_LAUNCH_OUT(float); }
   else return fail(LQ_ERR_UNSUPPORTED, "output: out dtype must be f16, bf16 or f32");
+#undef LQ_LAUNCH_OUT
   return check_launch("zoo_output_scalar_kernel");
 }
 
@@ -212,6 +228,7 @@ int run_output_scalar(const lq_zoo_problem* p, const lq_zoo_workspace* ws, const
   OutputArgs a;
   a.qq = ws->qq; a.kl = ws->kl; a.vlT = ws->vlT; a.hT = ws->hT; a.gc = ws->gc;
   a.sq = p->sq; a.sk = p->sk; a.svl = s_local_value; a.ss = p->sstate; a.o = p->o;
+  a.amat = reinterpret_cast<const __half*>(ws->amat);
   a.T = p->T; a.H = p->H; a.NT = p->T / p->chunk;
   if (p->K == 64 && p->V == 64) return launch_output<64, 64>(p, a, st);
   if (p->K == 64 && p->V == 128) return launch_output<64, 128>(p, a, st);
@@ -223,7 +240,7 @@ int run_output_scalar(const lq_zoo_problem* p, const lq_zoo_workspace* ws, const
 }  // namespace lq
 
 extern "C" int lq_zoo_output_scalar(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq_stream stream) {
-  if (int e = lq::validate_zoo_problem(p, false, false)) return e;
+  if (int e = lq::validate_zoo_problem(p, p && p->beta != nullptr, p && p->decay == LQ_DECAY_DIAGONAL)) return e;
   if (!ws) return lq::fail(LQ_ERR_NULL, "output: workspace descriptor is null");
   return lq::run_output_scalar(p, ws, p->sel ? p->sel : p->svl, (cudaStream_t)stream);
 }

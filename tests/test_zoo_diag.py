@@ -1,0 +1,108 @@
+"""chunk_gla_int8 and chunk_kda_int8 (CUDA, through the C ABI) against the CPU oracle.
+
+Mirrors tests/test_kernel_gla.py, tests/test_kernel_kda.py and the gla / kda rows of tests/test_kernel_regimes.py
+of the reference."""
+
+import pytest
+import torch
+
+from tests.helpers import OracleRun, code_mismatch, reference_check, rel_l2, zoo_inputs
+
+pytestmark = pytest.mark.gpu
+B, T, H, K, V = 2, 512, 4, 64, 128
+
+
+def run_case(q, k, v, g, beta, *, policy="kernel_static", bits=8, eta=0.0, sigma=1.0, tau=1.0, rot=False, label=""):
+    from linquant_b200.kernels.zoo.gla import chunk_gla_int8
+    from linquant_b200.kernels.zoo.kda import chunk_kda_int8
+    from oracle import zoo_oracle as zo
+
+    delta = beta is not None
+    Kd = q.shape[-1]
+    R, signs = zo.signed_hadamard(Kd, 3) if rot else (None, None)
+    orc = OracleRun(q, k, v, g, beta, family="delta" if delta else "linear", decay="diagonal", policy=policy, bits=bits,
+                    eta=eta, sigma=sigma, tau=tau, rot_qk=R)
+    ref, ref_state = orc.lineage()
+    exact = orc.exact()
+    dbg = {}
+    dev = "cuda"
+    if delta:
+        out, ht = chunk_kda_int8(q.to(dev), k.to(dev), v.to(dev), g.to(dev), beta.to(dev), orc.scales(dev), sigma=sigma,
+                                 tau=tau, eta=eta, scale=Kd**-0.5, chunk_size=64, bits=bits, output_final_state=True,
+                                 rot=signs, _debug=dbg)
+    else:
+        out, ht = chunk_gla_int8(q.to(dev), k.to(dev), v.to(dev), g.to(dev), orc.scales(dev), eta=eta, scale=Kd**-0.5,
+                                 chunk_size=64, bits=bits, output_final_state=True, rot=signs, _debug=dbg)
+    torch.cuda.synchronize()
+    ws = dbg["workspace"]
+    Bq, Tq, Hq, _ = q.shape
+    NT = Tq // 64
+    tile = lambda name: ws.view(name).view(Bq, Hq, NT, *ws.view(name).shape[2:])  # noqa: E731
+    gc_ref = g.view(Bq, NT, 64, Hq, Kd).float().cumsum(2).permute(0, 3, 1, 2, 4).contiguous()
+    assert torch.equal(tile("gc").cpu(), gc_ref), "per-channel chunk-local cumsum"
+    fr = {}
+    fr["q_read"] = code_mismatch(tile("qq"), orc.codes("q_read"), f"{label} q_read codes")
+    fr["k_write"] = code_mismatch(tile("kwT").transpose(-1, -2), orc.codes("k_write"), f"{label} k_write codes")
+    st = orc.codes("state")
+    hT = tile("hT").transpose(-1, -2)
+    assert int(hT[:, :, 0].abs().max()) == 0
+    if delta:
+        fr["w_read"] = code_mismatch(tile("wq"), orc.codes("w_read"), f"{label} W codes")
+        fr["e_local"] = code_mismatch(tile("vlT").transpose(-1, -2), orc.codes("e_local"), f"{label} E local codes")
+    else:
+        fr["v_local"] = code_mismatch(tile("vlT").transpose(-1, -2), orc.codes("v_local"), f"{label} v_local codes")
+        fr["v_write"] = code_mismatch(tile("vwT").transpose(-1, -2), orc.codes("v_write"), f"{label} v_write codes")
+    if NT > 1:
+        fr["state"] = code_mismatch(hT[:, :, 1:], st[:, :, :-1], f"{label} stored state codes")
+    err = rel_l2(out, ref)
+    print(f"{label}: tie fractions {fr} rel-L2 {err:.2e}")
+    assert err <= 2e-3, f"{label}: output rel-L2 {err:.3e} vs the quantised emulation"
+    reference_check(out, ref, exact, label)
+    assert rel_l2(ht, ref_state) <= 1e-3, f"{label}: final fp32 carry {rel_l2(ht, ref_state):.2e}"
+
+
+@pytest.mark.parametrize("eta", [0.0, 0.5, 1.0])
+def test_gla_matches_oracle(eta):
+    q, k, v, g, _ = zoo_inputs(B, T, H, K, V, decay="diagonal")
+    run_case(q, k, v, g, None, eta=eta, label=f"gla eta={eta}")
+
+
+@pytest.mark.parametrize("n", [128, 512])
+def test_gla_local_rqk(n):
+    q, k, v, g, _ = zoo_inputs(B, n, H, K, V, decay="diagonal")
+    run_case(q, k, v, g, None, eta=0.0, rot=True, label=f"gla local R_QK T={n}")
+
+
+@pytest.mark.parametrize("sigma,tau,eta", [(1.0, 1.0, 0.0), (0.0, 1.0, 0.5), (0.5, 0.5, 1.0)])
+def test_kda_matches_oracle(sigma, tau, eta):
+    q, k, v, g, beta = zoo_inputs(B, T, H, K, V, decay="diagonal", delta=True)
+    run_case(q, k, v, g, beta, sigma=sigma, tau=tau, eta=eta, label=f"kda sigma={sigma} tau={tau} eta={eta}")
+
+
+@pytest.mark.parametrize("n", [128, 512])
+def test_kda_local_rqk(n):
+    q, k, v, g, beta = zoo_inputs(B, n, H, K, V, decay="diagonal", delta=True)
+    run_case(q, k, v, g, beta, eta=0.0, rot=True, label=f"kda local R_QK T={n}")
+
+
+@pytest.mark.parametrize("policy,bits", [("kernel_pt", 8), ("kernel_pt", 6), ("kernel_ptk", 8), ("kernel_static", 6)])
+@pytest.mark.parametrize("cell", ["gla", "kda"])
+def test_regime_and_bits(cell, policy, bits):
+    q, k, v, g, beta = zoo_inputs(B, T, H, K, V, decay="diagonal", delta=cell == "kda")
+    run_case(q, k, v, g, beta, policy=policy, bits=bits, eta=0.0, label=f"{cell} {policy} bits={bits}")
+
+
+@pytest.mark.parametrize("cell", ["gla", "kda"])
+@pytest.mark.parametrize("dtype,Kd,Vd", [(torch.bfloat16, 128, 128), (torch.float16, 128, 64), (torch.bfloat16, 64, 64)])
+def test_shapes_dtypes(cell, dtype, Kd, Vd):
+    q, k, v, g, beta = zoo_inputs(2, 256, 3, Kd, Vd, decay="diagonal", delta=cell == "kda", dtype=dtype, seed=1)
+    run_case(q, k, v, g, beta, eta=0.0, rot=True, label=f"{cell} {dtype} K={Kd} V={Vd}")
+
+
+def test_kda_config_slice():
+    """KDA benchmark configuration on a slice: bf16, per-channel logsigmoid(N(4,1)) decay, 1% key outliers x20."""
+    from linquant_b200.synthetic import make_inputs
+
+    x = make_inputs("kda", seed=4, B=1, T=256)
+    q, k, v, g, beta = (x[n][:, :, :3].contiguous() for n in ("q", "k", "v", "g", "beta"))
+    run_case(q, k, v, g, beta, eta=0.0, rot=True, label="kda config slice")
