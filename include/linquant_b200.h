@@ -144,6 +144,67 @@ int lq_gla_fwd(const lq_zoo_problem* p, void* workspace, size_t workspace_bytes,
 /* Whole call of chunk_kda_int8 (zoo/kda.py:154-203). */
 int lq_kda_fwd(const lq_zoo_problem* p, void* workspace, size_t workspace_bytes, lq_stream stream);
 
+/* ------------------------------------------------------------------------------------------------------------
+ * Mamba-2 SSD op surface (SSDi8 arithmetic lineage): INT32 fixed-point carry, INT8 requantised CB, mixed roundings.
+ * x [B,L,H,P] f16/bf16 with element strides (it may be a view into xBC; P contiguous); q_B,q_C [B,L,G,N] int8;
+ * dt, dA [B,H,NC,C] fp32; states / passed [B,NC,H,P,N] int8; cb [B,NC,G,C,C] int8; out [B,L,H,P] fp16.
+ * (H,P) scale tensors are dense fp32 (callers materialise stride-0 views). L must be a multiple of chunk.
+ * ------------------------------------------------------------------------------------------------------------ */
+typedef struct {
+  int B, L, H, P, G, N, chunk;
+  int x_dtype;
+  long long x_stride_b, x_stride_t, x_stride_h; /* in elements */
+  const void* x;
+  const float* dt_in;   /* [B,L,H] raw dt (fp32) */
+  const float* A_log;   /* [H] */
+  const float* dt_bias; /* [H] or null */
+  float dt_scale, A_log_scale, dt_min, dt_max;
+  const float *dt_scale_dev, *A_log_scale_dev; /* optional one-element device tensors; they override the two floats */
+  int dt_softplus;
+  float *dt, *dA;
+  const int8_t *q_B, *q_C;
+  int8_t* q_BT;         /* scratch [B,NC,G,N,C]: q_B with the token index contiguous (value-side chunk state) */
+  const void* b_fp;     /* key side: unquantised B, same dtype as x, [B,L,G,N] */
+  const float *B_scale, *C_scale, *bscale_g, *cb_scale;     /* [G] */
+  const float *alpha_hp, *x_scale_hp, *state_scale;         /* [H,P] */
+  const float* b_gate_scale;                                /* key side, 4-D broadcastable (B,NC,H,N) */
+  long long bgs_stride[4];                                  /* its element strides (0 on broadcast dims) */
+  int8_t *states, *passed, *final_state, *cb;
+  const float* D;       /* [H] or [H,P] (already multiplied by its scale) or null */
+  int D_has_hdim;
+  void* out;
+} lq_ssd_problem;
+
+/* dt = clamp(softplus(dt_scale*dt + bias)), dA = dt * -exp(A_log_scale*A_log), chunk-local cumsum.
+ * Replaces _quant_chunk_cumsum_fwd (mamba2/chunk_cumsum.py:15-100). */
+int lq_ssd_chunk_cumsum(const lq_ssd_problem* p, lq_stream stream);
+/* Value-side chunk state (x gate-weighted and quantised with alpha_hp against INT8 B).
+ * Replaces _quant_chunk_state_fwd_xfp_static_int8 (mamba2/chunk_state.py:24-349). */
+int lq_ssd_chunk_state_value(const lq_ssd_problem* p, lq_stream stream);
+/* Key-side chunk state (INT8 x against gate-weighted B quantised in-kernel).
+ * Replaces _chunk_state_keyside_fwd (mamba2/chunk_state_keyside.py:17-424). */
+int lq_ssd_chunk_state_key(const lq_ssd_problem* p, lq_stream stream);
+/* INT32 fixed-point inter-chunk recurrence with a Q0.7 gate.
+ * Replaces _fixedpoint_state_passing_fwd (mamba2/state_passing.py:14-121). */
+int lq_ssd_state_passing(const lq_ssd_problem* p, lq_stream stream);
+/* Per-chunk INT8 C.B^T requantised to INT8 (b_is_fp: B quantised in-kernel from b_fp).
+ * Replaces _quant_bmm_chunk_fwd (mamba2/bmm_chunk.py:11-217). */
+int lq_ssd_bmm_chunk(const lq_ssd_problem* p, int b_is_fp, lq_stream stream);
+/* Output: INT8 C.S_prev with row gate + fp16 causal (CB*decay*dt).x + D*x.
+ * Replaces _quant_chunk_scan_fwd (mamba2/chunk_scan_v2.py:14-366). */
+int lq_ssd_chunk_scan(const lq_ssd_problem* p, lq_stream stream);
+
+/* Mamba-2 prologue on the B and C lanes of xBC [B,T,d_ssm+2*G*N] f16: [x D_QK, fp16 round] -> signs ->
+ * H_2 (x) H_{N/2} on bf16-rounded values -> fp16 round -> rint(. * inv_scale) clamp [-128,127].
+ * Replaces fused_split_rotate_quant_xBC (mamba2/fused_split_rotate_xBC.py:31-329). */
+int lq_ssd_split_rotate_quant(const void* xBC, int dtype, int B, int T, int d_ssm, int G, int N, const float* signs,
+                              const float* B_inv_scale, const float* C_inv_scale, const float* dqk_b,
+                              const float* dqk_c, int8_t* q_B, int8_t* q_C, lq_stream stream);
+/* Standalone Kronecker Hadamard rotation y = (x*signs) @ (H_2 (x) H_{D/2}); x [B,T,H,D] with token stride
+ * in_stride_t, y dense. Replaces kronecker_hadamard_fwd (kernels/hadamard.py:141-179). */
+int lq_kronecker_hadamard(const void* x, void* y, int dtype, int B, int T, int H, int D, long long in_stride_t,
+                          const float* signs, lq_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,700 @@
+// Mamba-2 SSD op surface, SSDi8 arithmetic lineage: chunk cumsum, INT8 chunk states (value- and key-side
+// absorption), INT32 fixed-point state passing, INT8 C.B^T, and the chunk scan.
+//
+// Reference arithmetic: linquant/kernels/mamba2/{chunk_cumsum,chunk_state,chunk_state_keyside,state_passing,
+// bmm_chunk,chunk_scan_v2}.py (line ranges at each kernel).
+#include <type_traits>
+
+#include "lq_common.cuh"
+
+namespace lq {
+
+__device__ __forceinline__ int round_half_away(float y, float lim) {
+  y = fminf(fmaxf(y, -lim), lim);
+  return __float2int_rz(__fadd_rn(y, copysignf(0.5f, y)));
+}
+__device__ __forceinline__ int round_rint(float y, float lo, float hi) {
+  return __float2int_rn(fminf(fmaxf(y, lo), hi));
+}
+
+// ------------------------------------------------------------------------------------------------ cumsum
+// mamba2/chunk_cumsum.py:52-74. One thread per head walks the chunk; the running sum is kept in double (the CPU
+// oracle's float cumsum accumulates in double).
+__global__ void ssd_cumsum_kernel(lq_ssd_problem p) {
+  const int c = blockIdx.x, b = blockIdx.y, h = threadIdx.x;
+  if (h >= p.H) return;
+  const int C = p.chunk, NC = p.L / C;
+  const float a_scale = p.A_log_scale_dev ? *p.A_log_scale_dev : p.A_log_scale;
+  const float d_scale = p.dt_scale_dev ? *p.dt_scale_dev : p.dt_scale;
+  const float A = -expf(__fmul_rn(a_scale, p.A_log[h]));
+  const float bias = p.dt_bias ? p.dt_bias[h] : 0.f;
+  double run = 0.0;
+  const size_t obase = (((size_t)b * p.H + h) * NC + c) * C;
+  for (int t = 0; t < C; ++t) {
+    float x = __fmul_rn(d_scale, p.dt_in[((size_t)b * p.L + (size_t)c * C + t) * p.H + h]);
+    if (p.dt_bias) x = __fadd_rn(x, bias);
+    if (p.dt_softplus) x = x > 20.f ? x : logf(__fadd_rn(1.0f, expf(x)));
+    x = fminf(fmaxf(x, p.dt_min), p.dt_max);
+    p.dt[obase + t] = x;
+    run += (double)__fmul_rn(x, A);
+    p.dA[obase + t] = (float)run;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ B transpose
+// q_B [B,L,G,N] -> q_BT [B,NC,G,N,C] (token index contiguous) so both operands of the value-side chunk-state
+// product have the reduction index contiguous. One CTA per (64-token block, group, batch).
+__global__ void __launch_bounds__(256) ssd_transpose_b_kernel(const int8_t* qB, int8_t* qBT, int L, int G, int N, int C) {
+  __shared__ uint32_t s[128][17];
+  const int blk = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  const int t0 = blk * 64;
+  const int c = t0 / C, tc = t0 % C;
+  const int tid = threadIdx.x;
+  // thread: token group tg (4 tokens) x 4 consecutive channels
+  for (int i = tid; i < 16 * (N / 4); i += 256) {
+    const int tg = i / (N / 4), n4 = i % (N / 4);
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      w[k] = *reinterpret_cast<const uint32_t*>(qB + (((size_t)b * L + t0 + 4 * tg + k) * G + g) * N + 4 * n4);
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch) {
+      const uint32_t lo = __byte_perm(w[0], w[1], 0x0040 + 0x11 * ch), hi = __byte_perm(w[2], w[3], 0x0040 + 0x11 * ch);
+      s[4 * n4 + ch][tg] = __byte_perm(lo, hi, 0x5410);
+    }
+  }
+  __syncthreads();
+  const int NC = L / C;
+  int8_t* dst = qBT + ((((size_t)b * NC + c) * G + g) * N) * C + tc;
+  for (int i = tid; i < N * 16; i += 256) {
+    const int n = i >> 4, w = i & 15;
+    *reinterpret_cast<uint32_t*>(dst + (size_t)n * C + 4 * w) = s[n][w];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ state passing
+// mamba2/state_passing.py:55-93: s32 <- ((s32 * gate_q + 64) >> 7) + new, gate_q = clamp(half_away(exp(dA_last)*128)),
+// out[:, c] = clamp(s32 entering chunk c), final = clamp(s32 after the last chunk). 16 state bytes per thread.
+__global__ void __launch_bounds__(256) ssd_state_passing_kernel(const int8_t* states, const float* dA, int8_t* out,
+                                                                int8_t* final_state, int H, int NC, int C, int D) {
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int d0 = (blockIdx.x * 256 + threadIdx.x) * 16;
+  if (d0 >= D) return;
+  int s32[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) s32[i] = 0;
+  const size_t cstride = (size_t)H * D;
+  const int8_t* src = states + ((size_t)b * NC * H + h) * D + d0;
+  int8_t* dst = out + ((size_t)b * NC * H + h) * D + d0;
+  const float* dAl = dA + (((size_t)b * H + h) * NC) * C + (C - 1);
+  uint4 nxt = __ldg(reinterpret_cast<const uint4*>(src));
+  for (int c = 0; c < NC; ++c) {
+    const uint4 cur = nxt;
+    if (c + 1 < NC) nxt = __ldg(reinterpret_cast<const uint4*>(src + (size_t)(c + 1) * cstride));
+    uint32_t o[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      int cd[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) cd[k] = min(max(s32[4 * w + k], -127), 127);
+      o[w] = pack4(cd[0], cd[1], cd[2], cd[3]);
+    }
+    *reinterpret_cast<uint4*>(dst + (size_t)c * cstride) = make_uint4(o[0], o[1], o[2], o[3]);
+    const float gs = __fmul_rn(expf(dAl[(size_t)c * C]), 128.f);
+    const int gq = round_half_away(gs, 127.f);
+    const uint32_t cw[4] = {cur.x, cur.y, cur.z, cur.w};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int nw = (int)(int8_t)((cw[i >> 2] >> (8 * (i & 3))) & 0xff);
+      s32[i] = ((s32[i] * gq + 64) >> 7) + nw;
+    }
+  }
+  uint32_t o[4];
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    int cd[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) cd[k] = min(max(s32[4 * w + k], -127), 127);
+    o[w] = pack4(cd[0], cd[1], cd[2], cd[3]);
+  }
+  *reinterpret_cast<uint4*>(final_state + ((size_t)b * H + h) * D + d0) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// ------------------------------------------------------------------------------------------------ chunk state
+// One CTA per (chunk, head, batch), headdim 64: states[p, n] = sum_k xq[k, p] * Bq[k, n] over the chunk's tokens.
+// Both operands need the token index contiguous: x is quantised on the fly and transposed through shared memory
+// (four tokens packed per word); value side reads the pre-transposed INT8 B straight from global memory, key side
+// quantises the gate-weighted B per head into shared memory the same way.
+//   value side  mamba2/chunk_state.py:186-246        xq = half_away((x / alpha_p) * gate_k), requant (alpha/S_out)*bscale_g
+//   key side    mamba2/chunk_state_keyside.py:267-321  xq = rint(x / x_scale_p), Bq = rint(B*gate_k*127/bg_n), rint requant
+template <typename T, int N, bool KEYSIDE>
+__global__ void __launch_bounds__(128) ssd_chunk_state_kernel(lq_ssd_problem p) {
+  constexpr int P = 64, LDW = 20;
+  __shared__ __align__(16) uint32_t s_x[2][P][LDW];
+  __shared__ __align__(16) uint32_t s_b[KEYSIDE ? 2 : 1][KEYSIDE ? N : 1][LDW];
+  __shared__ float s_gate[256];
+
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int C = p.chunk, NC = p.L / C, grp = h / (p.H / p.G);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, j = lane & 3;
+
+  const size_t cbase = (((size_t)b * p.H + h) * NC + c) * C;
+  {
+    const float last = p.dA[cbase + C - 1];
+    for (int t = tid; t < C; t += 128) s_gate[t] = __fmul_rn(expf(__fsub_rn(last, p.dA[cbase + t])), p.dt[cbase + t]);
+  }
+  float xinv[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int pp = 2 * lane + e;
+    xinv[e] = KEYSIDE ? 1.0f / fmaxf(p.x_scale_hp[h * P + pp], 1e-10f) : 1.0f / p.alpha_hp[h * P + pp];
+  }
+  float binv[KEYSIDE ? N / 32 : 1];
+  const float* bgs = nullptr;
+  if (KEYSIDE) {
+    bgs = p.b_gate_scale + b * p.bgs_stride[0] + c * p.bgs_stride[1] + h * p.bgs_stride[2];
+#pragma unroll
+    for (int q = 0; q < N / 32; ++q) binv[q] = 127.0f / bgs[(64 * (q >> 1) + 2 * lane + (q & 1)) * p.bgs_stride[3]];
+  }
+  __syncthreads();
+
+  const T* xp = reinterpret_cast<const T*>(p.x) + (size_t)b * p.x_stride_b + (size_t)h * p.x_stride_h + 2 * lane;
+  const T* bp = reinterpret_cast<const T*>(p.b_fp);
+  const int8_t* qbt = KEYSIDE ? nullptr : p.q_BT + ((((size_t)b * NC + c) * p.G + grp) * N) * C;
+
+  int acc[N / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < N / 8; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0;
+
+  for (int s = 0; s < C / 64; ++s) {
+    const int buf = s & 1;
+    for (int tg = warp; tg < 16; tg += 4) {
+      uint32_t w0 = 0u, w1 = 0u;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int t = 64 * s + 4 * tg + i;
+        const uint32_t raw = *reinterpret_cast<const uint32_t*>(xp + (size_t)(c * C + t) * p.x_stride_t);
+        float x0, x1;
+        if (sizeof(T) == 2 && std::is_same<T, __half>::value) {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&raw));
+          x0 = f.x; x1 = f.y;
+        } else {
+          x0 = __uint_as_float(raw << 16); x1 = __uint_as_float(raw & 0xffff0000u);
+        }
+        int c0, c1;
+        if (KEYSIDE) {
+          c0 = round_rint(__fmul_rn(x0, xinv[0]), -127.f, 127.f);
+          c1 = round_rint(__fmul_rn(x1, xinv[1]), -127.f, 127.f);
+        } else {
+          const float gk = s_gate[t];
+          c0 = round_half_away(__fmul_rn(__fmul_rn(x0, xinv[0]), gk), 127.f);
+          c1 = round_half_away(__fmul_rn(__fmul_rn(x1, xinv[1]), gk), 127.f);
+        }
+        w0 |= ((uint32_t)c0 & 0xffu) << (8 * i);
+        w1 |= ((uint32_t)c1 & 0xffu) << (8 * i);
+      }
+      s_x[buf][2 * lane][tg] = w0;
+      s_x[buf][2 * lane + 1][tg] = w1;
+    }
+    if (KEYSIDE) {
+      for (int tg = warp; tg < 16; tg += 4) {
+#pragma unroll
+        for (int half = 0; half < N / 64; ++half) {
+          uint32_t w0 = 0u, w1 = 0u;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int t = 64 * s + 4 * tg + i;
+            const uint32_t raw = *reinterpret_cast<const uint32_t*>(
+                bp + (((size_t)b * p.L + (size_t)c * C + t) * p.G + grp) * N + 64 * half + 2 * lane);
+            float x0, x1;
+            if (std::is_same<T, __half>::value) {
+              const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&raw));
+              x0 = f.x; x1 = f.y;
+            } else {
+              x0 = __uint_as_float(raw << 16); x1 = __uint_as_float(raw & 0xffff0000u);
+            }
+            const float gk = s_gate[t];
+            const int c0 = round_rint(__fmul_rn(__fmul_rn(x0, gk), binv[2 * half]), -127.f, 127.f);
+            const int c1 = round_rint(__fmul_rn(__fmul_rn(x1, gk), binv[2 * half + 1]), -127.f, 127.f);
+            w0 |= ((uint32_t)c0 & 0xffu) << (8 * i);
+            w1 |= ((uint32_t)c1 & 0xffu) << (8 * i);
+          }
+          s_b[KEYSIDE ? buf : 0][KEYSIDE ? 64 * half + 2 * lane : 0][tg] = w0;
+          s_b[KEYSIDE ? buf : 0][KEYSIDE ? 64 * half + 2 * lane + 1 : 0][tg] = w1;
+        }
+      }
+    }
+    __syncthreads();
+    const uint4 xa = *reinterpret_cast<const uint4*>(&s_x[buf][16 * warp + g][4 * j]);
+    const uint4 xb = *reinterpret_cast<const uint4*>(&s_x[buf][16 * warp + g + 8][4 * j]);
+#pragma unroll
+    for (int nt = 0; nt < N / 8; ++nt) {
+      const int nr = 32 * (nt >> 2) + 8 * (g >> 1) + 2 * (nt & 3) + (g & 1);
+      uint4 bq;
+      if (KEYSIDE) bq = *reinterpret_cast<const uint4*>(&s_b[KEYSIDE ? buf : 0][KEYSIDE ? nr : 0][4 * j]);
+      else bq = __ldg(reinterpret_cast<const uint4*>(qbt + (size_t)nr * C + 64 * s + 16 * j));
+      mma_s8(acc[nt], xa.x, xb.x, xa.y, xb.y, bq.x, bq.y);
+      mma_s8(acc[nt], xa.z, xb.z, xa.w, xb.w, bq.z, bq.w);
+    }
+  }
+
+  // epilogue: requantise to INT8, eight consecutive state channels per thread and row
+  const int pa = 16 * warp + g, pb = pa + 8;
+  int8_t* st = p.states + ((((size_t)b * NC + c) * p.H + h) * P) * N;
+  float ra, rb;
+  if (KEYSIDE) {
+    ra = p.x_scale_hp[h * P + pa] / p.state_scale[h * P + pa];
+    rb = p.x_scale_hp[h * P + pb] / p.state_scale[h * P + pb];
+  } else {
+    const float bs = p.bscale_g[grp];
+    ra = __fmul_rn(p.alpha_hp[h * P + pa] / p.state_scale[h * P + pa], bs);
+    rb = __fmul_rn(p.alpha_hp[h * P + pb] / p.state_scale[h * P + pb], bs);
+  }
+#pragma unroll
+  for (int ng = 0; ng < N / 32; ++ng) {
+    int ca[8], cb[8];
+#pragma unroll
+    for (int n4 = 0; n4 < 4; ++n4) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int i = 2 * n4 + e;
+        const float fa = (float)acc[4 * ng + n4][e], fb = (float)acc[4 * ng + n4][2 + e];
+        if (KEYSIDE) {
+          const float sn = bgs[(32 * ng + 8 * j + i) * p.bgs_stride[3]] / 127.0f;
+          ca[i] = round_rint(__fmul_rn(__fmul_rn(fa, sn), ra), -127.f, 127.f);
+          cb[i] = round_rint(__fmul_rn(__fmul_rn(fb, sn), rb), -127.f, 127.f);
+        } else {
+          ca[i] = round_half_away(__fmul_rn(fa, ra), 127.f);
+          cb[i] = round_half_away(__fmul_rn(fb, rb), 127.f);
+        }
+      }
+    }
+    *reinterpret_cast<uint2*>(st + (size_t)pa * N + 32 * ng + 8 * j) =
+        make_uint2(pack4(ca[0], ca[1], ca[2], ca[3]), pack4(ca[4], ca[5], ca[6], ca[7]));
+    *reinterpret_cast<uint2*>(st + (size_t)pb * N + 32 * ng + 8 * j) =
+        make_uint2(pack4(cb[0], cb[1], cb[2], cb[3]), pack4(cb[4], cb[5], cb[6], cb[7]));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ C.B^T
+// mamba2/bmm_chunk.py:103-139: cb[m, n] = rint( int32(C_i8[m,:] . B_i8[n,:]) * (s_C*s_B/S_cb) ) clamped to +-127.
+// One CTA per 64x64 output tile; fragments come straight from global memory (the state index is contiguous in both
+// operands). B_IS_FP quantises B in the fragment load: rint(b / s_B), clamp +-127.
+template <typename T, int N, bool B_IS_FP>
+__global__ void __launch_bounds__(128) ssd_bmm_kernel(lq_ssd_problem p) {
+  const int C = p.chunk, NC = p.L / C;
+  const int tiles = C / 64;
+  const int m0 = (blockIdx.x / tiles) * 64, n0 = (blockIdx.x % tiles) * 64;
+  const int c = blockIdx.y / p.G, grp = blockIdx.y % p.G, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, j = lane & 3;
+  const int ma = m0 + 16 * warp + g, mb = ma + 8;
+  const size_t rowC = ((size_t)b * p.L + (size_t)c * C) * p.G + grp;  // + token * G
+  const float a_sc = p.C_scale[grp], b_sc = p.B_scale[grp];
+  const float b_inv = 1.0f / b_sc;
+  uint4 qa[N / 64], qb[N / 64];
+#pragma unroll
+  for (int kk = 0; kk < N / 64; ++kk) {
+    qa[kk] = __ldg(reinterpret_cast<const uint4*>(p.q_C + (rowC + (size_t)ma * p.G) * N + 64 * kk + 16 * j));
+    qb[kk] = __ldg(reinterpret_cast<const uint4*>(p.q_C + (rowC + (size_t)mb * p.G) * N + 64 * kk + 16 * j));
+  }
+  const float inv_scb = __fmul_rn(a_sc, b_sc) / p.cb_scale[grp];
+  int8_t* out = p.cb + (((size_t)b * NC + c) * p.G + grp) * C * C;
+#pragma unroll
+  for (int ng = 0; ng < 2; ++ng) {
+    int ca[8], cb[8];
+#pragma unroll
+    for (int n4 = 0; n4 < 4; ++n4) {
+      const int tok = n0 + 32 * ng + 8 * (g >> 1) + 2 * n4 + (g & 1);
+      int acc[4] = {0, 0, 0, 0};
+#pragma unroll
+      for (int kk = 0; kk < N / 64; ++kk) {
+        uint4 bq;
+        if (B_IS_FP) {
+          const T* bp = reinterpret_cast<const T*>(p.b_fp) + (rowC + (size_t)tok * p.G) * N + 64 * kk + 16 * j;
+          float x[16];
+          float (&x0)[8] = *reinterpret_cast<float (*)[8]>(&x[0]);
+          float (&x1)[8] = *reinterpret_cast<float (*)[8]>(&x[8]);
+          Act<T>::unpack8(__ldg(reinterpret_cast<const uint4*>(bp)), x0);
+          Act<T>::unpack8(__ldg(reinterpret_cast<const uint4*>(bp + 8)), x1);
+          int cd[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) cd[i] = round_rint(__fmul_rn(x[i], b_inv), -127.f, 127.f);
+          bq = make_uint4(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4], cd[5], cd[6], cd[7]),
+                          pack4(cd[8], cd[9], cd[10], cd[11]), pack4(cd[12], cd[13], cd[14], cd[15]));
+        } else {
+          bq = __ldg(reinterpret_cast<const uint4*>(p.q_B + (rowC + (size_t)tok * p.G) * N + 64 * kk + 16 * j));
+        }
+        mma_s8(acc, qa[kk].x, qb[kk].x, qa[kk].y, qb[kk].y, bq.x, bq.y);
+        mma_s8(acc, qa[kk].z, qb[kk].z, qa[kk].w, qb[kk].w, bq.z, bq.w);
+      }
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        ca[2 * n4 + e] = round_rint(__fmul_rn((float)acc[e], inv_scb), -127.f, 127.f);
+        cb[2 * n4 + e] = round_rint(__fmul_rn((float)acc[2 + e], inv_scb), -127.f, 127.f);
+      }
+    }
+    *reinterpret_cast<uint2*>(out + (size_t)ma * C + n0 + 32 * ng + 8 * j) =
+        make_uint2(pack4(ca[0], ca[1], ca[2], ca[3]), pack4(ca[4], ca[5], ca[6], ca[7]));
+    *reinterpret_cast<uint2*>(out + (size_t)mb * C + n0 + 32 * ng + 8 * j) =
+        make_uint2(pack4(cb[0], cb[1], cb[2], cb[3]), pack4(cb[4], cb[5], cb[6], cb[7]));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ chunk scan
+// mamba2/chunk_scan_v2.py:160-256. One CTA per (chunk, head, batch), headdim 64. The x tile is staged once in shared
+// memory as fp16 (XOR-swizzled rows) and serves both the causal fp16 product (ldmatrix.trans B fragments) and the
+// D*x residual; C rows, passed states and the INT8 CB rows are read as fragments straight from global memory.
+//   out = int32(C_i8 . S_i8) * s_C * s_state[p] * exp(dA_m) + fp16(cb * S_cb * exp(dA_m - dA_k) * dt_k, k <= m) . fp16(x) + D x
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem_row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+
+template <typename T, int N>
+__global__ void __launch_bounds__(256) ssd_chunk_scan_kernel(lq_ssd_problem p) {
+  constexpr int P = 64;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int C = p.chunk, NC = p.L / C;
+  uint8_t* s_x = smem;                                   // [C][128 B] fp16, 16-byte chunk index ^ (row & 7)
+  float* s_dA = reinterpret_cast<float*>(smem + (size_t)C * 128);
+  float* s_dt = s_dA + C;
+
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int grp = h / (p.H / p.G);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, j = lane & 3;
+  const size_t cbase = (((size_t)b * p.H + h) * NC + c) * C;
+
+  for (int t = tid; t < C; t += 256) {
+    s_dA[t] = p.dA[cbase + t];
+    s_dt[t] = p.dt[cbase + t];
+  }
+  {
+    const T* xp = reinterpret_cast<const T*>(p.x) + (size_t)b * p.x_stride_b + (size_t)h * p.x_stride_h;
+    for (int i = tid; i < C * 8; i += 256) {
+      const int row = i >> 3, ch = i & 7;
+      uint4 raw = __ldg(reinterpret_cast<const uint4*>(xp + (size_t)(c * C + row) * p.x_stride_t + 8 * ch));
+      if (!std::is_same<T, __half>::value) {
+        float x[8];
+        Act<T>::unpack8(raw, x);
+        raw = make_uint4(Act<__half>::pack2(x[0], x[1]), Act<__half>::pack2(x[2], x[3]), Act<__half>::pack2(x[4], x[5]),
+                         Act<__half>::pack2(x[6], x[7]));
+      }
+      *reinterpret_cast<uint4*>(s_x + row * 128 + ((ch ^ (row & 7)) << 4)) = raw;
+    }
+  }
+  __syncthreads();
+
+  const float gscale = p.C_scale[grp], Scb = p.cb_scale[grp];
+  const int MT = C / 16;
+  const int8_t* qc = p.q_C + (((size_t)b * p.L + (size_t)c * C) * p.G + grp) * N;
+  const int8_t* sp = p.passed + ((((size_t)b * NC + c) * p.H + h) * P) * N;
+  const int8_t* cbp = p.cb + (((size_t)b * NC + c) * p.G + grp) * C * C;
+  __half* op = reinterpret_cast<__half*>(p.out);
+
+  for (int it = 0; it * 8 < MT; ++it) {
+    const int mt = (it & 1) ? it * 8 + 7 - warp : it * 8 + warp;  // pair light and heavy causal rows
+    if (mt >= MT) continue;
+    const int ma = 16 * mt + g, mb = ma + 8;
+    const float dAa = s_dA[ma], dAb = s_dA[mb];
+
+    // ---- state read (INT8)
+    float accf[8][4];
+    {
+      uint4 qa[N / 64], qb[N / 64];
+#pragma unroll
+      for (int kk = 0; kk < N / 64; ++kk) {
+        qa[kk] = __ldg(reinterpret_cast<const uint4*>(qc + (size_t)ma * p.G * N + 64 * kk + 16 * j));
+        qb[kk] = __ldg(reinterpret_cast<const uint4*>(qc + (size_t)mb * p.G * N + 64 * kk + 16 * j));
+      }
+      const float ga = expf(dAa), gb = expf(dAb);
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        int acc[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int kk = 0; kk < N / 64; ++kk) {
+          const uint4 bs = __ldg(reinterpret_cast<const uint4*>(sp + (size_t)(8 * nt + g) * N + 64 * kk + 16 * j));
+          mma_s8(acc, qa[kk].x, qb[kk].x, qa[kk].y, qb[kk].y, bs.x, bs.y);
+          mma_s8(acc, qa[kk].z, qb[kk].z, qa[kk].w, qb[kk].w, bs.z, bs.w);
+        }
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float ss = p.state_scale[h * P + 8 * nt + 2 * j + e];
+          accf[nt][e] = __fmul_rn(__fmul_rn(__fmul_rn((float)acc[e], gscale), ss), ga);
+          accf[nt][2 + e] = __fmul_rn(__fmul_rn(__fmul_rn((float)acc[2 + e], gscale), ss), gb);
+        }
+      }
+    }
+    // ---- causal fp16 product
+    float conv[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) conv[nt][0] = conv[nt][1] = conv[nt][2] = conv[nt][3] = 0.f;
+    for (int ks = 0; ks <= mt; ++ks) {
+      uint32_t af[4];
+#pragma unroll
+      for (int hi = 0; hi < 2; ++hi) {
+        const int k0 = 16 * ks + 8 * hi + 2 * j;
+        const uint16_t wa = *reinterpret_cast<const uint16_t*>(cbp + (size_t)ma * C + k0);
+        const uint16_t wb = *reinterpret_cast<const uint16_t*>(cbp + (size_t)mb * C + k0);
+        float va[2], vb[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int k = k0 + e;
+          const float dk = s_dA[k], dtk = s_dt[k];
+          const float ca = (float)(int8_t)((wa >> (8 * e)) & 0xff), cb = (float)(int8_t)((wb >> (8 * e)) & 0xff);
+          va[e] = (ma >= k) ? __fmul_rn(__fmul_rn(__fmul_rn(ca, Scb), expf(__fsub_rn(dAa, dk))), dtk) : 0.f;
+          vb[e] = (mb >= k) ? __fmul_rn(__fmul_rn(__fmul_rn(cb, Scb), expf(__fsub_rn(dAb, dk))), dtk) : 0.f;
+        }
+        af[2 * hi] = Act<__half>::pack2(va[0], va[1]);
+        af[2 * hi + 1] = Act<__half>::pack2(vb[0], vb[1]);
+      }
+#pragma unroll
+      for (int n2 = 0; n2 < 4; ++n2) {
+        const int mi = lane >> 3;
+        const int row = 16 * ks + 8 * (mi & 1) + (lane & 7);
+        const int ch = 2 * n2 + (mi >> 1);
+        uint32_t r[4];
+        ldmatrix_x4_trans(r, s_x + row * 128 + ((ch ^ (row & 7)) << 4));
+        mma_f16(conv[2 * n2], af[0], af[1], af[2], af[3], r[0], r[1]);
+        mma_f16(conv[2 * n2 + 1], af[0], af[1], af[2], af[3], r[2], r[3]);
+      }
+    }
+    // ---- combine, D*x residual, store fp16
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const int pc = 8 * nt + 2 * j;
+      float oa[2], ob[2];
+      const float2 xa = __half22float2(*reinterpret_cast<const __half2*>(s_x + ma * 128 + ((nt ^ (ma & 7)) << 4) + 4 * j));
+      const float2 xb = __half22float2(*reinterpret_cast<const __half2*>(s_x + mb * 128 + ((nt ^ (mb & 7)) << 4) + 4 * j));
+      const float xav[2] = {xa.x, xa.y}, xbv[2] = {xb.x, xb.y};
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        oa[e] = __fadd_rn(accf[nt][e], conv[nt][e]);
+        ob[e] = __fadd_rn(accf[nt][2 + e], conv[nt][2 + e]);
+        if (p.D != nullptr) {
+          const float Dv = p.D_has_hdim ? p.D[h * P + pc + e] : p.D[h];
+          oa[e] = __fadd_rn(oa[e], __fmul_rn(xav[e], Dv));
+          ob[e] = __fadd_rn(ob[e], __fmul_rn(xbv[e], Dv));
+        }
+      }
+      *reinterpret_cast<uint32_t*>(op + (((size_t)b * p.L + (size_t)c * C + ma) * p.H + h) * P + pc) = Act<__half>::pack2(oa[0], oa[1]);
+      *reinterpret_cast<uint32_t*>(op + (((size_t)b * p.L + (size_t)c * C + mb) * p.H + h) * P + pc) = Act<__half>::pack2(ob[0], ob[1]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ B/C prologue
+// mamba2/fused_split_rotate_xBC.py:90-138 and kernels/hadamard.py:70-103. A row of N state channels is held by
+// N/8 lanes; the H_2 (x) H_{N/2} product on bf16-rounded inputs is the full Walsh-Hadamard butterfly scaled by the
+// bf16 value of 1/sqrt(N/2) and then by 1/sqrt(2) in fp32.
+__device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ float fp16r(float x) { return __half2float(__float2half_rn(x)); }
+
+template <typename T, int N, bool QUANT>
+__global__ void __launch_bounds__(256) ssd_rotate_rows_kernel(const T* x, long long stride_b, long long stride_t,
+                                                              long long off_b, long long off_c, int T_len, int G,
+                                                              const float* signs, const float* inv_b, const float* inv_c,
+                                                              const float* dqk_b, const float* dqk_c, int8_t* q_b,
+                                                              int8_t* q_c, T* y) {
+  // QUANT: blockIdx.y in [0, 2G) selects (B|C, group); otherwise blockIdx.y is the head and y is the dense output.
+  constexpr int LPR = N / 8, RPW = 32 / LPR;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r = lane % LPR, sub = lane / LPR;
+  const int b = blockIdx.z;
+  const int which = QUANT ? blockIdx.y / G : 0, grp = QUANT ? blockIdx.y % G : blockIdx.y;
+  int t = (blockIdx.x * 8 + warp) * RPW + sub;
+  const bool live = t < T_len;
+  if (!live) t = T_len - 1;
+  const T* src = x + (size_t)b * stride_b + (size_t)t * stride_t + (which ? off_c : off_b) + (size_t)grp * N + 8 * r;
+  float v[8];
+  Act<T>::unpack8(__ldg(reinterpret_cast<const uint4*>(src)), v);
+  const float* dq = QUANT ? (which ? dqk_c : dqk_b) : nullptr;
+  if (dq != nullptr) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = fp16r(__fmul_rn(v[i], fp16r(dq[grp * N + 8 * r + i])));
+  }
+  if (signs != nullptr) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = bf16r(__fmul_rn(v[i], signs[grp * N + 8 * r + i]));
+    fwht8<LPR>(v, r);
+    const float hs = bf16r(N == 128 ? 0.125f : 0.17677669529663687f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(v[i], hs), 0.70710678118654752f);
+  }
+  if (QUANT) {
+    const float inv = which ? inv_c[grp] : inv_b[grp];
+    int cd[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) cd[i] = round_rint(__fmul_rn(fp16r(v[i]), inv), -128.f, 127.f);
+    if (live) {
+      int8_t* dst = (which ? q_c : q_b) + (((size_t)b * T_len + t) * G + grp) * N + 8 * r;
+      *reinterpret_cast<uint2*>(dst) = make_uint2(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4], cd[5], cd[6], cd[7]));
+    }
+  } else if (live) {
+    T* dst = y + (((size_t)b * T_len + t) * G + grp) * N + 8 * r;
+    *reinterpret_cast<uint4*>(dst) = make_uint4(Act<T>::pack2(v[0], v[1]), Act<T>::pack2(v[2], v[3]),
+                                                Act<T>::pack2(v[4], v[5]), Act<T>::pack2(v[6], v[7]));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ launchers
+static int ssd_check(const lq_ssd_problem* p, const char* what) {
+  if (!p) return fail(LQ_ERR_NULL, "%s: problem descriptor is null", what);
+  if (p->B <= 0 || p->L <= 0 || p->H <= 0 || p->G <= 0) return fail(LQ_ERR_SHAPE, "%s: non-positive extent", what);
+  if (p->chunk <= 0 || p->chunk % 64 != 0 || p->chunk > 256) return fail(LQ_ERR_UNSUPPORTED, "%s: chunk size %d (64, 128, 192 or 256 supported)", what, p->chunk);
+  if (p->L % p->chunk != 0) return fail(LQ_ERR_SHAPE, "%s: L=%d must be a multiple of the chunk size %d", what, p->L, p->chunk);
+  if (p->H % p->G != 0) return fail(LQ_ERR_SHAPE, "%s: nheads %d not divisible by ngroups %d", what, p->H, p->G);
+  return LQ_OK;
+}
+static int ssd_check_pn(const lq_ssd_problem* p, const char* what) {
+  if (p->P != 64) return fail(LQ_ERR_UNSUPPORTED, "%s: headdim %d (this build implements headdim 64)", what, p->P);
+  if (p->N != 64 && p->N != 128) return fail(LQ_ERR_UNSUPPORTED, "%s: d_state %d (64 or 128 supported)", what, p->N);
+  if (p->x_dtype != LQ_F16 && p->x_dtype != LQ_BF16) return fail(LQ_ERR_UNSUPPORTED, "%s: x must be f16 or bf16", what);
+  if (!p->x || (reinterpret_cast<uintptr_t>(p->x) & 15u) || (p->x_stride_t % 8) || (p->x_stride_b % 8) || (p->x_stride_h % 8))
+    return fail(LQ_ERR_ALIGN, "%s: x must be 16-byte aligned with strides that are multiples of 8 elements", what);
+  return LQ_OK;
+}
+
+template <bool KEYSIDE>
+static void launch_chunk_state(const lq_ssd_problem* p, dim3 grid, cudaStream_t st) {
+  if (p->x_dtype == LQ_F16) {
+    if (p->N == 128) ssd_chunk_state_kernel<__half, 128, KEYSIDE><<<grid, 128, 0, st>>>(*p);
+    else ssd_chunk_state_kernel<__half, 64, KEYSIDE><<<grid, 128, 0, st>>>(*p);
+  } else {
+    if (p->N == 128) ssd_chunk_state_kernel<__nv_bfloat16, 128, KEYSIDE><<<grid, 128, 0, st>>>(*p);
+    else ssd_chunk_state_kernel<__nv_bfloat16, 64, KEYSIDE><<<grid, 128, 0, st>>>(*p);
+  }
+}
+template <bool B_IS_FP>
+static void launch_bmm(const lq_ssd_problem* p, dim3 grid, cudaStream_t st) {
+  if (p->x_dtype == LQ_BF16) {
+    if (p->N == 128) ssd_bmm_kernel<__nv_bfloat16, 128, B_IS_FP><<<grid, 128, 0, st>>>(*p);
+    else ssd_bmm_kernel<__nv_bfloat16, 64, B_IS_FP><<<grid, 128, 0, st>>>(*p);
+  } else {
+    if (p->N == 128) ssd_bmm_kernel<__half, 128, B_IS_FP><<<grid, 128, 0, st>>>(*p);
+    else ssd_bmm_kernel<__half, 64, B_IS_FP><<<grid, 128, 0, st>>>(*p);
+  }
+}
+
+}  // namespace lq
+
+using namespace lq;
+
+extern "C" int lq_ssd_chunk_cumsum(const lq_ssd_problem* p, lq_stream stream) {
+  if (int e = ssd_check(p, "chunk_cumsum")) return e;
+  if (!p->dt_in || !p->A_log || !p->dt || !p->dA) return fail(LQ_ERR_NULL, "chunk_cumsum: dt_in, A_log, dt, dA required");
+  if (p->H > 1024) return fail(LQ_ERR_UNSUPPORTED, "chunk_cumsum: more than 1024 heads");
+  ssd_cumsum_kernel<<<dim3(p->L / p->chunk, p->B), ((p->H + 31) / 32) * 32, 0, (cudaStream_t)stream>>>(*p);
+  return check_launch("ssd_cumsum_kernel");
+}
+
+extern "C" int lq_ssd_state_passing(const lq_ssd_problem* p, lq_stream stream) {
+  if (int e = ssd_check(p, "state_passing")) return e;
+  if (!p->states || !p->passed || !p->final_state || !p->dA) return fail(LQ_ERR_NULL, "state_passing: states, passed, final_state, dA required");
+  const int D = p->P * p->N;
+  if (D % 16 != 0) return fail(LQ_ERR_SHAPE, "state_passing: P*N must be a multiple of 16");
+  dim3 grid((D / 16 + 255) / 256, p->H, p->B);
+  ssd_state_passing_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p->states, p->dA, p->passed, p->final_state, p->H,
+                                                                    p->L / p->chunk, p->chunk, D);
+  return check_launch("ssd_state_passing_kernel");
+}
+
+static int ssd_chunk_state(const lq_ssd_problem* p, bool keyside, lq_stream stream) {
+  const char* what = keyside ? "chunk_state_key" : "chunk_state_value";
+  if (int e = ssd_check(p, what)) return e;
+  if (int e = ssd_check_pn(p, what)) return e;
+  if (!p->dt || !p->dA || !p->states || !p->state_scale) return fail(LQ_ERR_NULL, "%s: dt, dA, states, state_scale required", what);
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 grid(p->L / p->chunk, p->H, p->B);
+  if (keyside) {
+    if (!p->b_fp || !p->x_scale_hp || !p->b_gate_scale) return fail(LQ_ERR_NULL, "%s: b_fp, x_scale_hp, b_gate_scale required", what);
+    launch_chunk_state<true>(p, grid, st);
+  } else {
+    if (!p->q_B || !p->q_BT || !p->alpha_hp || !p->bscale_g) return fail(LQ_ERR_NULL, "%s: q_B, q_BT, alpha_hp, bscale_g required", what);
+    ssd_transpose_b_kernel<<<dim3(p->L / 64, p->G, p->B), 256, 0, st>>>(p->q_B, p->q_BT, p->L, p->G, p->N, p->chunk);
+    if (int e = check_launch("ssd_transpose_b_kernel")) return e;
+    launch_chunk_state<false>(p, grid, st);
+  }
+  return check_launch("ssd_chunk_state_kernel");
+}
+extern "C" int lq_ssd_chunk_state_value(const lq_ssd_problem* p, lq_stream stream) { return ssd_chunk_state(p, false, stream); }
+extern "C" int lq_ssd_chunk_state_key(const lq_ssd_problem* p, lq_stream stream) { return ssd_chunk_state(p, true, stream); }
+
+extern "C" int lq_ssd_bmm_chunk(const lq_ssd_problem* p, int b_is_fp, lq_stream stream) {
+  if (int e = ssd_check(p, "bmm_chunk")) return e;
+  if (p->N != 64 && p->N != 128) return fail(LQ_ERR_UNSUPPORTED, "bmm_chunk: d_state %d (64 or 128 supported)", p->N);
+  if (!p->q_C || !p->C_scale || !p->B_scale || !p->cb_scale || !p->cb) return fail(LQ_ERR_NULL, "bmm_chunk: q_C, scales, cb required");
+  if (b_is_fp ? !p->b_fp : !p->q_B) return fail(LQ_ERR_NULL, "bmm_chunk: B operand missing");
+  const int tiles = p->chunk / 64;
+  dim3 grid(tiles * tiles, (p->L / p->chunk) * p->G, p->B);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (b_is_fp) launch_bmm<true>(p, grid, st);
+  else launch_bmm<false>(p, grid, st);
+  return check_launch("ssd_bmm_kernel");
+}
+
+template <typename T, int N>
+static int launch_scan(const lq_ssd_problem* p, cudaStream_t st) {
+  const size_t smem = (size_t)p->chunk * 128 + 2 * sizeof(float) * p->chunk;
+  dim3 grid(p->L / p->chunk, p->H, p->B);
+  ssd_chunk_scan_kernel<T, N><<<grid, 256, smem, st>>>(*p);
+  return check_launch("ssd_chunk_scan_kernel");
+}
+extern "C" int lq_ssd_chunk_scan(const lq_ssd_problem* p, lq_stream stream) {
+  if (int e = ssd_check(p, "chunk_scan")) return e;
+  if (int e = ssd_check_pn(p, "chunk_scan")) return e;
+  if (!p->cb || !p->dt || !p->dA || !p->q_C || !p->C_scale || !p->passed || !p->state_scale || !p->cb_scale || !p->out)
+    return fail(LQ_ERR_NULL, "chunk_scan: cb, dt, dA, q_C, C_scale, passed, state_scale, cb_scale, out required");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (p->x_dtype == LQ_F16) return p->N == 128 ? launch_scan<__half, 128>(p, st) : launch_scan<__half, 64>(p, st);
+  return p->N == 128 ? launch_scan<__nv_bfloat16, 128>(p, st) : launch_scan<__nv_bfloat16, 64>(p, st);
+}
+
+template <typename T, bool QUANT>
+static int launch_rotate(const T* x, long long sb, long long stt, long long ob, long long oc, int B, int T_len, int G, int N,
+                         int gy, const float* signs, const float* ib, const float* ic, const float* db, const float* dc,
+                         int8_t* qb, int8_t* qc, T* y, cudaStream_t st) {
+  const int rows_per_cta = 8 * (32 / (N / 8));
+  dim3 grid((T_len + rows_per_cta - 1) / rows_per_cta, gy, B);
+  if (N == 128) ssd_rotate_rows_kernel<T, 128, QUANT><<<grid, 256, 0, st>>>(x, sb, stt, ob, oc, T_len, G, signs, ib, ic, db, dc, qb, qc, y);
+  else if (N == 64) ssd_rotate_rows_kernel<T, 64, QUANT><<<grid, 256, 0, st>>>(x, sb, stt, ob, oc, T_len, G, signs, ib, ic, db, dc, qb, qc, y);
+  else return fail(LQ_ERR_UNSUPPORTED, "Hadamard rows: width %d (64 or 128 supported)", N);
+  return check_launch("ssd_rotate_rows_kernel");
+}
+
+extern "C" int lq_ssd_split_rotate_quant(const void* xBC, int dtype, int B, int T, int d_ssm, int G, int N, const float* signs,
+                                         const float* B_inv_scale, const float* C_inv_scale, const float* dqk_b,
+                                         const float* dqk_c, int8_t* q_B, int8_t* q_C, lq_stream stream) {
+  if (!xBC || !B_inv_scale || !C_inv_scale || !q_B || !q_C) return fail(LQ_ERR_NULL, "split_rotate_quant: null argument");
+  if (B <= 0 || T <= 0 || G <= 0) return fail(LQ_ERR_SHAPE, "split_rotate_quant: non-positive extent");
+  if ((d_ssm % 8) || (reinterpret_cast<uintptr_t>(xBC) & 15u)) return fail(LQ_ERR_ALIGN, "split_rotate_quant: xBC must be 16-byte aligned, d_ssm a multiple of 8");
+  if ((dqk_b == nullptr) != (dqk_c == nullptr)) return fail(LQ_ERR_NULL, "split_rotate_quant: dqk_b and dqk_c go together");
+  const long long xdim = (long long)d_ssm + 2LL * G * N;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == LQ_F16)
+    return launch_rotate<__half, true>(reinterpret_cast<const __half*>(xBC), (long long)T * xdim, xdim, d_ssm, d_ssm + (long long)G * N,
+                                       B, T, G, N, 2 * G, signs, B_inv_scale, C_inv_scale, dqk_b, dqk_c, q_B, q_C, nullptr, st);
+  if (dtype == LQ_BF16)
+    return launch_rotate<__nv_bfloat16, true>(reinterpret_cast<const __nv_bfloat16*>(xBC), (long long)T * xdim, xdim, d_ssm,
+                                              d_ssm + (long long)G * N, B, T, G, N, 2 * G, signs, B_inv_scale, C_inv_scale, dqk_b,
+                                              dqk_c, q_B, q_C, nullptr, st);
+  return fail(LQ_ERR_UNSUPPORTED, "split_rotate_quant: xBC must be f16 or bf16");
+}
+
+extern "C" int lq_kronecker_hadamard(const void* x, void* y, int dtype, int B, int T, int H, int D, long long in_stride_t,
+                                     const float* signs, lq_stream stream) {
+  if (!x || !y || !signs) return fail(LQ_ERR_NULL, "kronecker_hadamard: null argument");
+  if ((reinterpret_cast<uintptr_t>(x) & 15u) || (in_stride_t % 8)) return fail(LQ_ERR_ALIGN, "kronecker_hadamard: x must be 16-byte aligned, token stride a multiple of 8");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == LQ_F16)
+    return launch_rotate<__half, false>(reinterpret_cast<const __half*>(x), (long long)T * in_stride_t, in_stride_t, 0, 0, B, T, H, D, H,
+                                        signs, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, reinterpret_cast<__half*>(y), st);
+  if (dtype == LQ_BF16)
+    return launch_rotate<__nv_bfloat16, false>(reinterpret_cast<const __nv_bfloat16*>(x), (long long)T * in_stride_t, in_stride_t, 0, 0,
+                                               B, T, H, D, H, signs, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+                                               reinterpret_cast<__nv_bfloat16*>(y), st);
+  return fail(LQ_ERR_UNSUPPORTED, "kronecker_hadamard: x must be f16 or bf16");
+}

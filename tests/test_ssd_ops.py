@@ -1,0 +1,140 @@
+"""Mamba-2 SSD ops (CUDA, through the C ABI) against the CPU restatement in oracle/ssd_oracle.py.
+
+The reference has no tests for these ops; the oracle is a line-by-line restatement of its Triton sources, so these
+tests pin the CUDA kernels to that restatement only (INT8 outputs bit-exact up to rounding-boundary ties)."""
+
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import ssd_oracle as so
+from tests.helpers import code_mismatch, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+def make_case(B=2, L=512, H=4, P=64, G=1, N=128, chunk=256, dtype=torch.float16, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(B, L, H, P, generator=g)
+    x[..., :2] *= 8.0  # a few heavy channels
+    Bm = torch.randn(B, L, G, N, generator=g)
+    Cm = torch.randn(B, L, G, N, generator=g)
+    dt_raw = torch.randn(B, L, H, generator=g) * 0.5 - 2.0
+    A_log = torch.log(torch.exp(torch.rand(H, generator=g) * math.log(16.0)))
+    D = torch.randn(H, generator=g)
+    x, Bm, Cm = x.to(dtype), Bm.to(dtype), Cm.to(dtype)
+    sB = (Bm.float().abs().amax(dim=(0, 1, 3)) / 127).clamp_min(1e-6)
+    sC = (Cm.float().abs().amax(dim=(0, 1, 3)) / 127).clamp_min(1e-6)
+    qB = torch.round(Bm.float() / sB.view(1, 1, G, 1)).clamp(-127, 127).to(torch.int8)
+    qC = torch.round(Cm.float() / sC.view(1, 1, G, 1)).clamp(-127, 127).to(torch.int8)
+    dA, dtc = so.chunk_cumsum(dt_raw, 1.0, A_log, 1.0, chunk, None, True)
+    nc = L // chunk
+    gate = torch.exp(dA[..., -1:] - dA) * dtc  # [B,H,NC,C]
+    xw = x.float().view(B, nc, chunk, H, P).permute(0, 3, 1, 2, 4) * gate.unsqueeze(-1)
+    alpha = (xw.abs().amax(dim=(0, 2, 3)) / 127).clamp_min(1e-8)  # (H,P)
+    x_scale = (x.float().abs().amax(dim=(0, 1)) / 127).clamp_min(1e-8)
+    rep = H // G
+    Bf = Bm.float().view(B, nc, chunk, G, N).permute(0, 3, 1, 2, 4).repeat_interleave(rep, 1)
+    local = xw.transpose(-1, -2) @ Bf  # [B,H,NC,P,N]
+    run, amax = torch.zeros(B, H, P, N), torch.zeros(H, P)
+    for c in range(nc):
+        run = run * torch.exp(dA[:, :, c, -1]).view(B, H, 1, 1) + local[:, :, c]
+        amax = torch.maximum(amax, run.abs().amax(dim=(0, 3)))
+    state_scale = (amax / 127).clamp_min(1e-8)
+    b_gate = (Bf * gate.unsqueeze(-1)).abs().amax(dim=(0, 2, 3)).clamp_min(1e-8).view(1, 1, H, N)  # raw amax, not /127
+    Cf = Cm.float().view(B, nc, chunk, G, N).permute(0, 1, 3, 2, 4)
+    Bg = Bm.float().view(B, nc, chunk, G, N).permute(0, 1, 3, 2, 4)
+    cb_scale = ((Cf @ Bg.transpose(-1, -2)).abs().amax(dim=(0, 1, 3, 4)) / 127).clamp_min(1e-8)
+    return dict(x=x, Bm=Bm, Cm=Cm, qB=qB, qC=qC, sB=sB, sC=sC, dt_raw=dt_raw, A_log=A_log, D=D, alpha=alpha, x_scale=x_scale,
+                state_scale=state_scale, b_gate=b_gate, cb_scale=cb_scale, chunk=chunk, dA=dA, dt=dtc)
+
+
+def cu(t):
+    return t.cuda() if torch.is_tensor(t) else t
+
+
+@pytest.mark.parametrize("chunk,N,dtype", [(256, 128, torch.float16), (64, 64, torch.float16), (128, 128, torch.bfloat16)])
+def test_sub_ops_match_oracle(chunk, N, dtype):
+    from linquant_b200.kernels.mamba2 import ssd_combined as sc
+
+    k = make_case(N=N, chunk=chunk, dtype=dtype)
+    dA, dt = sc._quant_chunk_cumsum_fwd(cu(k["dt_raw"]), 1.0, cu(k["A_log"]), torch.tensor(1.0).cuda(), chunk, None, True)
+    assert rel_l2(dt, k["dt"]) < 1e-6 and (dA.cpu() - k["dA"]).abs().max() < 1e-5 * k["dA"].abs().max()
+    # the remaining ops are checked on the oracle's own dt / dA so that each is isolated
+    dtd, dAd = cu(k["dt"]), cu(k["dA"])
+    st_ref = so.chunk_state_value(k["x"], k["qB"], k["dt"], k["dA"], k["alpha"], k["sB"], k["state_scale"])
+    st = sc._quant_chunk_state_fwd_xfp_static_int8(cu(k["x"]), cu(k["qB"]), dtd, dAd, cu(k["alpha"]), cu(k["sB"]), cu(k["state_scale"]))
+    code_mismatch(st, st_ref, "value-side chunk states")
+    stk_ref = so.chunk_state_key(k["x"], k["x_scale"], k["Bm"], k["dt"], k["dA"], k["state_scale"], k["b_gate"])
+    stk = sc._chunk_state_keyside_fwd(cu(k["x"]), cu(k["x_scale"]), cu(k["Bm"]), dtd, dAd, cu(k["state_scale"]), cu(k["b_gate"]))
+    code_mismatch(stk, stk_ref, "key-side chunk states")
+    B, nc, H, P, Nn = st_ref.shape
+    sp_ref, fin_ref = so.state_passing(st_ref.reshape(B, nc, H, P * Nn), k["dA"][..., -1])
+    sp, fin = sc._fixedpoint_state_passing_fwd(cu(st_ref).reshape(B, nc, H, P * Nn), dAd[..., -1])
+    code_mismatch(sp, sp_ref, "passed states", budget=1e-3, max_step=2)
+    code_mismatch(fin, fin_ref, "final state", budget=1e-3, max_step=2)
+    cb_ref = so.bmm_chunk(k["qC"], k["sC"], k["qB"], k["sB"], chunk, k["cb_scale"])
+    cb = sc._quant_bmm_chunk_fwd(cu(k["qC"]), cu(k["sC"]), cu(k["qB"]), cu(k["sB"]), chunk, cu(k["cb_scale"]))
+    code_mismatch(cb, cb_ref, "CB codes")
+    cbk_ref = so.bmm_chunk(k["qC"], k["sC"], k["Bm"], k["sB"], chunk, k["cb_scale"], b_is_fp=True)
+    cbk = sc._quant_bmm_chunk_fwd(cu(k["qC"]), cu(k["sC"]), cu(k["Bm"]), cu(k["sB"]), chunk, cu(k["cb_scale"]), b_is_fp=True)
+    code_mismatch(cbk, cbk_ref, "CB codes (B quantised in-kernel)")
+    passed = sp_ref.reshape(B, nc, H, P, Nn)
+    out_ref = so.chunk_scan(cb_ref, k["x"], k["dt"], k["dA"], k["qC"], k["sC"], passed, k["D"], 1.0, k["state_scale"], k["cb_scale"])
+    out = sc._chunk_scan_v2(cu(cb_ref), cu(k["x"]), dtd, dAd, cu(k["qC"]), cu(k["sC"]), cu(passed), cu(k["D"]), torch.tensor(1.0).cuda(),
+                            cu(k["state_scale"]), cu(k["cb_scale"]))
+    assert out.dtype == torch.float16 and rel_l2(out, out_ref) < 2e-3, f"chunk scan rel-L2 {rel_l2(out, out_ref):.2e}"
+
+
+@pytest.mark.parametrize("keyside", [False, True])
+def test_combined_matches_oracle(keyside):
+    from linquant_b200.kernels.mamba2.ssd_combined import _quant_mamba_chunk_scan_combined_fwd as fwd
+
+    k = make_case(B=2, L=1024, H=8, chunk=256, seed=1)
+    kw = dict(dt_softplus=True, static_state_scale=k["state_scale"], static_cb_scale=k["cb_scale"], alpha_hp=k["alpha"],
+              bscale_g=k["sB"], keyside=keyside, x_scale_hp=k["x_scale"], b_fp=k["Bm"], b_gate_scale=k["b_gate"])
+    ref, _ = so.ssd_combined(k["x"], k["dt_raw"], 1.0, k["A_log"], 1.0, k["qB"], k["sB"], k["qC"], k["sC"], 256, k["D"], 1.0, **kw)
+    out, none = fwd(cu(k["x"]), cu(k["dt_raw"]), 1.0, cu(k["A_log"]), 1.0, cu(k["qB"]), cu(k["sB"]), cu(k["qC"]), cu(k["sC"]), 256,
+                    cu(k["D"]), 1.0, **{n: cu(v) for n, v in kw.items()})
+    assert none is None
+    err = rel_l2(out, ref)
+    assert err < 2e-3, f"combined SSD keyside={keyside}: rel-L2 {err:.2e}"
+
+
+def test_x_as_strided_view_of_xBC_and_prologue():
+    from linquant_b200.kernels.mamba2.chunk_state import _quant_chunk_state_fwd_xfp_static_int8 as cs
+    from linquant_b200.kernels.mamba2.fused_split_rotate_xBC import fused_split_rotate_quant_xBC
+
+    H, P, G, N, B, T = 4, 64, 1, 128, 2, 512
+    g = torch.Generator().manual_seed(3)
+    xBC = torch.randn(B, T, H * P + 2 * G * N, generator=g).half()
+    signs = torch.randint(0, 2, (G, N), generator=g).float() * 2 - 1
+    dq = torch.rand(G, N, generator=g) + 0.5
+    binv = torch.tensor([127.0 / 4.0])
+    cinv = torch.tensor([127.0 / 5.0])
+    for rs, db, dc in ((signs, dq, 1.0 / dq), (signs, None, None), (None, None, None)):
+        x_ref, qB_ref, qC_ref = so.split_rotate_quant(xBC, rs, H, G, N, P, binv, cinv, db, dc)
+        x, qB, qC = fused_split_rotate_quant_xBC(xBC.cuda(), cu(rs), H, G, N, P, binv.cuda(), cinv.cuda(), cu(db), cu(dc))
+        assert torch.equal(x.cpu(), x_ref) and x.stride(1) == H * P + 2 * G * N
+        code_mismatch(qB, qB_ref, "q_B codes")
+        code_mismatch(qC, qC_ref, "q_C codes")
+    k = make_case(B=B, L=T, H=H, N=N, chunk=256, seed=3)
+    st_ref = so.chunk_state_value(x_ref, k["qB"], k["dt"], k["dA"], k["alpha"], k["sB"], k["state_scale"])
+    st = cs(x, cu(k["qB"]), cu(k["dt"]), cu(k["dA"]), cu(k["alpha"]), cu(k["sB"]), cu(k["state_scale"]))
+    code_mismatch(st, st_ref, "chunk states from a strided x view")
+
+
+@pytest.mark.parametrize("D,dtype", [(128, torch.float16), (64, torch.bfloat16)])
+def test_kronecker_hadamard(D, dtype):
+    from linquant_b200.kernels.hadamard import hadamard_matrix, kronecker_hadamard_fwd
+
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(2, 100, 3, D, generator=g).to(dtype)
+    signs = torch.randint(0, 2, (3, D), generator=g).float() * 2 - 1
+    y = kronecker_hadamard_fwd(x.cuda(), signs.cuda(), 3)
+    ref = so.kronecker_hadamard(x, signs)
+    assert y.dtype == dtype and rel_l2(y, ref) < 1e-3
+    exact = (x.float() * signs) @ hadamard_matrix(D)
+    assert rel_l2(y, exact) < 1e-2
