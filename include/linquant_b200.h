@@ -181,6 +181,16 @@ int lq_ssd_chunk_cumsum(const lq_ssd_problem* p, lq_stream stream);
 /* Value-side chunk state (x gate-weighted and quantised with alpha_hp against INT8 B).
  * Replaces _quant_chunk_state_fwd_xfp_static_int8 (mamba2/chunk_state.py:24-349). */
 int lq_ssd_chunk_state_value(const lq_ssd_problem* p, lq_stream stream);
+/* The same op for hosts that cannot allocate device memory when they call it (a server that gave all of HBM to its own
+ * pools at start-up, a plugin under a runtime that forbids allocation after load). It has no counterpart in the
+ * reference. p->q_BT is ignored: the transposed copy of q_B goes to an 8 MiB array that is part of the library image
+ * (lq_ssd_static_scratch_bytes()), so B*L*G*N must not exceed that, else LQ_ERR_WORKSPACE. Inputs and the states
+ * output are still the caller's. The entry calls no allocating routine. The first call on each device looks up the
+ * array's device address (cudaGetSymbolAddress) with that device current: make that first call before any stream
+ * capture. All calls on a device share the one array and it keeps the previous call's contents (every byte that is
+ * read is rewritten first, nothing relies on zeros); two calls whose kernels overlap on the GPU race on it. */
+size_t lq_ssd_static_scratch_bytes(void);
+int lq_ssd_chunk_state_value_static(const lq_ssd_problem* p, lq_stream stream);
 /* Key-side chunk state (INT8 x against gate-weighted B quantised in-kernel).
  * Replaces _chunk_state_keyside_fwd (mamba2/chunk_state_keyside.py:17-424). */
 int lq_ssd_chunk_state_key(const lq_ssd_problem* p, lq_stream stream);

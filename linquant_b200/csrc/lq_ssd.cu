@@ -3,6 +3,7 @@
 //
 // Reference arithmetic: linquant/kernels/mamba2/{chunk_cumsum,chunk_state,chunk_state_keyside,state_passing,
 // bmm_chunk,chunk_scan_v2}.py (line ranges at each kernel).
+#include <mutex>
 #include <type_traits>
 
 #include "lq_common.cuh"
@@ -621,6 +622,48 @@ static int ssd_chunk_state(const lq_ssd_problem* p, bool keyside, lq_stream stre
   return check_launch("ssd_chunk_state_kernel");
 }
 extern "C" int lq_ssd_chunk_state_value(const lq_ssd_problem* p, lq_stream stream) { return ssd_chunk_state(p, false, stream); }
+
+// ---- value-side chunk state without any caller-provided or freshly allocated scratch
+// The transposed copy of q_B normally lives in a buffer the caller allocates (p->q_BT). Some hosts cannot do that at
+// call time: a serving process that handed all device memory to its own pools at start-up, or a plugin that runs
+// under a runtime which forbids allocation once the model is loaded. For them the scratch is this fixed array inside
+// the library image. Every GPU that loads the library holds these bytes until the process exits.
+namespace lq {
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;  // 8 MiB: B * L * ngroups * d_state may not exceed this
+static __device__ __align__(256) int8_t g_static_qbt[kStaticScratchBytes];
+static int8_t* g_static_qbt_addr[64];  // device address of the array, per device ordinal (the host-side name of a
+static std::mutex g_static_mu;         // __device__ array is only a handle: a kernel must be given this address)
+
+static int static_scratch(int8_t** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(LQ_ERR_LAUNCH, "static scratch: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return fail(LQ_ERR_UNSUPPORTED, "static scratch: device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (g_static_qbt_addr[dev] == nullptr) {
+    int8_t* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_static_qbt);
+    if (e != cudaSuccess || ptr == nullptr)
+      return fail(LQ_ERR_LAUNCH, "static scratch: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_static_qbt_addr[dev] = ptr;
+  }
+  *out = g_static_qbt_addr[dev];
+  return LQ_OK;
+}
+}  // namespace lq
+
+extern "C" size_t lq_ssd_static_scratch_bytes(void) { return lq::kStaticScratchBytes; }
+
+extern "C" int lq_ssd_chunk_state_value_static(const lq_ssd_problem* p, lq_stream stream) {
+  if (!p) return fail(LQ_ERR_NULL, "chunk_state_value_static: problem descriptor is null");
+  const size_t need = (size_t)p->B * (size_t)p->L * (size_t)p->G * (size_t)p->N;
+  if (p->B <= 0 || p->L <= 0 || p->G <= 0 || p->N <= 0 || need > lq::kStaticScratchBytes)
+    return fail(LQ_ERR_WORKSPACE, "chunk_state_value_static: B*L*G*N = %zu bytes of scratch needed, the built-in array holds %zu; "
+                "use lq_ssd_chunk_state_value with a caller-owned q_BT for larger problems", need, lq::kStaticScratchBytes);
+  lq_ssd_problem q = *p;
+  if (int e = lq::static_scratch(&q.q_BT)) return e;
+  return ssd_chunk_state(&q, false, stream);
+}
 extern "C" int lq_ssd_chunk_state_key(const lq_ssd_problem* p, lq_stream stream) { return ssd_chunk_state(p, true, stream); }
 
 extern "C" int lq_ssd_bmm_chunk(const lq_ssd_problem* p, int b_is_fp, lq_stream stream) {
