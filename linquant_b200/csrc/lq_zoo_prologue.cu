@@ -117,10 +117,15 @@ void fill_prologue_args(const lq_zoo_problem* p, const lq_zoo_workspace* ws, Pro
   a.scale = p->scale; a.eta = p->eta; a.qmax = p->qmax; a.skip_v = 0;
 }
 
+int run_prologue_linear_mma(const lq_zoo_problem* p, const PrologueArgs& a, cudaStream_t st);
+
 int run_prologue_linear(const lq_zoo_problem* p, const lq_zoo_workspace* ws, int skip_v, cudaStream_t st) {
   PrologueArgs a;
   fill_prologue_args(p, ws, a);
   a.skip_v = skip_v;
+  // the tensor-core rotation needs operands that are exact in the activation dtype: with a D_QK rescale ahead of the
+  // rotation the fp32 butterfly kernel below is used instead
+  if (p->dqk == nullptr) return run_prologue_linear_mma(p, a, st);
   if (p->act_dtype == LQ_F16) return launch_prologue<__half>(p, a, st);
   if (p->act_dtype == LQ_BF16) return launch_prologue<__nv_bfloat16>(p, a, st);
   return fail(LQ_ERR_UNSUPPORTED, "prologue: activation dtype must be f16 or bf16");
