@@ -45,98 +45,153 @@ __device__ __forceinline__ void mma_act<__nv_bfloat16>(float (&c)[4], uint32_t a
 }
 
 template <typename T, int K, int V, bool Q127>
-__global__ void __launch_bounds__(256, 2) zoo_prologue_linear_mma_kernel(PrologueArgs a, int chunks_per_cta) {
+__global__ void __launch_bounds__(256, 2) zoo_prologue_linear_mma_kernel(PrologueArgs a, int n_tiles) {
   constexpr int C = kChunk;
-  constexpr int KS = K / 16, NTK = K / 8;
+  constexpr int KS = K / 16;
+  constexpr int RAW_Q = C * K * 2, RAW_V = C * V * 2;
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  uint2* s_tab = reinterpret_cast<uint2*>(smem_raw);                    // [KS][NTK][32] B fragments of the Hadamard matrix
-  uint32_t(*s_kw)[17] = reinterpret_cast<uint32_t(*)[17]>(s_tab + KS * NTK * 32);
+  uint32_t(*s_kw)[17] = reinterpret_cast<uint32_t(*)[17]>(smem_raw);
   uint32_t(*s_vl)[17] = s_kw + K;
   uint32_t(*s_vw)[17] = s_vl + V;
-  float* s_sgn = reinterpret_cast<float*>(s_vw + V);                    // [K] sign * 1/sqrt(K)
-  float* s_ikw = s_sgn + K;                                             // [K] 1 / skw
-  float* s_ivl = s_ikw + K;                                             // [V]
-  float* s_ivw = s_ivl + V;                                             // [V]
-  float* s_gc = s_ivw + V;                                              // [C]
-  float* s_fk = s_gc + C;
-  float* s_fv = s_fk + C;
+  float* s_sgn = reinterpret_cast<float*>(s_vw + V);  // [K] sign * 1/sqrt(K)
+  float* s_ikw = s_sgn + K;                           // [K] 1 / skw
+  float* s_ivl = s_ikw + K;                           // [V]
+  float* s_ivw = s_ivl + V;                           // [V]
+  // raw activation tiles (cp.async): q,k of two chunks in flight, v of one; 16-byte pieces XOR-swizzled with bit 1
+  // of the token index so that the 128-bit fragment reads are conflict free
+  uint8_t* s_qk = reinterpret_cast<uint8_t*>(s_ivw + V);  // [2 buf][q|k][C][K*2]
+  uint8_t* s_v = s_qk + 4 * RAW_Q;                        // [C][V*2]
 
-  const int bh = blockIdx.y;
-  const int b = bh / a.H, h = bh % a.H;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, j = lane & 3;
   const bool rot = a.signs != nullptr;
-
-  // ---- per-CTA staging: Hadamard B-fragment table, channel scales
-  if (rot) {
-    const uint32_t one = std::is_same<T, __half>::value ? 0x3C00u : 0x3F80u;
-    for (int i = tid; i < KS * NTK * 32; i += 256) {
-      const int ln = i & 31, nt = (i >> 5) % NTK, s = (i >> 5) / NTK;
-      const int gg = ln >> 2, jj = ln & 3;
-      const int n = 32 * (nt >> 2) + 8 * (gg >> 1) + 2 * (nt & 3) + (gg & 1);
-      const int ch = 32 * (s >> 1) + 8 * jj + 4 * (s & 1);
-      uint32_t w[2];
-#pragma unroll
-      for (int hi = 0; hi < 2; ++hi) {
-        const uint32_t lo16 = one | ((__popc((ch + 2 * hi) & n) & 1) << 15);
-        const uint32_t hi16 = one | ((__popc((ch + 2 * hi + 1) & n) & 1) << 15);
-        w[hi] = lo16 | (hi16 << 16);
-      }
-      s_tab[i] = make_uint2(w[0], w[1]);
-    }
-  }
   const float norm = K == 64 ? 0.125f : 0.08838834764831845f;
-  for (int i = tid; i < K; i += 256) {
-    s_sgn[i] = rot ? a.signs[i] * norm : 1.0f;
-    s_ikw[i] = 1.0f / a.skw[h * K + i];
-  }
-  for (int i = tid; i < V; i += 256) {
-    s_ivl[i] = 1.0f / a.svl[h * V + i];
-    s_ivw[i] = 1.0f / a.svw[h * V + i];
-  }
-  const float inv_sq = 1.0f / a.sq[h], inv_sk = 1.0f / a.sk[h];
   const T* qp = reinterpret_cast<const T*>(a.q);
   const T* kp = reinterpret_cast<const T*>(a.k);
   const T* vp = reinterpret_cast<const T*>(a.v);
 
-  const int c_end = min(a.NT, (int)(blockIdx.x + 1) * chunks_per_cta);
-  for (int c = blockIdx.x * chunks_per_cta; c < c_end; ++c) {
-    const size_t tile = (size_t)bh * a.NT + c;
-    __syncthreads();  // previous chunk's transposer reads are done; staging is visible
-    if (warp == 0) {
-      if (a.g != nullptr) {
-        chunk_decay_scan(a.g, b, c, h, a.T, a.H, s_gc);
-      } else {
-        s_gc[lane] = 0.f;
-        s_gc[lane + 32] = 0.f;
-      }
-    }
-    __syncthreads();
-    if (tid < C) {
-      const float d = s_gc[C - 1] - s_gc[tid];
-      s_fk[tid] = a.g ? expf((1.0f - a.eta) * d) : 1.0f;
-      s_fv[tid] = a.g ? expf(a.eta * d) : 1.0f;
-      a.gc[tile * C + tid] = s_gc[tid];
-    }
-    __syncthreads();
+  // B fragments of the Sylvester matrix without a table. With input channel c = 32u + 8j + 4h + 2hi + e (k-step
+  // s = 2u + h, register hi, half e) and output channel n = 32(nt>>2) + 8(g>>1) + 2(nt&3) + (g&1), the sign
+  // (-1)^popc(c & n) splits into a per-lane part (e*g0 ^ j0*g1 ^ j1*g2), a part hi*(nt&1), and a part that depends
+  // on (s, nt) only. The last two are compile-time choices between the base register and its negation.
+  uint32_t hb0, hb0n;
+  {
+    const uint32_t one = std::is_same<T, __half>::value ? 0x3C00u : 0x3F80u;
+    const uint32_t L = ((j & 1) & ((g >> 1) & 1)) ^ (((j >> 1) & 1) & ((g >> 2) & 1));
+    hb0 = (one | (L << 15)) | ((one | ((L ^ (g & 1)) << 15)) << 16);
+    hb0n = hb0 ^ 0x80008000u;
+  }
 
-    const int mt = warp & 3;
-    const int ta = 16 * mt + 2 * g, tb = ta + 1;  // this thread's two tokens of the m-tile
-    const size_t rowa = (((size_t)b * a.T + (size_t)c * C + ta) * a.H + h);
-    // ---------------------------------------------------------------- q (warps 0-3) or k (warps 4-7)
+  // persistent CTAs: tile t = (batch, chunk, head) with the head fastest, strided by the grid: every CTA gets the same
+  // number of tiles to within one, and the CTAs in flight read all heads of the same tokens (adjacent in memory)
+  auto stage_qk = [&](int t, int buf) {
+    const int h = t % a.H, c = (t / a.H) % a.NT, b = t / (a.H * a.NT);
+    uint8_t* dst = s_qk + buf * 2 * RAW_Q;
+    const size_t row0 = ((size_t)b * a.T + (size_t)c * C) * a.H + h;
+    for (int i = tid; i < C * (K / 8); i += 256) {
+      const int tk = i / (K / 8), ch = i % (K / 8);
+      const int sw = (ch ^ (((tk >> 1) & 1) << 2)) << 4;
+      cp_async16(dst + tk * (K * 2) + sw, qp + (row0 + (size_t)tk * a.H) * K + 8 * ch);
+      cp_async16(dst + RAW_Q + tk * (K * 2) + sw, kp + (row0 + (size_t)tk * a.H) * K + 8 * ch);
+    }
+  };
+  auto stage_v = [&](int t) {
+    if (a.skip_v) return;
+    const int h = t % a.H, c = (t / a.H) % a.NT, b = t / (a.H * a.NT);
+    const size_t row0 = ((size_t)b * a.T + (size_t)c * C) * a.H + h;
+    for (int i = tid; i < C * (V / 8); i += 256) {
+      const int tk = i / (V / 8), ch = i % (V / 8);
+      cp_async16(s_v + tk * (V * 2) + ((ch ^ (((tk >> 1) & 1) << 2)) << 4), vp + (row0 + (size_t)tk * a.H) * V + 8 * ch);
+    }
+  };
+  auto load_g = [&](int t, float& g0, float& g1) {
+    if (a.g == nullptr) { g0 = g1 = 0.f; return; }
+    const int h = t % a.H, c = (t / a.H) % a.NT, b = t / (a.H * a.NT);
+    const size_t base = ((size_t)b * a.T + (size_t)c * C) * a.H + h;
+    g0 = __ldg(a.g + base + (size_t)lane * a.H);
+    g1 = __ldg(a.g + base + (size_t)(lane + 32) * a.H);
+  };
+  const int t_begin = blockIdx.x, t_step = gridDim.x;
+  if (t_begin >= n_tiles) return;
+  stage_qk(t_begin, 0);
+  stage_v(t_begin);
+  cp_async_commit();
+  float gn0, gn1;
+  load_g(t_begin, gn0, gn1);
+
+  const int mt = warp & 3;
+  const int ta = 16 * mt + 2 * g, tb = ta + 1;  // this thread's two tokens of the m-tile
+  const int swz = ((ta >> 1) & 1) << 2;         // tb shares bit 1 of the token index
+
+  int h_staged = -1;
+  float inv_sq = 1.f, inv_sk = 1.f;
+  for (int t = t_begin, it = 0; t < n_tiles; t += t_step, ++it) {
+    const int h = t % a.H, c = (t / a.H) % a.NT, b = t / (a.H * a.NT);
+    const size_t tile = ((size_t)b * a.H + h) * a.NT + c;
+    const int buf = it & 1;
+    const bool more = t + t_step < n_tiles;
+    cp_async_wait<0>();
+    __syncthreads();  // raw tiles of this chunk have landed; the previous chunk's compute and copy-out are done
+    if (more) {
+      stage_qk(t + t_step, buf ^ 1);
+      cp_async_commit();
+    }
+    if (h != h_staged) {  // per-head channel scales (uniform branch)
+      for (int i = tid; i < K; i += 256) {
+        s_sgn[i] = rot ? a.signs[i] * norm : 1.0f;
+        s_ikw[i] = 1.0f / a.skw[h * K + i];
+      }
+      for (int i = tid; i < V; i += 256) {
+        s_ivl[i] = 1.0f / a.svl[h * V + i];
+        s_ivw[i] = 1.0f / a.svw[h * V + i];
+      }
+      h_staged = h;
+      inv_sq = 1.0f / a.sq[h];
+      inv_sk = 1.0f / a.sk[h];
+      __syncthreads();
+    }
+    // ---- chunk-local cumulative log-decay, per warp (double accumulate), no shared memory
+    float gca, gcb, glast;
     {
-      const bool is_q = warp < 4;
-      const T* src = is_q ? qp : kp;
+      double x0 = (double)gn0, x1 = (double)gn1;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const double y0 = __shfl_up_sync(0xffffffffu, x0, d), y1 = __shfl_up_sync(0xffffffffu, x1, d);
+        if (lane >= d) { x0 += y0; x1 += y1; }
+      }
+      x1 += __shfl_sync(0xffffffffu, x0, 31);
+      const float f0 = (float)x0, f1 = (float)x1;
+      if (warp == 0) {
+        a.gc[tile * C + lane] = f0;
+        a.gc[tile * C + 32 + lane] = f1;
+      }
+      glast = __shfl_sync(0xffffffffu, f1, 31);
+      const float sel = (mt >> 1) ? f1 : f0;
+      gca = __shfl_sync(0xffffffffu, sel, ta & 31);
+      gcb = __shfl_sync(0xffffffffu, sel, tb & 31);
+      if (more) load_g(t + t_step, gn0, gn1);
+    }
+    const bool use_g = a.g != nullptr;
+    const float da = glast - gca, db = glast - gcb;
+    // ---------------------------------------------------------------- q then k: a warp owns an m-tile and one half
+    // of the output channels of both operands (equal work in every warp)
+#pragma unroll
+    for (int op = 0; op < 2; ++op) {
+      const bool is_q = op == 0;
+      const int half = warp >> 2;
+      const uint32_t hb1 = half ? hb0n : hb0, hb1n = half ? hb0 : hb0n;
+      const uint8_t* src = s_qk + buf * 2 * RAW_Q + (is_q ? 0 : RAW_Q);
       uint4 ra[K / 32], rb[K / 32];
 #pragma unroll
       for (int u = 0; u < K / 32; ++u) {
-        ra[u] = __ldg(reinterpret_cast<const uint4*>(src + rowa * K + 32 * u + 8 * j));
-        rb[u] = __ldg(reinterpret_cast<const uint4*>(src + (rowa + a.H) * K + 32 * u + 8 * j));
+        ra[u] = *reinterpret_cast<const uint4*>(src + ta * (K * 2) + (((4 * u + j) ^ swz) << 4));
+        rb[u] = *reinterpret_cast<const uint4*>(src + tb * (K * 2) + (((4 * u + j) ^ swz) << 4));
       }
-      const float fka = s_fk[ta], fkb = s_fk[tb];
+      const float fka = use_g ? expf((1.0f - a.eta) * da) : 1.0f, fkb = use_g ? expf((1.0f - a.eta) * db) : 1.0f;
       int8_t* rowmajor = (is_q ? a.qq : a.kl) + (tile * C) * K;
 #pragma unroll
-      for (int ng = 0; ng < K / 32; ++ng) {
+      for (int ngl = 0; ngl < K / 64; ++ngl) {
+        const int ng = half * (K / 64) + ngl;
         float va[8], vb[8];
         if (rot) {
           float acc[4][4];
@@ -149,8 +204,11 @@ __global__ void __launch_bounds__(256, 2) zoo_prologue_linear_mma_kernel(Prologu
             const uint32_t a0 = wa[2 * (s & 1)], a2 = wa[2 * (s & 1) + 1], a1 = wb[2 * (s & 1)], a3 = wb[2 * (s & 1) + 1];
 #pragma unroll
             for (int n4 = 0; n4 < 4; ++n4) {
-              const uint2 bf = s_tab[(s * NTK + 4 * ng + n4) * 32 + lane];
-              mma_act<T>(acc[n4], a0, a1, a2, a3, bf.x, bf.y);
+              // output n-tile nt = 4*ng + n4; its bits above n4 are ngl (compile time) and the warp's channel half
+              const int Uc = ((s & 1) & ((n4 >> 1) & 1)) ^ (K == 128 ? (((s >> 1) & 1) & (ngl & 1)) : 0);
+              const bool dep = K == 128 ? ((s >> 2) & 1) : ((s >> 1) & 1);
+              const uint32_t base = dep ? hb1 : hb0, neg = dep ? hb1n : hb0n;
+              mma_act<T>(acc[n4], a0, a1, a2, a3, Uc ? neg : base, (Uc ^ (n4 & 1)) ? neg : base);
             }
           }
           const float4 s0 = *reinterpret_cast<const float4*>(s_sgn + 32 * ng + 8 * j);
@@ -164,8 +222,8 @@ __global__ void __launch_bounds__(256, 2) zoo_prologue_linear_mma_kernel(Prologu
               vb[2 * n4 + e] = Act<T>::round(__fmul_rn(acc[n4][2 + e], sg[2 * n4 + e]));
             }
         } else {
-          Act<T>::unpack8(ra[ng], va);
-          Act<T>::unpack8(rb[ng], vb);
+          Act<T>::unpack8(half ? ra[K / 64 + ngl] : ra[ngl], va);
+          Act<T>::unpack8(half ? rb[K / 64 + ngl] : rb[ngl], vb);
         }
         const int cb = 32 * ng + 8 * j;
         int ca[8], cc[8];
@@ -200,13 +258,13 @@ __global__ void __launch_bounds__(256, 2) zoo_prologue_linear_mma_kernel(Prologu
     // ---------------------------------------------------------------- v: eight warps, m-tile x channel half
     if (!a.skip_v) {
       const int half = warp >> 2;
-      const float fva = s_fv[ta], fvb = s_fv[tb];
+      const float fva = use_g ? expf(a.eta * da) : 1.0f, fvb = use_g ? expf(a.eta * db) : 1.0f;
 #pragma unroll
       for (int uu = 0; uu < V / 64; ++uu) {
         const int cb = 32 * (half * (V / 64) + uu) + 8 * j;
         float va[8], vb[8];
-        Act<T>::unpack8(__ldg(reinterpret_cast<const uint4*>(vp + rowa * V + cb)), va);
-        Act<T>::unpack8(__ldg(reinterpret_cast<const uint4*>(vp + (rowa + a.H) * V + cb)), vb);
+        Act<T>::unpack8(*reinterpret_cast<const uint4*>(s_v + ta * (V * 2) + (((cb >> 3) ^ swz) << 4)), va);
+        Act<T>::unpack8(*reinterpret_cast<const uint4*>(s_v + tb * (V * 2) + (((cb >> 3) ^ swz) << 4)), vb);
         const float4 l0 = *reinterpret_cast<const float4*>(s_ivl + cb), l1 = *reinterpret_cast<const float4*>(s_ivl + cb + 4);
         const float4 w0 = *reinterpret_cast<const float4*>(s_ivw + cb), w1 = *reinterpret_cast<const float4*>(s_ivw + cb + 4);
         const float il[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
@@ -222,6 +280,10 @@ __global__ void __launch_bounds__(256, 2) zoo_prologue_linear_mma_kernel(Prologu
       }
     }
     __syncthreads();
+    if (more) {  // the single v buffer is free again
+      stage_v(t + t_step);
+      cp_async_commit();
+    }
     uint32_t* kw_out = reinterpret_cast<uint32_t*>(a.kwT + tile * (size_t)(K * C));
     for (int i = tid; i < K * 16; i += 256) kw_out[i] = s_kw[i >> 4][i & 15];
     if (!a.skip_v) {
@@ -237,17 +299,24 @@ __global__ void __launch_bounds__(256, 2) zoo_prologue_linear_mma_kernel(Prologu
 
 template <typename T, int K, int V>
 static int launch_mma(const lq_zoo_problem* p, const PrologueArgs& a, cudaStream_t st) {
-  const int cpb = (a.NT % 4 == 0 && (long long)a.NT * p->B * p->H >= 4096) ? 4 : 1;
-  dim3 grid((a.NT + cpb - 1) / cpb, p->B * p->H), block(256);
-  const size_t smem = sizeof(uint2) * (K / 16) * (K / 8) * 32 + sizeof(uint32_t) * 17 * (K + 2 * V) +
-                      sizeof(float) * (2 * K + 2 * V + 3 * 64);
+  const int tiles = a.NT * p->B * p->H;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // a grid that is a multiple of the head count keeps every CTA on one head (its scales are staged once)
+  int ctas = 2 * sms;
+  if (p->H <= ctas) ctas = (ctas / p->H) * p->H;
+  dim3 grid(tiles < ctas ? tiles : ctas), block(256);
+  const size_t smem = sizeof(uint32_t) * 17 * (K + 2 * V) + sizeof(float) * (2 * K + 2 * V) + (size_t)(4 * 64 * K * 2 + 64 * V * 2);
   cudaError_t e;
   if (p->qmax == 127.f) {
     e = cudaFuncSetAttribute(zoo_prologue_linear_mma_kernel<T, K, V, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) zoo_prologue_linear_mma_kernel<T, K, V, true><<<grid, block, smem, st>>>(a, cpb);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(zoo_prologue_linear_mma_kernel<T, K, V, true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (e == cudaSuccess) zoo_prologue_linear_mma_kernel<T, K, V, true><<<grid, block, smem, st>>>(a, tiles);
   } else {
     e = cudaFuncSetAttribute(zoo_prologue_linear_mma_kernel<T, K, V, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) zoo_prologue_linear_mma_kernel<T, K, V, false><<<grid, block, smem, st>>>(a, cpb);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(zoo_prologue_linear_mma_kernel<T, K, V, false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (e == cudaSuccess) zoo_prologue_linear_mma_kernel<T, K, V, false><<<grid, block, smem, st>>>(a, tiles);
   }
   if (e != cudaSuccess) return fail(LQ_ERR_LAUNCH, "prologue: cannot opt in to %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
   return check_launch("zoo_prologue_linear_mma_kernel");
