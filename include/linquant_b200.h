@@ -91,6 +91,7 @@ typedef struct {
   void* amat;  /* [BH,NT,C,C] fp16 intra-chunk matrix (diagonal decay) */
   float* genv; /* [BH,NT,C]   log of the scalar write envelope (diagonal decay) */
   float* gcl;  /* [BH,NT,K]   cumulative log-decay at the chunk end (diagonal decay) */
+  int* status; /* one word, zeroed by the whole-call entries; a kernel whose bounded device-side wait expired sets it */
 } lq_zoo_workspace;
 int lq_zoo_carve_workspace(const lq_zoo_problem* p, int delta_family, void* workspace, size_t workspace_bytes,
                            lq_zoo_workspace* out);

@@ -33,7 +33,7 @@ class ZooProblem(C.Structure):
 
 
 class ZooWorkspace(C.Structure):
-    _fields_ = [(n, C.c_void_p) for n in ("qq", "kl", "kwT", "vlT", "vwT", "hT", "wq", "gc", "u", "fw", "amat", "genv", "gcl")]
+    _fields_ = [(n, C.c_void_p) for n in ("qq", "kl", "kwT", "vlT", "vwT", "hT", "wq", "gc", "u", "fw", "amat", "genv", "gcl", "status")]
 
 
 class LinQuantError(RuntimeError):
@@ -105,6 +105,7 @@ _WS_LAYOUT = {  # name -> (torch dtype, lambda(BH,NT,C,K,V) -> shape)
     "amat": (torch.float16, lambda BH, NT, Cc, K, V: (BH, NT, Cc, Cc)),
     "gcl": (torch.float32, lambda BH, NT, Cc, K, V: (BH, NT, K)),
     "genv": (torch.float32, lambda BH, NT, Cc, K, V: (BH, NT, Cc)),
+    "status": (torch.int32, lambda BH, NT, Cc, K, V: (1,)),
 }
 
 
@@ -122,6 +123,12 @@ class Workspace:
         self.desc = ZooWorkspace()
         check(lib().lq_zoo_carve_workspace(C.byref(prob), int(delta), C.c_void_p(self.base), C.c_size_t(n),
                                            C.byref(self.desc)), "carve workspace")
+        self.view("status").zero_()
+
+    def check_status(self):
+        """After the stream has drained: raises if a kernel's bounded device-side wait expired."""
+        if int(self.view("status").item()) != 0:
+            raise LinQuantError("a device-side wait timed out (status word set by the kernel)")
 
     def view(self, name):
         p = getattr(self.desc, name)
@@ -139,4 +146,13 @@ class Workspace:
             numel *= s
         start = p - self.base + self.off0
         raw = self.buf[start:start + numel * torch.empty((), dtype=dt).element_size()]
-        return raw.view(dt).view(shape)
+        t = raw.view(dt).view(shape)
+        if name == "kl":  # rows are stored in MMA-column order: undo the permutation (copy) for inspection
+            tok = torch.arange(shape[2], device=t.device)
+            pos = (tok & ~15) | (((tok >> 1) & 1) << 3) | (((tok >> 2) & 3) << 1) | (tok & 1)
+            t = t[:, :, pos]
+        elif name == "hT":
+            v = torch.arange(shape[2], device=t.device)
+            pos = (v & ~31) | (((v >> 1) & 3) << 3) | (((v >> 3) & 3) << 1) | (v & 1)
+            t = t[:, :, pos]
+        return t

@@ -75,6 +75,7 @@ static size_t carve(const lq_zoo_problem* p, int delta, void* ws, lq_zoo_workspa
   w.amat = p->decay == LQ_DECAY_DIAGONAL ? cv.take<uint16_t>(BH * NT * C * C) : nullptr;
   w.genv = p->decay == LQ_DECAY_DIAGONAL ? cv.take<float>(BH * NT * C) : nullptr;
   w.gcl = p->decay == LQ_DECAY_DIAGONAL ? cv.take<float>(BH * NT * K) : nullptr;
+  w.status = cv.take<int>(64);
   if (out) *out = w;
   return (cv.off + 255) & ~size_t(255);
 }
@@ -111,6 +112,7 @@ extern "C" int lq_simple_gla_fwd(const lq_zoo_problem* p, void* workspace, size_
   lq_zoo_workspace ws;
   if (int e = lq_zoo_carve_workspace(p, 0, workspace, workspace_bytes, &ws)) return e;
   cudaStream_t st = (cudaStream_t)stream;
+  cudaMemsetAsync(ws.status, 0, sizeof(int), st);
   if (int e = lq::run_prologue_linear(p, &ws, 0, st)) return e;
   if (int e = lq::run_state_linear(p, &ws, st)) return e;
   return lq::run_output_scalar(p, &ws, p->svl, st);
@@ -121,6 +123,7 @@ extern "C" int lq_delta_fwd(const lq_zoo_problem* p, void* workspace, size_t wor
   lq_zoo_workspace ws;
   if (int e = lq_zoo_carve_workspace(p, 1, workspace, workspace_bytes, &ws)) return e;
   cudaStream_t st = (cudaStream_t)stream;
+  cudaMemsetAsync(ws.status, 0, sizeof(int), st);
   if (int e = lq::run_prologue_delta(p, &ws, st)) return e;
   if (int e = lq::run_state_delta(p, &ws, st)) return e;
   return lq::run_output_scalar(p, &ws, p->sel, st);

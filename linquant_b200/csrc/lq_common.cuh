@@ -29,6 +29,18 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
   return __byte_perm(lo, hi, 0x5410);
 }
 
+// ---- row orders of the two tiles that are B operands of the output contractions
+// The k_local tile and the stored-state tile are laid out so that MMA column n of the output kernel is simply row n
+// of the tile, while a thread's accumulator fragment still covers four consecutive tokens (k_local) or eight
+// consecutive value channels (state). Within each group the row index is a fixed bit permutation of the token /
+// channel index.
+__device__ __host__ __forceinline__ int kl_row_of_token(int t) {  // low 4 bits [j1 j0 h e] -> [h j1 j0 e]
+  return (t & ~15) | (((t >> 1) & 1) << 3) | (((t >> 2) & 3) << 1) | (t & 1);
+}
+__device__ __host__ __forceinline__ int state_row_of_channel(int v) {  // low 5 bits [j1 j0 n1 n0 e] -> [n1 n0 j1 j0 e]
+  return (v & ~31) | (((v >> 1) & 3) << 3) | (((v >> 3) & 3) << 1) | (v & 1);
+}
+
 // ---- activation dtype traits
 template <typename T>
 struct Act;

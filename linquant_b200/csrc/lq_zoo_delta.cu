@@ -280,7 +280,7 @@ __global__ void __launch_bounds__(128) zoo_state_delta_kernel(DeltaStateArgs a) 
           cd[2 * nt + 1] = q8(carry[mt][nt][2 * hi + 1], iss_r[i], 127.f);
         }
         uint8_t* sdst = s_h + swz_row<K>(vl, kown >> 4) + (kown & 15);
-        int8_t* gdst = hc + (size_t)(v0 + vl) * K + kown;
+        int8_t* gdst = hc + (size_t)state_row_of_channel(v0 + vl) * K + kown;
         if (NTK == 4) {
           const uint2 w = make_uint2(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4 % (2 * NTK)], cd[5 % (2 * NTK)],
                                                                             cd[6 % (2 * NTK)], cd[7 % (2 * NTK)]));

@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(128) zoo_output_scalar_kernel(OutputArgs a) {
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         int acc[4] = {0, 0, 0, 0};
-        const int tok_row = 16 * ks + 4 * (g >> 1) + 2 * half + (g & 1);
+        const int tok_row = 16 * ks + 8 * half + g;  // row n of the k_local tile is MMA column n
 #pragma unroll
         for (int kk = 0; kk < KK; ++kk) {
           const uint4 bk = *reinterpret_cast<const uint4*>(s_k + swz_k<K>(tok_row, 4 * kk + j));
@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(128) zoo_output_scalar_kernel(OutputArgs a) {
 #pragma unroll
     for (int n4 = 0; n4 < 4; ++n4) {
       const int nt = 4 * ng + n4;
-      const int vr = 32 * ng + 8 * (g >> 1) + 2 * n4 + (g & 1);
+      const int vr = 8 * nt + g;  // row n of the stored-state tile is MMA column n
       int acc[4] = {0, 0, 0, 0};
 #pragma unroll
       for (int kk = 0; kk < KK; ++kk) {
@@ -223,8 +223,13 @@ static int launch_output(const lq_zoo_problem* p, const OutputArgs& a, cudaStrea
 int validate_zoo_problem(const lq_zoo_problem* p, bool delta, bool diagonal);
 
 // k_local codes and local value codes/scales are parameters so the delta family can pass (Hw, E) tiles.
+int run_output_tc(const lq_zoo_problem* p, const lq_zoo_workspace* ws, const float* s_local_value, cudaStream_t st);
+
 int run_output_scalar(const lq_zoo_problem* p, const lq_zoo_workspace* ws, const float* s_local_value,
                       cudaStream_t st) {
+  // K = 128 with none / scalar decay runs on the tcgen05 + TMA kernel; other shapes and the diagonal-decay variant
+  // (A precomputed, no q.k^T product) on the warp-level MMA kernel below
+  if (p->K == 128 && p->decay != LQ_DECAY_DIAGONAL && ws->status != nullptr) return run_output_tc(p, ws, s_local_value, st);
   OutputArgs a;
   a.qq = ws->qq; a.kl = ws->kl; a.vlT = ws->vlT; a.hT = ws->hT; a.gc = ws->gc;
   a.sq = p->sq; a.sk = p->sk; a.svl = s_local_value; a.ss = p->sstate; a.o = p->o;

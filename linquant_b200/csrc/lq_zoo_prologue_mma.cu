@@ -240,8 +240,9 @@ __global__ void __launch_bounds__(256, 2) zoo_prologue_linear_mma_kernel(Prologu
             cc[i] = code32<Q127>(vb[i], inv_sk, a.qmax);
           }
         }
-        *reinterpret_cast<uint2*>(rowmajor + (size_t)ta * K + cb) = make_uint2(pack4s(ca, 0), pack4s(ca, 4));
-        *reinterpret_cast<uint2*>(rowmajor + (size_t)tb * K + cb) = make_uint2(pack4s(cc, 0), pack4s(cc, 4));
+        const int pa_ = is_q ? ta : kl_row_of_token(ta), pb_ = is_q ? tb : kl_row_of_token(tb);
+        *reinterpret_cast<uint2*>(rowmajor + (size_t)pa_ * K + cb) = make_uint2(pack4s(ca, 0), pack4s(ca, 4));
+        *reinterpret_cast<uint2*>(rowmajor + (size_t)pb_ * K + cb) = make_uint2(pack4s(cc, 0), pack4s(cc, 4));
         if (!is_q) {
           const float4 i0 = *reinterpret_cast<const float4*>(s_ikw + cb);
           const float4 i1 = *reinterpret_cast<const float4*>(s_ikw + cb + 4);

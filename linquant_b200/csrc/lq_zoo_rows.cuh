@@ -111,7 +111,7 @@ __device__ __forceinline__ void prologue_qk_rows(const PrologueArgs& a, int b, i
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) cd[j] = q8(x[j], inv_sk, a.qmax);
-      *reinterpret_cast<uint2*>(a.kl + orow) =
+      *reinterpret_cast<uint2*>(a.kl + (tile * C + kl_row_of_token(t)) * K + 8 * r) =
           make_uint2(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4], cd[5], cd[6], cd[7]));
       const float fk = s_fk[t];
 #pragma unroll

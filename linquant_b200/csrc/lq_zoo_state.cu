@@ -91,9 +91,9 @@ __global__ void __launch_bounds__(128) zoo_state_linear_kernel(StateArgs a) {
         cb[i] = q8(carry_b[i], iss_b, 127.f);
       }
       int8_t* hc = hT + (size_t)c * V * K;
-      *reinterpret_cast<uint2*>(hc + va * K + k0 + 8 * j) =
+      *reinterpret_cast<uint2*>(hc + state_row_of_channel(va) * K + k0 + 8 * j) =
           make_uint2(pack4(ca[0], ca[1], ca[2], ca[3]), pack4(ca[4], ca[5], ca[6], ca[7]));
-      *reinterpret_cast<uint2*>(hc + vb * K + k0 + 8 * j) =
+      *reinterpret_cast<uint2*>(hc + state_row_of_channel(vb) * K + k0 + 8 * j) =
           make_uint2(pack4(cb[0], cb[1], cb[2], cb[3]), pack4(cb[4], cb[5], cb[6], cb[7]));
     }
 

@@ -28,6 +28,7 @@ def run_case(q, k, v, g, beta, *, policy="kernel_static", bits=8, eta=1.0, sigma
                                output_final_state=True, rot=signs, dqk=None if dqk is None else dqk.to(dev), _debug=dbg)
     torch.cuda.synchronize()
     ws = dbg["workspace"]
+    ws.check_status()
     Bq, Tq, Hq, _ = q.shape
     NT = Tq // 64
     tile = lambda name: ws.view(name).view(Bq, Hq, NT, *ws.view(name).shape[2:])  # noqa: E731

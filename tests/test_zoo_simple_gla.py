@@ -28,6 +28,7 @@ def run_case(q, k, v, g, *, policy="kernel_static", bits=8, eta=1.0, rot=False, 
                                     rot=signs, dqk=None if dqk is None else dqk.to(dev), _debug=dbg)
     torch.cuda.synchronize()
     ws = dbg["workspace"]
+    ws.check_status()
     Bq, Tq, Hq, _ = q.shape
     Vd = v.shape[-1]
     NT = Tq // 64
