@@ -187,11 +187,14 @@ def run_ours(args):
     ho = torch.empty(v.shape, dtype=v.dtype).pin_memory()
     dq, dk, dv, dg = (torch.empty_like(t, device=dev) for t in (hq, hk, hv, hg))
 
+    from linquant_b200.host_pipeline import SimpleGlaHostPipeline
+
+    pipe = SimpleGlaHostPipeline(B, T, H, K, V, q.dtype, dev)
+    del dq, dk, dv, dg
+
     def e2e_step():
-        dq.copy_(hq, non_blocking=True); dk.copy_(hk, non_blocking=True)
-        dv.copy_(hv, non_blocking=True); dg.copy_(hg, non_blocking=True)
-        out, _ = chunk_simple_gla_int8(dq, dk, dv, dg, scales, eta=cfg["eta"], chunk_size=cfg["chunk"], rot=signs_d)
-        ho.copy_(out, non_blocking=True)
+        # public host-buffer call: per batch element H2D -> prologue/state/output -> D2H, copies overlapped with kernels
+        pipe(hq, hk, hv, hg, scales, ho, eta=cfg["eta"], chunk_size=cfg["chunk"], rot=signs_d)
 
     for _ in range(2):
         e2e_step()

@@ -69,6 +69,7 @@ typedef struct {
   const float *sw, *sel, *sew;                     /* delta-family extras (null for the linear family) */
   void* o;                /* [B,T,H,V] */
   float* final_state;     /* [B,H,K,V] fp32 carry after the last chunk, or null */
+  const float* initial_state; /* [B,H,K,V] fp32 carry entering the first chunk (linear family), or null = zero */
 } lq_zoo_problem;
 
 /* Bytes of workspace the zoo entries need for this problem (a host-side computation). */

@@ -31,14 +31,20 @@ __global__ void ssd_cumsum_kernel(lq_ssd_problem p) {
   const float bias = p.dt_bias ? p.dt_bias[h] : 0.f;
   double run = 0.0;
   const size_t obase = (((size_t)b * p.H + h) * NC + c) * C;
-  for (int t = 0; t < C; ++t) {
-    float x = __fmul_rn(d_scale, p.dt_in[((size_t)b * p.L + (size_t)c * C + t) * p.H + h]);
-    if (p.dt_bias) x = __fadd_rn(x, bias);
-    if (p.dt_softplus) x = x > 20.f ? x : logf(__fadd_rn(1.0f, expf(x)));
-    x = fminf(fmaxf(x, p.dt_min), p.dt_max);
-    p.dt[obase + t] = x;
-    run += (double)__fmul_rn(x, A);
-    p.dA[obase + t] = (float)run;
+  for (int t0 = 0; t0 < C; t0 += 16) {
+    float raw[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) raw[i] = __ldg(p.dt_in + ((size_t)b * p.L + (size_t)c * C + t0 + i) * p.H + h);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float x = __fmul_rn(d_scale, raw[i]);
+      if (p.dt_bias) x = __fadd_rn(x, bias);
+      if (p.dt_softplus) x = x > 20.f ? x : logf(__fadd_rn(1.0f, expf(x)));
+      x = fminf(fmaxf(x, p.dt_min), p.dt_max);
+      p.dt[obase + t0 + i] = x;
+      run += (double)__fmul_rn(x, A);
+      p.dA[obase + t0 + i] = (float)run;
+    }
   }
 }
 
@@ -446,8 +452,8 @@ __global__ void __launch_bounds__(256) ssd_chunk_scan_kernel(lq_ssd_problem p) {
           const int k = k0 + e;
           const float dk = s_dA[k], dtk = s_dt[k];
           const float ca = (float)(int8_t)((wa >> (8 * e)) & 0xff), cb = (float)(int8_t)((wb >> (8 * e)) & 0xff);
-          va[e] = (ma >= k) ? __fmul_rn(__fmul_rn(__fmul_rn(ca, Scb), expf(__fsub_rn(dAa, dk))), dtk) : 0.f;
-          vb[e] = (mb >= k) ? __fmul_rn(__fmul_rn(__fmul_rn(cb, Scb), expf(__fsub_rn(dAb, dk))), dtk) : 0.f;
+          va[e] = (ma >= k) ? __fmul_rn(__fmul_rn(__fmul_rn(ca, Scb), __expf(__fsub_rn(dAa, dk))), dtk) : 0.f;
+          vb[e] = (mb >= k) ? __fmul_rn(__fmul_rn(__fmul_rn(cb, Scb), __expf(__fsub_rn(dAb, dk))), dtk) : 0.f;
         }
         af[2 * hi] = Act<__half>::pack2(va[0], va[1]);
         af[2 * hi + 1] = Act<__half>::pack2(vb[0], vb[1]);

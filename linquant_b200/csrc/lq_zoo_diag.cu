@@ -56,20 +56,33 @@ __global__ void __launch_bounds__(256) zoo_diag_rows_kernel(DiagArgs a) {
   const size_t tile = (size_t)bh * a.NT + c;
   const float e_hw = (1.f - a.sigma) * a.tau;
 
-  if (tid < K) {
-    double acc = 0.0;
-    float f = 0.f;
-    for (int t = 0; t < C; ++t) {
-      acc += (double)a.g[(((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K + tid];
-      f = (float)acc;
-      s_gc[t * LD + tid] = f;
-      a.gc[(tile * C + t) * K + tid] = f;
-    }
-    a.gcl[tile * K + tid] = f;
-  } else if (DELTA && tid >= 128 && tid < 128 + C) {
+  // stage the raw log-decays of the chunk (coalesced), then one thread per channel scans them in double
+  for (int i = tid; i < C * (K / 4); i += 256) {
+    const int t = i / (K / 4), c4 = i % (K / 4);
+    *reinterpret_cast<float4*>(s_gc + t * LD + 4 * c4) =
+        __ldg(reinterpret_cast<const float4*>(a.g + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K) + c4);
+  }
+  if (DELTA && tid >= 128 && tid < 128 + C) {
     const int t = tid - 128;
     const float bt = a.beta[((size_t)b * a.T + (size_t)c * C + t) * a.H + h];
     s_hw[t] = pow_exact01(bt, e_hw);
+  }
+  __syncthreads();
+  if (tid < K) {
+    double acc = 0.0;
+    float f = 0.f;
+#pragma unroll 8
+    for (int t = 0; t < C; ++t) {
+      acc += (double)s_gc[t * LD + tid];
+      f = (float)acc;
+      s_gc[t * LD + tid] = f;
+    }
+    a.gcl[tile * K + tid] = f;
+  }
+  __syncthreads();
+  for (int i = tid; i < C * (K / 4); i += 256) {
+    const int t = i / (K / 4), c4 = i % (K / 4);
+    reinterpret_cast<float4*>(a.gc + (tile * C + t) * K)[c4] = *reinterpret_cast<const float4*>(s_gc + t * LD + 4 * c4);
   }
   __syncthreads();
   for (int tt = 0; tt < 8; ++tt) {
@@ -381,7 +394,7 @@ __global__ void __launch_bounds__(256) zoo_kda_wy_kernel(DiagArgs a) {
     const int l8 = tid & 7;
     float sum = 0.f;
     for (int n = l8; n < K; n += 8) {
-      const float w = expf(s_gc[i * LD + n] - s_gc[jj * LD + n]);
+      const float w = __expf(s_gc[i * LD + n] - s_gc[jj * LD + n]);
       sum = fmaf(s_kf[i * LD + n] * s_kf[jj * LD + n], w, sum);
     }
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);

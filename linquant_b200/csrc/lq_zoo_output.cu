@@ -247,5 +247,5 @@ int run_output_scalar(const lq_zoo_problem* p, const lq_zoo_workspace* ws, const
 extern "C" int lq_zoo_output_scalar(const lq_zoo_problem* p, const lq_zoo_workspace* ws, lq_stream stream) {
   if (int e = lq::validate_zoo_problem(p, p && p->beta != nullptr, p && p->decay == LQ_DECAY_DIAGONAL)) return e;
   if (!ws) return lq::fail(LQ_ERR_NULL, "output: workspace descriptor is null");
-  return lq::run_output_scalar(p, ws, p->sel ? p->sel : p->svl, (cudaStream_t)stream);
+  return lq::run_output_scalar(p, ws, p->beta != nullptr ? p->sel : p->svl, (cudaStream_t)stream);  // delta family: E scales
 }

@@ -21,6 +21,7 @@ struct StateArgs {
   const float* gcl;  // diagonal decay: [BH,NT,K] cumulative log-decay at the chunk end, per key channel
   int8_t* hT;
   float* final_state;  // [B,H,K,V] or null
+  const float* initial_state;  // [B,H,K,V] or null
   int H, NT, use_g;
 };
 
@@ -56,6 +57,14 @@ __global__ void __launch_bounds__(128) zoo_state_linear_kernel(StateArgs a) {
   float carry_a[8], carry_b[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) carry_a[i] = carry_b[i] = 0.f;
+  if (a.initial_state != nullptr) {
+    const float* is = a.initial_state + (size_t)bh * K * V;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      carry_a[i] = is[(size_t)(k0 + 8 * j + i) * V + va];
+      carry_b[i] = is[(size_t)(k0 + 8 * j + i) * V + vb];
+    }
+  }
 
   uint4 A_lo, A_hi, Bq[4];
   float glast = 0.f;
@@ -146,7 +155,7 @@ int validate_zoo_problem(const lq_zoo_problem* p, bool delta, bool diagonal);
 int run_state_linear(const lq_zoo_problem* p, const lq_zoo_workspace* ws, cudaStream_t st) {
   StateArgs a;
   a.kwT = ws->kwT; a.vwT = ws->vwT; a.gc = ws->gc; a.skw = p->skw; a.svw = p->svw; a.ss = p->sstate;
-  a.hT = ws->hT; a.final_state = p->final_state; a.H = p->H; a.NT = p->T / p->chunk;
+  a.hT = ws->hT; a.final_state = p->final_state; a.initial_state = p->initial_state; a.H = p->H; a.NT = p->T / p->chunk;
   a.use_g = p->g != nullptr;
   a.gcl = ws->gcl;
   const bool diag = p->decay == LQ_DECAY_DIAGONAL;

@@ -35,7 +35,7 @@ def _sylvester(n):
 
 
 def make_problem(q, k, v, g, beta, scales, *, decay, eta, sigma, tau, scale, chunk_size, bits, out, final_state,
-                 rot_signs, dqk, keep):
+                 rot_signs, dqk, keep, initial_state=None):
     """Builds the C descriptor. ``keep`` collects every temporary tensor whose storage the descriptor points to."""
     B, T, H, K = q.shape
     V = v.shape[-1]
@@ -60,6 +60,7 @@ def make_problem(q, k, v, g, beta, scales, *, decay, eta, sigma, tau, scale, chu
         put(name, _cabi.f32c(scales.get(key), dev))
     put("o", out)
     put("final_state", final_state)
+    put("initial_state", None if initial_state is None else initial_state.to(device=dev, dtype=torch.float32).contiguous())
     return P
 
 

@@ -287,7 +287,7 @@ def _cell_delta(Q, Kc, Vc, gcc, bt, S, carry, o):
 
 def chunk_prefill(q, k, v, g, beta, *, family, decay, scale, qz, rot_qk=None, rot_v=None, eta=0.0, sigma=1.0,
                   tau=1.0, chunk=64, read_post=True, storage="rotated", out_dtype=None, act_dtype=None,
-                  return_final_state=False):
+                  return_final_state=False, initial_state=None):
     """Chunkwise forward of one (family, decay) cell on CPU in float64 (reference.py:24-73).
 
     q,k [B,T,H,K]; v [B,T,H,V]; g [B,T,H] (scalar decay), [B,T,H,K] (diagonal) or None; beta [B,T,H] or None.
@@ -316,6 +316,8 @@ def chunk_prefill(q, k, v, g, beta, *, family, decay, scale, qz, rot_qk=None, ro
                 unrot=rot_v.T if (rot_v is not None and storage == "canonical") else None)
     S = q.new_zeros(B, H, K, Vt.shape[-1])
     carry = None
+    if initial_state is not None:  # fp32 carry handed over from an earlier segment: the first chunk reads its INT8 copy
+        S, carry = qz.pass_state(S, initial_state.to(F64), 1.0, 0.0)
     out = torch.empty_like(Vt)
     cell = _cell_linear if family == "linear" else _cell_delta
     for c in range(nc):

@@ -109,3 +109,42 @@ def test_shape_errors():
     sc["kw"] = torch.ones(2, 32, device="cuda")
     with pytest.raises(NotImplementedError):
         chunk_simple_gla_int8(q.cuda(), k.cuda(), v.cuda(), g.cuda(), sc)
+
+
+def test_initial_state_and_segmented_sequence():
+    """A sequence cut into segments (what the sequence-parallel mode does across GPUs): the carry handed from one
+    segment to the next reproduces the unsplit run up to fp32 rounding of the carry."""
+    from linquant_b200 import seqpar
+    from linquant_b200.kernels.zoo.simple_gla import chunk_simple_gla_int8
+
+    q, k, v, g, _ = zoo_inputs(2, 512, 3, 128, 128, decay="scalar", dtype=torch.bfloat16, seed=7)
+    orc = OracleRun(q, k, v, g, None, family="linear", decay="scalar", policy="kernel_pt")
+    ref = orc.run()
+    dev = "cuda"
+    sc = orc.scales(dev)
+    qd, kd, vd, gd = q.to(dev), k.to(dev), v.to(dev), g.to(dev)
+    whole, fs = chunk_simple_gla_int8(qd, kd, vd, gd, sc, output_final_state=True)
+    # two calls chained through initial_state
+    a, sa = chunk_simple_gla_int8(qd[:, :256], kd[:, :256], vd[:, :256], gd[:, :256], sc, output_final_state=True)
+    b, sb = chunk_simple_gla_int8(qd[:, 256:], kd[:, 256:], vd[:, 256:], gd[:, 256:], sc, output_final_state=True,
+                                  initial_state=sa)
+    assert torch.equal(torch.cat([a, b], 1), whole) and torch.equal(sb, fs), "chained calls reproduce the unsplit call exactly"
+    # four segments with the exclusive scan of the carries
+    seg = seqpar.segmented_on_one_device(qd, kd, vd, gd, sc, 4)
+    assert rel_l2(seg, whole) <= 1e-3 and rel_l2(seg, ref) <= 2e-3, f"{rel_l2(seg, whole):.2e} {rel_l2(seg, ref):.2e}"
+
+
+def test_host_pipeline_matches_device_call():
+    from linquant_b200.host_pipeline import SimpleGlaHostPipeline
+    from linquant_b200.kernels.zoo.simple_gla import chunk_simple_gla_int8
+
+    q, k, v, g, _ = zoo_inputs(3, 256, 2, 128, 128, decay="scalar", dtype=torch.bfloat16, seed=8)
+    orc = OracleRun(q, k, v, g, None, family="linear", decay="scalar", policy="kernel_pt")
+    sc = orc.scales("cuda")
+    want, _ = chunk_simple_gla_int8(q.cuda(), k.cuda(), v.cuda(), g.cuda(), sc)
+    pipe = SimpleGlaHostPipeline(3, 256, 2, 128, 128, torch.bfloat16, "cuda")
+    ho = torch.empty(v.shape, dtype=v.dtype).pin_memory()
+    for _ in range(2):
+        pipe(q.pin_memory(), k.pin_memory(), v.pin_memory(), g.pin_memory(), sc, ho)
+        torch.cuda.synchronize()
+        assert torch.equal(ho, want.cpu())
