@@ -1,9 +1,14 @@
 """CPU restatement of the SSDi8-lineage Mamba-2 SSD ops (TEST INFRASTRUCTURE, not a product path).
 
-PARITY UNPINNED: the reference has no test, golden vector or CPU implementation for these ops (its versions are
-Triton kernels under ``linquant/kernels/mamba2/`` which need a GPU, and the SSDi8 project they descend from is an
-un-fetched submodule). Every function below is therefore a line-by-line restatement, in fp32 torch on the CPU, of
-the arithmetic written in the Triton source it cites; nothing independent pins it.
+PARITY PINNED on outputs of the reference itself: the reference implements these ops only as Triton kernels (under
+``linquant/kernels/mamba2/`` and ``linquant/kernels/hadamard.py``; the SSDi8 project they descend from is an
+un-fetched submodule) and holds no test or golden vector for them, so the fixtures ``tests/golden/ssd_*.npz`` were
+produced by running those kernels, unmodified, on the CPU with Triton's interpreter
+(``tests/golden/make_golden_ssd.py``). ``tests/test_ssd_oracle_golden.py`` holds every function below to them:
+integer results (chunk states, fixed-point recurrence, CB, rotated B/C codes) and the Hadamard outputs bit for bit,
+the fp32 prefix sums and the fp16 scan output to summation-order tolerance. What the interpreter cannot pin is the
+GPU's own transcendental rounding (exp, log); each function is a line-by-line restatement, in fp32 torch on the
+CPU, of the arithmetic written in the Triton source it cites.
 
   chunk_cumsum        <- mamba2/chunk_cumsum.py:15-100
   chunk_state_value   <- mamba2/chunk_state.py:24-349          (value-side absorption, half-away rounding)

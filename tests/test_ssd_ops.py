@@ -138,3 +138,83 @@ def test_kronecker_hadamard(D, dtype):
     assert y.dtype == dtype and rel_l2(y, ref) < 1e-3
     exact = (x.float() * signs) @ hadamard_matrix(D)
     assert rel_l2(y, exact) < 1e-2
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# CUDA ops against the golden vectors written by the reference's own Triton kernels (tests/golden/ssd_*.npz)
+def _gold(name):
+    import os
+
+    import numpy as np
+
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", name + ".npz"))
+    return {k: torch.from_numpy(np.ascontiguousarray(z[k])) for k in z.files}
+
+
+@pytest.mark.parametrize("name", ["ssd_value_n128", "ssd_key_n64"])
+def test_ops_match_reference_kernel_golden(name):
+    from linquant_b200.kernels.mamba2 import ssd_combined as sc
+
+    g = _gold(name)
+    key, C = bool(g["keyside"]), int(g["chunk"])
+    one = torch.ones(1).cuda()
+    dA, dt = sc._quant_chunk_cumsum_fwd(cu(g["dt_raw"]), one, cu(g["A_log"]), one, C, cu(g["dt_bias"]), True)
+    assert float((dt.cpu() - g["dt"]).abs().max()) <= 1e-6
+    assert float((dA.cpu() - g["dA"]).abs().max()) <= 2e-4
+    dtd, dAd = cu(g["dt"]), cu(g["dA"])
+    if key:
+        st = sc._chunk_state_keyside_fwd(cu(g["x"]), cu(g["x_scale_hp"]), cu(g["b_fp"]), dtd, dAd, cu(g["state_scale"]),
+                                         cu(g["b_gate_scale"]))
+    else:
+        st = sc._quant_chunk_state_fwd_xfp_static_int8(cu(g["x"]), cu(g["q_B"]), dtd, dAd, cu(g["alpha_hp"]), cu(g["B_scale"]),
+                                                       cu(g["state_scale"]))
+    code_mismatch(st, g["states"], f"{name}: chunk states vs the reference kernel")
+    B, NC, H, P, N = g["states"].shape
+    sp, fin = sc._fixedpoint_state_passing_fwd(cu(g["states"]).reshape(B, NC, H, P * N), dAd[..., -1])
+    code_mismatch(sp, g["passed"], f"{name}: entering states vs the reference kernel", budget=1e-3, max_step=2)
+    code_mismatch(fin, g["final"], f"{name}: final state vs the reference kernel", budget=1e-3, max_step=2)
+    cb = sc._quant_bmm_chunk_fwd(cu(g["q_C"]), cu(g["C_scale"]), cu(g["b_fp"] if key else g["q_B"]), cu(g["B_scale"]), C,
+                                 cu(g["cb_scale"]), b_is_fp=key)
+    code_mismatch(cb, g["cb"], f"{name}: CB codes vs the reference kernel")
+    out = sc._chunk_scan_v2(cu(g["cb"]), cu(g["x"]), dtd, dAd, cu(g["q_C"]), cu(g["C_scale"]),
+                            cu(g["passed"]).reshape(B, NC, H, P, N), cu(g["D"]), one, cu(g["state_scale"]), cu(g["cb_scale"]))
+    err = rel_l2(out, g["out"])
+    assert err <= 2e-3, f"{name}: chunk scan rel-L2 {err:.2e} vs the reference kernel"
+    full, _ = sc._quant_mamba_chunk_scan_combined_fwd(
+        cu(g["x"]), cu(g["dt_raw"]), one, cu(g["A_log"]), one, cu(g["q_B"]), cu(g["B_scale"]), cu(g["q_C"]), cu(g["C_scale"]), C,
+        cu(g["D"]), one, dt_bias=cu(g["dt_bias"]), dt_softplus=True, static_state_scale=cu(g["state_scale"]),
+        static_cb_scale=cu(g["cb_scale"]), alpha_hp=cu(g["alpha_hp"]), bscale_g=cu(g["B_scale"]), keyside=key,
+        x_scale_hp=cu(g["x_scale_hp"]), b_fp=cu(g["b_fp"]), b_gate_scale=cu(g["b_gate_scale"]))
+    err = rel_l2(full, g["out"])
+    assert err <= 2e-3, f"{name}: combined forward rel-L2 {err:.2e} vs the reference kernels"
+
+
+@pytest.mark.parametrize("name", ["ssd_split_rotate", "ssd_split_rotate_dqk"])
+def test_split_rotate_matches_reference_kernel_golden(name):
+    from linquant_b200.kernels.mamba2.fused_split_rotate_xBC import fused_split_rotate_quant_xBC
+
+    g = _gold(name)
+    x, qB, qC = fused_split_rotate_quant_xBC(cu(g["xBC"]), cu(g["signs"]), int(g["nheads"]), int(g["G"]), int(g["N"]),
+                                             int(g["headdim"]), cu(g["B_inv"]), cu(g["C_inv"]), cu(g.get("dqk_b")),
+                                             cu(g.get("dqk_c")))
+    assert torch.equal(x.cpu().contiguous(), g["x_view"])
+    code_mismatch(qB, g["q_B"], f"{name}: q_B vs the reference kernel")
+    code_mismatch(qC, g["q_C"], f"{name}: q_C vs the reference kernel")
+
+
+@pytest.mark.parametrize("name", ["ssd_kron_hadamard_f16", "ssd_kron_hadamard_bf16"])
+def test_kronecker_hadamard_matches_reference_kernel_golden(name):
+    import os
+
+    import numpy as np
+
+    from linquant_b200.kernels.hadamard import kronecker_hadamard_fwd
+
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", name + ".npz"))
+    bf = bool(z["bf16"])
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).view(torch.bfloat16) if bf else torch.from_numpy(np.ascontiguousarray(a))  # noqa: E731
+    x, s, y = t(z["x"]), t(z["signs"]), t(z["y"])
+    got = kronecker_hadamard_fwd(x.cuda(), s.cuda(), x.shape[2]).cpu()
+    assert got.dtype == y.dtype
+    frac = float((got != y).float().mean())
+    assert frac <= 1e-3 and float((got.float() - y.float()).abs().max()) <= 0.04, f"{name}: {frac:.2e} of outputs differ"
