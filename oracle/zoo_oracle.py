@@ -15,6 +15,9 @@ chunk by chunk, which is what the bit-exact parity tests compare against.
 
 Parity pin: ``tests/golden/`` holds outputs of the reference itself (generated where the reference is
 importable, by ``tests/golden/make_golden.py``); ``tests/test_oracle_golden.py`` checks this file against them.
+A second pin comes from the reference's INT8 Triton kernels themselves, run on the CPU with Triton's interpreter
+(``tests/golden/make_golden_zoo_kernels.py`` -> ``zoo_kernel_*.npz``): ``tests/test_zoo_kernel_golden.py`` holds
+the kernel-lineage emulation here to their outputs and final carries.
 """
 
 from __future__ import annotations
