@@ -37,6 +37,11 @@ ALGO_BYTES_PER_HEAD_TOKEN = {
     "state": 2 * 128 + 4.0 / 64 + 128 * 128 / 64,
     "output": 3 * 128 + 128 * 128 / 64 + 4 + 128 * 2,
 }
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel at this workload, from ncu captures of
+# `python bench.py --kernels-only --steps 1 --warmup 3` (summaries under profiles/). Outputs that are still in the
+# 126 MB L2 when the kernel ends are not counted by those counters, which is why traffic can sit below the
+# algorithmic bytes.
+NCU_DRAM_BYTES_PER_LAUNCH = {"prologue": 328.1e6, "state": 96.3e6, "output": None}
 
 
 def measured_peak():
@@ -182,6 +187,16 @@ def run_ours(args):
     ms = t0.elapsed_time(t1)
     stage_ms = [sum(e[i].elapsed_time(e[i + 1]) for e in evs) / args.steps for i in range(3)]
 
+    if args.kernels_only:
+        if sampler:
+            sampler.stop(world)
+        if rank == 0:
+            print(json.dumps({"kernels_only": True, "ms_per_step": ms / args.steps,
+                              "stage_us": [round(1e3 * t, 2) for t in stage_ms]}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
     # end to end through the public call with host buffers: H2D of q,k,v,g from pinned memory, the op, D2H of o
     hq, hk, hv, hg = (x[n].pin_memory() for n in ("q", "k", "v", "g"))
     ho = torch.empty(v.shape, dtype=v.dtype).pin_memory()
@@ -236,7 +251,8 @@ def run_ours(args):
                 "d2h_bytes_per_step": ho.numel() * ho.element_size()},
         "gpu_launches": 3 * args.steps,
         "roofline": {"bound": "hbm", "kernel": names[dom], "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": NCU_DRAM_BYTES_PER_LAUNCH[names[dom]],
+                     "algorithmic_bytes": ALGO_BYTES_PER_HEAD_TOKEN[names[dom]] * head_tokens,
                      "stage_us": {n: round(1e3 * t, 2) for n, t in zip(names, stage_ms)},
                      "path_achieved": path_gbs, "path_frac": path_gbs / peak},
         "clocks": clocks,
@@ -308,6 +324,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="device-resident stage loop only (no host-buffer leg, no CPU baseline): the command profiled by ncu")
     args = ap.parse_args()
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:  # plain `python bench.py --gpus N`: become N ranks
         os.execv(sys.executable, [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",

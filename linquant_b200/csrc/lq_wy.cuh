@@ -49,26 +49,32 @@ __device__ __forceinline__ void wy_product(float (&acc)[NT][4], const float* s_T
 
 
 // T = (I + G)^-1 for a strictly lower-triangular 64x64 G (both [64][68] fp32 in shared memory), 256 threads.
-// Column `col` is built by four lanes, each owning every fourth row of the column in registers and a quarter of
-// each row's dot product (reference: torch.linalg.solve_triangular, zoo/gated_delta_rule.py:40-41).
+// Forward substitution, one column of T per group of four lanes, in its right-looking form: as soon as T[i][col]
+// is known, every later row's running sum  sum_j G[row][j] T[j][col]  takes its term j = i. Lane r of the group
+// keeps the sums of rows 4m + r in registers, so a step is one shuffle (the owner of row i publishes the value)
+// followed by independent multiply-adds; nothing is reduced across lanes. Columns 8w .. 8w+7 belong to warp w and
+// are zero above row 8w, so the warp skips those steps (reference: torch.linalg.solve_triangular,
+// zoo/gated_delta_rule.py:40-41).
 __device__ __forceinline__ void wy_solve(const float* s_G, float* s_T) {
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31;
   const int col = tid >> 2, r = tid & 3;
-  float tc[16];
+  const int first = 8 * (tid >> 5);
+  float part[16];
 #pragma unroll
-  for (int m = 0; m < 16; ++m) tc[m] = 0.f;
+  for (int m = 0; m < 16; ++m) part[m] = 0.f;
 #pragma unroll
   for (int i = 0; i < 64; ++i) {
-    float part = 0.f;
-#pragma unroll
-    for (int m = 0; m <= (i - 1) / 4 && i > 0; ++m) {
-      if (4 * m + r < i) part = fmaf(s_G[i * 68 + 4 * m + r], tc[m], part);
+    if (i < first) {  // warp-uniform
+      if (r == 0) s_T[i * 68 + col] = 0.f;
+      continue;
     }
-    part += __shfl_xor_sync(0xffffffffu, part, 1);
-    part += __shfl_xor_sync(0xffffffffu, part, 2);
-    const float val = (i == col ? 1.f : 0.f) - part;
-    if ((i & 3) == r) tc[i >> 2] = val;
+    float val = (i == col ? 1.f : 0.f) - part[i >> 2];
+    val = __shfl_sync(0xffffffffu, val, (lane & ~3) | (i & 3));
     if (r == 0) s_T[i * 68 + col] = val;
+#pragma unroll
+    for (int m = i >> 2; m < 16; ++m) {
+      if (m > (i >> 2) || r > (i & 3)) part[m] = fmaf(s_G[(4 * m + r) * 68 + i], val, part[m]);
+    }
   }
 }
 
