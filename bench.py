@@ -38,10 +38,10 @@ ALGO_BYTES_PER_HEAD_TOKEN = {
     "output": 3 * 128 + 128 * 128 / 64 + 4 + 128 * 2,
 }
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel at this workload, from ncu captures of
-# `python bench.py --kernels-only --steps 1 --warmup 3` (summaries under profiles/). Outputs that are still in the
+# `python bench.py --kernels-only --steps 1 --warmup 3` (profiles/simple_gla_cfg1_tc_kernels.md). Outputs that are still in the
 # 126 MB L2 when the kernel ends are not counted by those counters, which is why traffic can sit below the
 # algorithmic bytes.
-NCU_DRAM_BYTES_PER_LAUNCH = {"prologue": 328.1e6, "state": 96.3e6, "output": None}
+NCU_DRAM_BYTES_PER_LAUNCH = {"prologue": 326.1e6, "state": 97.1e6, "output": 210.8e6}
 
 
 def measured_peak():
