@@ -140,12 +140,21 @@ __global__ void __launch_bounds__(128) ssd_chunk_state_kernel(lq_ssd_problem p) 
   __shared__ __align__(16) uint32_t s_x[2][P][LDW];
   __shared__ __align__(16) uint32_t s_b[KEYSIDE ? 2 : 1][KEYSIDE ? N : 1][LDW];
   __shared__ float s_gate[256];
+  extern __shared__ __align__(16) uint8_t s_raw[];  // [C][128 B]: the chunk's x rows as stored, fetched up front
 
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int C = p.chunk, NC = p.L / C, grp = h / (p.H / p.G);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, j = lane & 3;
 
+  {
+    const T* xrow = reinterpret_cast<const T*>(p.x) + (size_t)b * p.x_stride_b + (size_t)h * p.x_stride_h;
+    for (int i = tid; i < C * 8; i += 128) {
+      const int row = i >> 3, ch = i & 7;
+      cp_async16(s_raw + row * 128 + ch * 16, xrow + (size_t)(c * C + row) * p.x_stride_t + 8 * ch);
+    }
+    cp_async_commit();
+  }
   const size_t cbase = (((size_t)b * p.H + h) * NC + c) * C;
   {
     const float last = p.dA[cbase + C - 1];
@@ -164,9 +173,9 @@ __global__ void __launch_bounds__(128) ssd_chunk_state_kernel(lq_ssd_problem p) 
 #pragma unroll
     for (int q = 0; q < N / 32; ++q) binv[q] = 127.0f / bgs[(64 * (q >> 1) + 2 * lane + (q & 1)) * p.bgs_stride[3]];
   }
+  cp_async_wait<0>();
   __syncthreads();
 
-  const T* xp = reinterpret_cast<const T*>(p.x) + (size_t)b * p.x_stride_b + (size_t)h * p.x_stride_h + 2 * lane;
   const T* bp = reinterpret_cast<const T*>(p.b_fp);
   const int8_t* qbt = KEYSIDE ? nullptr : p.q_BT + ((((size_t)b * NC + c) * p.G + grp) * N) * C;
 
@@ -181,7 +190,7 @@ __global__ void __launch_bounds__(128) ssd_chunk_state_kernel(lq_ssd_problem p) 
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int t = 64 * s + 4 * tg + i;
-        const uint32_t raw = *reinterpret_cast<const uint32_t*>(xp + (size_t)(c * C + t) * p.x_stride_t);
+        const uint32_t raw = *reinterpret_cast<const uint32_t*>(s_raw + t * 128 + 4 * lane);
         float x0, x1;
         if (sizeof(T) == 2 && std::is_same<T, __half>::value) {
           const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&raw));
@@ -368,6 +377,7 @@ __global__ void __launch_bounds__(256) ssd_chunk_scan_kernel(lq_ssd_problem p) {
   uint8_t* s_x = smem;                                   // [C][128 B] fp16, 16-byte chunk index ^ (row & 7)
   float* s_dA = reinterpret_cast<float*>(smem + (size_t)C * 128);
   float* s_dt = s_dA + C;
+  float* s_tab = s_dt + C;                               // [8 warps][C] below-diagonal decay table of the warp's m-tile
 
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int grp = h / (p.H / p.G);
@@ -435,33 +445,60 @@ __global__ void __launch_bounds__(256) ssd_chunk_scan_kernel(lq_ssd_problem p) {
         }
       }
     }
-    // ---- causal fp16 product
+    // ---- causal fp16 product. Within a k16 step the reduction index is permuted so that lane j owns four
+    // consecutive tokens 4j .. 4j+3 (one 32-bit load of CB codes per row); the x rows handed to ldmatrix follow
+    // the same permutation. Tiles strictly below the diagonal take the decay from a per-warp table
+    //   tab[k] = Scb * exp(dA[16 mt] - dA[k]) * dt[k]   (k < 16 mt, exponent <= 0)
+    // times the row factor exp(dA[m] - dA[16 mt]) (<= 1); the diagonal tile evaluates exp(dA[m] - dA[k]) directly
+    // under the causal mask.
     float conv[8][4];
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) conv[nt][0] = conv[nt][1] = conv[nt][2] = conv[nt][3] = 0.f;
+    float* tab = s_tab + warp * C;
+    const float dref = s_dA[16 * mt];
+    __syncwarp();
+    for (int k = lane; k < 16 * mt; k += 32) tab[k] = __fmul_rn(__fmul_rn(Scb, __expf(__fsub_rn(dref, s_dA[k]))), s_dt[k]);
+    __syncwarp();
+    const float ea = __expf(__fsub_rn(dAa, dref)), eb = __expf(__fsub_rn(dAb, dref));
+    const int mi = lane >> 3, rr = lane & 7;
+    const int xrow = 4 * (rr >> 1) + 2 * (mi & 1) + (rr & 1);  // ldmatrix row of this lane within a k16 step
+    const int8_t* cba = cbp + (size_t)ma * C + 4 * j;
+    const int8_t* cbb = cbp + (size_t)mb * C + 4 * j;
+    uint32_t wa_n = __ldg(reinterpret_cast<const uint32_t*>(cba)), wb_n = __ldg(reinterpret_cast<const uint32_t*>(cbb));
     for (int ks = 0; ks <= mt; ++ks) {
       uint32_t af[4];
+      const int k0 = 16 * ks + 4 * j;
+      const uint32_t wa = wa_n, wb = wb_n;
+      if (ks < mt) {  // CB codes of the next step, in flight during this one
+        wa_n = __ldg(reinterpret_cast<const uint32_t*>(cba + 16 * (ks + 1)));
+        wb_n = __ldg(reinterpret_cast<const uint32_t*>(cbb + 16 * (ks + 1)));
+      }
+      float va[4], vb[4];
+      if (ks < mt) {
+        const float4 t4 = *reinterpret_cast<const float4*>(tab + k0);
+        const float tv[4] = {t4.x, t4.y, t4.z, t4.w};
 #pragma unroll
-      for (int hi = 0; hi < 2; ++hi) {
-        const int k0 = 16 * ks + 8 * hi + 2 * j;
-        const uint16_t wa = *reinterpret_cast<const uint16_t*>(cbp + (size_t)ma * C + k0);
-        const uint16_t wb = *reinterpret_cast<const uint16_t*>(cbp + (size_t)mb * C + k0);
-        float va[2], vb[2];
+        for (int e = 0; e < 4; ++e) {
+          va[e] = __fmul_rn(__fmul_rn((float)(int8_t)(wa >> (8 * e)), ea), tv[e]);
+          vb[e] = __fmul_rn(__fmul_rn((float)(int8_t)(wb >> (8 * e)), eb), tv[e]);
+        }
+      } else {
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
+        for (int e = 0; e < 4; ++e) {
           const int k = k0 + e;
           const float dk = s_dA[k], dtk = s_dt[k];
-          const float ca = (float)(int8_t)((wa >> (8 * e)) & 0xff), cb = (float)(int8_t)((wb >> (8 * e)) & 0xff);
+          const float ca = (float)(int8_t)(wa >> (8 * e)), cb = (float)(int8_t)(wb >> (8 * e));
           va[e] = (ma >= k) ? __fmul_rn(__fmul_rn(__fmul_rn(ca, Scb), __expf(__fsub_rn(dAa, dk))), dtk) : 0.f;
           vb[e] = (mb >= k) ? __fmul_rn(__fmul_rn(__fmul_rn(cb, Scb), __expf(__fsub_rn(dAb, dk))), dtk) : 0.f;
         }
-        af[2 * hi] = Act<__half>::pack2(va[0], va[1]);
-        af[2 * hi + 1] = Act<__half>::pack2(vb[0], vb[1]);
       }
+      af[0] = Act<__half>::pack2(va[0], va[1]);
+      af[1] = Act<__half>::pack2(vb[0], vb[1]);
+      af[2] = Act<__half>::pack2(va[2], va[3]);
+      af[3] = Act<__half>::pack2(vb[2], vb[3]);
 #pragma unroll
       for (int n2 = 0; n2 < 4; ++n2) {
-        const int mi = lane >> 3;
-        const int row = 16 * ks + 8 * (mi & 1) + (lane & 7);
+        const int row = 16 * ks + xrow;
         const int ch = 2 * n2 + (mi >> 1);
         uint32_t r[4];
         ldmatrix_x4_trans(r, s_x + row * 128 + ((ch ^ (row & 7)) << 4));
@@ -565,14 +602,20 @@ static int ssd_check_pn(const lq_ssd_problem* p, const char* what) {
   return LQ_OK;
 }
 
+template <typename T, int N, bool KEYSIDE>
+static void launch_chunk_state_T(const lq_ssd_problem* p, dim3 grid, cudaStream_t st) {
+  const int smem = p->chunk * 128;  // static + dynamic shared memory exceeds 48 KB on the key side: opt in
+  cudaFuncSetAttribute(ssd_chunk_state_kernel<T, N, KEYSIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+  ssd_chunk_state_kernel<T, N, KEYSIDE><<<grid, 128, smem, st>>>(*p);
+}
 template <bool KEYSIDE>
 static void launch_chunk_state(const lq_ssd_problem* p, dim3 grid, cudaStream_t st) {
   if (p->x_dtype == LQ_F16) {
-    if (p->N == 128) ssd_chunk_state_kernel<__half, 128, KEYSIDE><<<grid, 128, 0, st>>>(*p);
-    else ssd_chunk_state_kernel<__half, 64, KEYSIDE><<<grid, 128, 0, st>>>(*p);
+    if (p->N == 128) launch_chunk_state_T<__half, 128, KEYSIDE>(p, grid, st);
+    else launch_chunk_state_T<__half, 64, KEYSIDE>(p, grid, st);
   } else {
-    if (p->N == 128) ssd_chunk_state_kernel<__nv_bfloat16, 128, KEYSIDE><<<grid, 128, 0, st>>>(*p);
-    else ssd_chunk_state_kernel<__nv_bfloat16, 64, KEYSIDE><<<grid, 128, 0, st>>>(*p);
+    if (p->N == 128) launch_chunk_state_T<__nv_bfloat16, 128, KEYSIDE>(p, grid, st);
+    else launch_chunk_state_T<__nv_bfloat16, 64, KEYSIDE>(p, grid, st);
   }
 }
 template <bool B_IS_FP>
@@ -687,7 +730,7 @@ extern "C" int lq_ssd_bmm_chunk(const lq_ssd_problem* p, int b_is_fp, lq_stream 
 
 template <typename T, int N>
 static int launch_scan(const lq_ssd_problem* p, cudaStream_t st) {
-  const size_t smem = (size_t)p->chunk * 128 + 2 * sizeof(float) * p->chunk;
+  const size_t smem = (size_t)p->chunk * 128 + 10 * sizeof(float) * p->chunk;
   dim3 grid(p->L / p->chunk, p->H, p->B);
   ssd_chunk_scan_kernel<T, N><<<grid, 256, smem, st>>>(*p);
   return check_launch("ssd_chunk_scan_kernel");

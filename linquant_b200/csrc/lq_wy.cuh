@@ -47,6 +47,33 @@ __device__ __forceinline__ void wy_product(float (&acc)[NT][4], const float* s_T
   }
 }
 
+// Same product with a general fp32 right factor: both factors split into a TF32 "big" part and a TF32 remainder,
+// three MMAs per tile (small*big, big*small, big*big), products good to about 2^-21 relative.
+template <int NT>
+__device__ __forceinline__ void wy_product_split(float (&acc)[NT][4], const float* s_T, const float* s_cw, const float* s_B,
+                                                 int LDB, int mt, int n0, int g, int j) {
+  const int ia = 16 * mt + g, ib = ia + 8;
+  for (int kk = 0; kk < 2 * mt + 2; ++kk) {
+    const int c0 = 8 * kk + j, c1 = c0 + 4;
+    const float x[4] = {s_T[ia * 68 + c0] * s_cw[c0], s_T[ib * 68 + c0] * s_cw[c0], s_T[ia * 68 + c1] * s_cw[c1],
+                        s_T[ib * 68 + c1] * s_cw[c1]};
+    uint32_t big[4], sml[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      big[i] = tf32_rna(x[i]);
+      sml[i] = tf32_rna(x[i] - __uint_as_float(big[i]));
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const float y0 = s_B[c0 * LDB + n0 + 8 * nt + g], y1 = s_B[c1 * LDB + n0 + 8 * nt + g];
+      const uint32_t b0 = tf32_rna(y0), b1 = tf32_rna(y1);
+      const uint32_t s0 = tf32_rna(y0 - __uint_as_float(b0)), s1 = tf32_rna(y1 - __uint_as_float(b1));
+      mma_tf32(acc[nt], sml[0], sml[1], sml[2], sml[3], b0, b1);
+      mma_tf32(acc[nt], big[0], big[1], big[2], big[3], s0, s1);
+      mma_tf32(acc[nt], big[0], big[1], big[2], big[3], b0, b1);
+    }
+  }
+}
 
 // T = (I + G)^-1 for a strictly lower-triangular 64x64 G (both [64][68] fp32 in shared memory), 256 threads.
 // Forward substitution, one column of T per group of four lanes, in its right-looking form: as soon as T[i][col]

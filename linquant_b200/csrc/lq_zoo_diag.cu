@@ -338,17 +338,54 @@ __global__ void __launch_bounds__(256) zoo_diag_amat_kernel(DiagArgs a) {
 }
 
 // ------------------------------------------------------------------------------------------------ KDA WY prep
+// Gram matrix G[i][j] = beta_i^sigma beta_j^(1-sigma) sum_n k[i,n] k[j,n] exp(gc[i,n] - gc[j,n]), i > j, in 16-token
+// secondary chunks like the A matrix: inside a diagonal block every (i, j, n) takes its own exp (exponent <= 0);
+// for block row I against the earlier tokens the operands are re-scaled around the anchor row 16 I,
+//   kd[i,n] = k[i,n] exp(gc[i,n] - gc[16I,n]),  ke[j,n] = k[j,n] exp(gc[16I,n] - gc[j,n])   (both factors <= 1),
+// and contracted on the tensor cores as 3xTF32 (big*big + big*small + small*big), which keeps fp32-grade products.
+// W and U are T diag(beta^sigma) times k exp(gc) (3xTF32, both operands split) and times v (exact in TF32).
+template <typename T, int K>
+__device__ __forceinline__ void kda_scaled_rows(const DiagArgs& a, int b, int c, int h, const float* s_gc, float* s_x,
+                                                int anchor_row, int first_row, int nrows, int dst_row, bool toward_anchor) {
+  // rows [first_row, first_row + nrows) of k, times exp(gc[row] - gc[anchor]) (toward_anchor) or exp(gc[anchor] - gc[row]),
+  // or times exp(gc[row]) when anchor_row < 0; written as fp32 to s_x rows dst_row ...
+  constexpr int C = 64, LD = K + 4, LPR = K / 8;
+  const T* kp = reinterpret_cast<const T*>(a.k);
+  for (int i = threadIdx.x; i < nrows * LPR; i += 256) {
+    const int rr = i / LPR, seg = i % LPR;
+    const int t = first_row + rr;
+    float x[8];
+    Act<T>::unpack8(__ldg(reinterpret_cast<const uint4*>(kp + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K + 8 * seg)), x);
+    const float4 g0 = *reinterpret_cast<const float4*>(s_gc + t * LD + 8 * seg);
+    const float4 g1 = *reinterpret_cast<const float4*>(s_gc + t * LD + 8 * seg + 4);
+    float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+    if (anchor_row >= 0) {
+      const float4 a0 = *reinterpret_cast<const float4*>(s_gc + anchor_row * LD + 8 * seg);
+      const float4 a1 = *reinterpret_cast<const float4*>(s_gc + anchor_row * LD + 8 * seg + 4);
+      const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) gv[e] = toward_anchor ? __fsub_rn(gv[e], av[e]) : __fsub_rn(av[e], gv[e]);
+    }
+    float y[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = __fmul_rn(x[e], anchor_row >= 0 ? __expf(gv[e]) : expf(gv[e]));
+    *reinterpret_cast<float4*>(s_x + (dst_row + rr) * LD + 8 * seg) = make_float4(y[0], y[1], y[2], y[3]);
+    *reinterpret_cast<float4*>(s_x + (dst_row + rr) * LD + 8 * seg + 4) = make_float4(y[4], y[5], y[6], y[7]);
+  }
+}
+
 template <typename T, int K, int V>
 __global__ void __launch_bounds__(256) zoo_kda_wy_kernel(DiagArgs a) {
-  constexpr int C = 64, LD = K + 4, LDV = V + 8;
+  constexpr int C = 64, LD = K + 4, LDV = V + 8, SUB = 16;
+  constexpr int REG0 = C * (LD > LDV ? LD : LDV);
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  float* s_gc = reinterpret_cast<float*>(smem_raw);  // later: gc * log2(e)
-  float* s_kf = s_gc + C * LD;
-  float* s_vf = s_kf + C * LD;
-  float* s_G = s_vf + C * LDV;
+  float* s_gc = reinterpret_cast<float*>(smem_raw);  // gc tile; v (fp32) once the decayed keys are formed
+  float* s_x = s_gc + REG0;                          // k (fp32), then anchored operands, then k exp(gc)
+  float* s_G = s_x + C * LD;
   float* s_T = s_G + C * 68;
   float* s_bs = s_T + C * 68;
   float* s_b1 = s_bs + C;
+  float* s_vf = s_gc;
 
   const int c = blockIdx.x, bh = blockIdx.y;
   const int b = bh / a.H, h = bh % a.H;
@@ -359,20 +396,12 @@ __global__ void __launch_bounds__(256) zoo_kda_wy_kernel(DiagArgs a) {
   load_gc_tile<K>(a.gc + tile * (size_t)(C * K), s_gc);
   {
     const T* kp = reinterpret_cast<const T*>(a.k);
-    const T* vp = reinterpret_cast<const T*>(a.v);
     for (int i = tid; i < C * (K / 8); i += 256) {
       const int t = i / (K / 8), seg = i % (K / 8);
       float x[8];
-      Act<T>::unpack8(*reinterpret_cast<const uint4*>(kp + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K + 8 * seg), x);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) s_kf[t * LD + 8 * seg + e] = x[e];
-    }
-    for (int i = tid; i < C * (V / 8); i += 256) {
-      const int t = i / (V / 8), seg = i % (V / 8);
-      float x[8];
-      Act<T>::unpack8(*reinterpret_cast<const uint4*>(vp + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * V + 8 * seg), x);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) s_vf[t * LDV + 8 * seg + e] = x[e];
+      Act<T>::unpack8(__ldg(reinterpret_cast<const uint4*>(kp + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K + 8 * seg)), x);
+      *reinterpret_cast<float4*>(s_x + t * LD + 8 * seg) = make_float4(x[0], x[1], x[2], x[3]);
+      *reinterpret_cast<float4*>(s_x + t * LD + 8 * seg + 4) = make_float4(x[4], x[5], x[6], x[7]);
     }
   }
   if (tid < C) {
@@ -384,47 +413,107 @@ __global__ void __launch_bounds__(256) zoo_kda_wy_kernel(DiagArgs a) {
   for (int i = tid; i < C * 68; i += 256) s_G[i] = 0.f;
   __syncthreads();
 
-  // Gram matrix with exact per-channel weights, strictly lower triangle: 2016 pairs, eight lanes per pair
-  for (int pass = 0; pass < 63; ++pass) {
+  // ---- diagonal blocks: 4 x 120 strictly-lower pairs, eight lanes per pair, exact per-channel weights
+  for (int pass = 0; pass < 15; ++pass) {
     const int p = pass * 32 + (tid >> 3);
-    int i = (int)((sqrtf(8.f * p + 1.f) + 1.f) * 0.5f);
-    while (i * (i + 1) / 2 <= p) ++i;
-    while (i * (i - 1) / 2 > p) --i;
-    const int jj = p - i * (i - 1) / 2;
+    const int I = p / 120, rem = p % 120;
+    int i = (int)((sqrtf(8.f * rem + 1.f) + 1.f) * 0.5f);
+    while (i * (i + 1) / 2 <= rem) ++i;
+    while (i * (i - 1) / 2 > rem) --i;
+    const int jj = rem - i * (i - 1) / 2;
+    const int ti = SUB * I + i, tj = SUB * I + jj;
     const int l8 = tid & 7;
     float sum = 0.f;
+#pragma unroll 4
     for (int n = l8; n < K; n += 8) {
-      const float w = __expf(s_gc[i * LD + n] - s_gc[jj * LD + n]);
-      sum = fmaf(s_kf[i * LD + n] * s_kf[jj * LD + n], w, sum);
+      const float w = __expf(s_gc[ti * LD + n] - s_gc[tj * LD + n]);
+      sum = fmaf(s_x[ti * LD + n] * s_x[tj * LD + n], w, sum);
     }
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-    if (l8 == 0) s_G[i * 68 + jj] = s_bs[i] * s_b1[jj] * sum;
+    if (l8 == 0) s_G[ti * 68 + tj] = s_bs[ti] * s_b1[tj] * sum;
   }
   __syncthreads();
+
+  // ---- off-diagonal blocks: block row I against tokens [0, 16 I), anchored at row 16 I
+  for (int I = 1; I < C / SUB; ++I) {
+    kda_scaled_rows<T, K>(a, b, c, h, s_gc, s_x, SUB * I, 0, SUB * I, 0, false);        // ke -> rows 0 .. 16I-1
+    kda_scaled_rows<T, K>(a, b, c, h, s_gc, s_x, SUB * I, SUB * I, SUB, 48, true);      // kd -> rows 48 .. 63
+    __syncthreads();
+    if (warp < 2 * I) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      const float* ra = s_x + (48 + g) * LD;
+      const float* rb = s_x + (56 + g) * LD;
+      const float* rn = s_x + (8 * warp + g) * LD;
+#pragma unroll 4
+      for (int kk = 0; kk < K / 8; ++kk) {
+        const int c0 = 8 * kk + j4, c1 = c0 + 4;
+        const float xa[4] = {ra[c0], rb[c0], ra[c1], rb[c1]};
+        const float xb[2] = {rn[c0], rn[c1]};
+        uint32_t ab[4], as_[4], bb[2], bs_[2];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          ab[e] = tf32_rna(xa[e]);
+          as_[e] = tf32_rna(xa[e] - __uint_as_float(ab[e]));
+        }
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          bb[e] = tf32_rna(xb[e]);
+          bs_[e] = tf32_rna(xb[e] - __uint_as_float(bb[e]));
+        }
+        mma_tf32(acc, as_[0], as_[1], as_[2], as_[3], bb[0], bb[1]);
+        mma_tf32(acc, ab[0], ab[1], ab[2], ab[3], bs_[0], bs_[1]);
+        mma_tf32(acc, ab[0], ab[1], ab[2], ab[3], bb[0], bb[1]);
+      }
+      const int ia = SUB * I + g, ib = ia + 8;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int jj = 8 * warp + 2 * j4 + e;
+        s_G[ia * 68 + jj] = s_bs[ia] * s_b1[jj] * acc[e];
+        s_G[ib * 68 + jj] = s_bs[ib] * s_b1[jj] * acc[2 + e];
+      }
+    }
+    __syncthreads();
+  }
   wy_solve(s_G, s_T);
-  // decayed keys k * exp(gc) in place (the Gram pass is done with the bare keys)
-  for (int i = tid; i < C * K; i += 256) {
-    const int t = i / K, n = i % K;
-    s_kf[t * LD + n] = s_kf[t * LD + n] * expf(s_gc[t * LD + n]);
-  }
+  // decayed keys k * exp(gc) (the Gram passes are done); then the gc region is free for v
+  kda_scaled_rows<T, K>(a, b, c, h, s_gc, s_x, -1, 0, C, 0, false);
   __syncthreads();
-  // W = T diag(beta^sigma) (k * exp(gc)): fp32 FMA, one channel per thread, rows interleaved over the groups
   {
-    constexpr int GR = 256 / K;
-    const int n = tid % K, rg = tid / K;
-    const float inv_sw = 1.0f / a.sw[h];
-    for (int i = rg; i < C; i += GR) {
-      float acc = 0.f;
-      for (int jj = 0; jj <= i; ++jj) acc = fmaf(s_T[i * 68 + jj] * s_bs[jj], s_kf[jj * LD + n], acc);
-      a.wq[(tile * C + i) * K + n] = (int8_t)q8(Act<T>::round(acc), inv_sw, a.qmax);
+    const T* vp = reinterpret_cast<const T*>(a.v);
+    for (int i = tid; i < C * (V / 8); i += 256) {
+      const int t = i / (V / 8), seg = i % (V / 8);
+      float x[8];
+      Act<T>::unpack8(__ldg(reinterpret_cast<const uint4*>(vp + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * V + 8 * seg)), x);
+      *reinterpret_cast<float4*>(s_vf + t * LDV + 8 * seg) = make_float4(x[0], x[1], x[2], x[3]);
+      *reinterpret_cast<float4*>(s_vf + t * LDV + 8 * seg + 4) = make_float4(x[4], x[5], x[6], x[7]);
     }
   }
-  // U = T diag(beta^sigma) v on the tensor cores (v is exact in TF32)
+  const int mt = warp & 3, nh = warp >> 2;
+  // ---- W = T diag(beta^sigma) (k exp(gc))  -> w_read codes
+  {
+    constexpr int NTW = K / 16;
+    float acc[NTW][4];
+#pragma unroll
+    for (int nt = 0; nt < NTW; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    const int n0 = nh * (K / 2);
+    wy_product_split<NTW>(acc, s_T, s_bs, s_x, LD, mt, n0, g, j4);
+    const float inv_sw = 1.0f / a.sw[h];
+    const int ia = 16 * mt + g, ib = ia + 8;
+#pragma unroll
+    for (int nt = 0; nt < NTW; ++nt) {
+      const int col = n0 + 8 * nt + 2 * j4;
+      const int a0 = q8(Act<T>::round(acc[nt][0]), inv_sw, a.qmax), a1 = q8(Act<T>::round(acc[nt][1]), inv_sw, a.qmax);
+      const int b0 = q8(Act<T>::round(acc[nt][2]), inv_sw, a.qmax), b1 = q8(Act<T>::round(acc[nt][3]), inv_sw, a.qmax);
+      *reinterpret_cast<uint16_t*>(a.wq + (tile * C + ia) * K + col) = (uint16_t)((a0 & 0xff) | ((a1 & 0xff) << 8));
+      *reinterpret_cast<uint16_t*>(a.wq + (tile * C + ib) * K + col) = (uint16_t)((b0 & 0xff) | ((b1 & 0xff) << 8));
+    }
+  }
+  __syncthreads();  // v staged by all threads
+  // ---- U = T diag(beta^sigma) v (v is exact in TF32)
   {
     constexpr int NTU = V / 16;
-    const int mt = warp & 3, nh = warp >> 2;
     float acc[NTU][4];
 #pragma unroll
     for (int nt = 0; nt < NTU; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
@@ -474,7 +563,7 @@ static int run_diag_T(const lq_zoo_problem* p, const DiagArgs& a, bool delta, in
     const size_t smem = sizeof(float) * (64 * (K + 4) + 64 * 65 + 64) + (size_t)(64 * K * 2 + 16 * K + 48 * K);
     return launch_big_smem(zoo_diag_amat_kernel<T, K>, "zoo_diag_amat_kernel", grid, smem, a, st);
   }
-  const size_t smem = sizeof(float) * (2 * 64 * (K + 4) + 64 * (V + 8) + 2 * 64 * 68 + 128);
+  const size_t smem = sizeof(float) * (64 * ((K + 4) > (V + 8) ? (K + 4) : (V + 8)) + 64 * (K + 4) + 2 * 64 * 68 + 128);
   return launch_big_smem(zoo_kda_wy_kernel<T, K, V>, "zoo_kda_wy_kernel", grid, smem, a, st);
 }
 
