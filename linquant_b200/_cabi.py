@@ -29,7 +29,7 @@ class ZooProblem(C.Structure):
                 ("rot_signs", C.c_void_p), ("dqk", C.c_void_p),
                 ("sq", C.c_void_p), ("sk", C.c_void_p), ("skw", C.c_void_p), ("svl", C.c_void_p), ("svw", C.c_void_p),
                 ("sstate", C.c_void_p), ("sw", C.c_void_p), ("sel", C.c_void_p), ("sew", C.c_void_p),
-                ("o", C.c_void_p), ("final_state", C.c_void_p), ("initial_state", C.c_void_p)]
+                ("o", C.c_void_p), ("final_state", C.c_void_p), ("initial_state", C.c_void_p), ("unrot_t", C.c_void_p)]
 
 
 class ZooWorkspace(C.Structure):

@@ -378,6 +378,13 @@ __global__ void __launch_bounds__(256) ssd_chunk_scan_kernel(lq_ssd_problem p) {
   float* s_dA = reinterpret_cast<float*>(smem + (size_t)C * 128);
   float* s_dt = s_dA + C;
   float* s_tab = s_dt + C;                               // [8 warps][C] below-diagonal decay table of the warp's m-tile
+  int8_t* s_qc = reinterpret_cast<int8_t*>(s_tab + 8 * C);  // [C][N] q_C codes of the chunk
+  int8_t* s_S = s_qc + (size_t)C * N;                       // [64][N] INT8 state entering the chunk
+  float* s_ss = reinterpret_cast<float*>(s_S + 64 * N);     // [64] state scales, [64] D
+  float* s_D = s_ss + 64;
+  // byte offset of 16-byte piece `ch` of row `row` in the two INT8 tiles: an MMA fragment load touches two rows x
+  // four pieces per quarter-warp, so odd rows swap their 64-byte halves (rows of 64 bytes interleave by themselves)
+  auto frag_off = [](int row, int ch) { return N == 128 ? row * 128 + ((ch ^ ((row & 1) << 2)) << 4) : row * 64 + (ch << 4); };
 
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int grp = h / (p.H / p.G);
@@ -385,9 +392,24 @@ __global__ void __launch_bounds__(256) ssd_chunk_scan_kernel(lq_ssd_problem p) {
   const int g = lane >> 2, j = lane & 3;
   const size_t cbase = (((size_t)b * p.H + h) * NC + c) * C;
 
+  const int8_t* qc = p.q_C + (((size_t)b * p.L + (size_t)c * C) * p.G + grp) * N;
+  const int8_t* sp = p.passed + ((((size_t)b * NC + c) * p.H + h) * P) * N;
+  for (int i = tid; i < C * (N / 16); i += 256) {
+    const int row = i / (N / 16), ch = i % (N / 16);
+    cp_async16(s_qc + frag_off(row, ch), qc + (size_t)row * p.G * N + 16 * ch);
+  }
+  for (int i = tid; i < 64 * (N / 16); i += 256) {
+    const int row = i / (N / 16), ch = i % (N / 16);
+    cp_async16(s_S + frag_off(row, ch), sp + (size_t)row * N + 16 * ch);
+  }
+  cp_async_commit();
   for (int t = tid; t < C; t += 256) {
     s_dA[t] = p.dA[cbase + t];
     s_dt[t] = p.dt[cbase + t];
+  }
+  if (tid < 64) {
+    s_ss[tid] = p.state_scale[h * P + tid];
+    s_D[tid] = p.D == nullptr ? 0.f : (p.D_has_hdim ? p.D[h * P + tid] : p.D[h]);
   }
   {
     const T* xp = reinterpret_cast<const T*>(p.x) + (size_t)b * p.x_stride_b + (size_t)h * p.x_stride_h;
@@ -403,12 +425,11 @@ __global__ void __launch_bounds__(256) ssd_chunk_scan_kernel(lq_ssd_problem p) {
       *reinterpret_cast<uint4*>(s_x + row * 128 + ((ch ^ (row & 7)) << 4)) = raw;
     }
   }
+  cp_async_wait<0>();
   __syncthreads();
 
   const float gscale = p.C_scale[grp], Scb = p.cb_scale[grp];
   const int MT = C / 16;
-  const int8_t* qc = p.q_C + (((size_t)b * p.L + (size_t)c * C) * p.G + grp) * N;
-  const int8_t* sp = p.passed + ((((size_t)b * NC + c) * p.H + h) * P) * N;
   const int8_t* cbp = p.cb + (((size_t)b * NC + c) * p.G + grp) * C * C;
   __half* op = reinterpret_cast<__half*>(p.out);
 
@@ -424,8 +445,8 @@ __global__ void __launch_bounds__(256) ssd_chunk_scan_kernel(lq_ssd_problem p) {
       uint4 qa[N / 64], qb[N / 64];
 #pragma unroll
       for (int kk = 0; kk < N / 64; ++kk) {
-        qa[kk] = __ldg(reinterpret_cast<const uint4*>(qc + (size_t)ma * p.G * N + 64 * kk + 16 * j));
-        qb[kk] = __ldg(reinterpret_cast<const uint4*>(qc + (size_t)mb * p.G * N + 64 * kk + 16 * j));
+        qa[kk] = *reinterpret_cast<const uint4*>(s_qc + frag_off(ma, 4 * kk + j));
+        qb[kk] = *reinterpret_cast<const uint4*>(s_qc + frag_off(mb, 4 * kk + j));
       }
       const float ga = expf(dAa), gb = expf(dAb);
 #pragma unroll
@@ -433,13 +454,13 @@ __global__ void __launch_bounds__(256) ssd_chunk_scan_kernel(lq_ssd_problem p) {
         int acc[4] = {0, 0, 0, 0};
 #pragma unroll
         for (int kk = 0; kk < N / 64; ++kk) {
-          const uint4 bs = __ldg(reinterpret_cast<const uint4*>(sp + (size_t)(8 * nt + g) * N + 64 * kk + 16 * j));
+          const uint4 bs = *reinterpret_cast<const uint4*>(s_S + frag_off(8 * nt + g, 4 * kk + j));
           mma_s8(acc, qa[kk].x, qb[kk].x, qa[kk].y, qb[kk].y, bs.x, bs.y);
           mma_s8(acc, qa[kk].z, qb[kk].z, qa[kk].w, qb[kk].w, bs.z, bs.w);
         }
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const float ss = p.state_scale[h * P + 8 * nt + 2 * j + e];
+          const float ss = s_ss[8 * nt + 2 * j + e];
           accf[nt][e] = __fmul_rn(__fmul_rn(__fmul_rn((float)acc[e], gscale), ss), ga);
           accf[nt][2 + e] = __fmul_rn(__fmul_rn(__fmul_rn((float)acc[2 + e], gscale), ss), gb);
         }
@@ -464,46 +485,58 @@ __global__ void __launch_bounds__(256) ssd_chunk_scan_kernel(lq_ssd_problem p) {
     const int xrow = 4 * (rr >> 1) + 2 * (mi & 1) + (rr & 1);  // ldmatrix row of this lane within a k16 step
     const int8_t* cba = cbp + (size_t)ma * C + 4 * j;
     const int8_t* cbb = cbp + (size_t)mb * C + 4 * j;
-    uint32_t wa_n = __ldg(reinterpret_cast<const uint32_t*>(cba)), wb_n = __ldg(reinterpret_cast<const uint32_t*>(cbb));
-    for (int ks = 0; ks <= mt; ++ks) {
-      uint32_t af[4];
-      const int k0 = 16 * ks + 4 * j;
-      const uint32_t wa = wa_n, wb = wb_n;
-      if (ks < mt) {  // CB codes of the next step, in flight during this one
-        wa_n = __ldg(reinterpret_cast<const uint32_t*>(cba + 16 * (ks + 1)));
-        wb_n = __ldg(reinterpret_cast<const uint32_t*>(cbb + 16 * (ks + 1)));
-      }
-      float va[4], vb[4];
-      if (ks < mt) {
-        const float4 t4 = *reinterpret_cast<const float4*>(tab + k0);
-        const float tv[4] = {t4.x, t4.y, t4.z, t4.w};
+    // CB codes travel four k16 steps ahead of their use (a ring of four register pairs)
+    uint32_t wa_r[4], wb_r[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          va[e] = __fmul_rn(__fmul_rn((float)(int8_t)(wa >> (8 * e)), ea), tv[e]);
-          vb[e] = __fmul_rn(__fmul_rn((float)(int8_t)(wb >> (8 * e)), eb), tv[e]);
+    for (int u = 0; u < 4; ++u) {
+      const int ks = u <= mt ? u : mt;
+      wa_r[u] = __ldg(reinterpret_cast<const uint32_t*>(cba + 16 * ks));
+      wb_r[u] = __ldg(reinterpret_cast<const uint32_t*>(cbb + 16 * ks));
+    }
+    for (int ks0 = 0; ks0 <= mt; ks0 += 4) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int ks = ks0 + u;
+        if (ks > mt) break;
+        uint32_t af[4];
+        const int k0 = 16 * ks + 4 * j;
+        const uint32_t wa = wa_r[u], wb = wb_r[u];
+        if (ks + 4 <= mt) {
+          wa_r[u] = __ldg(reinterpret_cast<const uint32_t*>(cba + 16 * (ks + 4)));
+          wb_r[u] = __ldg(reinterpret_cast<const uint32_t*>(cbb + 16 * (ks + 4)));
         }
-      } else {
+        float va[4], vb[4];
+        if (ks < mt) {
+          const float4 t4 = *reinterpret_cast<const float4*>(tab + k0);
+          const float tv[4] = {t4.x, t4.y, t4.z, t4.w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int k = k0 + e;
-          const float dk = s_dA[k], dtk = s_dt[k];
-          const float ca = (float)(int8_t)(wa >> (8 * e)), cb = (float)(int8_t)(wb >> (8 * e));
-          va[e] = (ma >= k) ? __fmul_rn(__fmul_rn(__fmul_rn(ca, Scb), __expf(__fsub_rn(dAa, dk))), dtk) : 0.f;
-          vb[e] = (mb >= k) ? __fmul_rn(__fmul_rn(__fmul_rn(cb, Scb), __expf(__fsub_rn(dAb, dk))), dtk) : 0.f;
+          for (int e = 0; e < 4; ++e) {
+            va[e] = __fmul_rn(__fmul_rn((float)(int8_t)(wa >> (8 * e)), ea), tv[e]);
+            vb[e] = __fmul_rn(__fmul_rn((float)(int8_t)(wb >> (8 * e)), eb), tv[e]);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int k = k0 + e;
+            const float dk = s_dA[k], dtk = s_dt[k];
+            const float ca = (float)(int8_t)(wa >> (8 * e)), cb = (float)(int8_t)(wb >> (8 * e));
+            va[e] = (ma >= k) ? __fmul_rn(__fmul_rn(__fmul_rn(ca, Scb), __expf(__fsub_rn(dAa, dk))), dtk) : 0.f;
+            vb[e] = (mb >= k) ? __fmul_rn(__fmul_rn(__fmul_rn(cb, Scb), __expf(__fsub_rn(dAb, dk))), dtk) : 0.f;
+          }
         }
-      }
-      af[0] = Act<__half>::pack2(va[0], va[1]);
-      af[1] = Act<__half>::pack2(vb[0], vb[1]);
-      af[2] = Act<__half>::pack2(va[2], va[3]);
-      af[3] = Act<__half>::pack2(vb[2], vb[3]);
+        af[0] = Act<__half>::pack2(va[0], va[1]);
+        af[1] = Act<__half>::pack2(vb[0], vb[1]);
+        af[2] = Act<__half>::pack2(va[2], va[3]);
+        af[3] = Act<__half>::pack2(vb[2], vb[3]);
 #pragma unroll
-      for (int n2 = 0; n2 < 4; ++n2) {
-        const int row = 16 * ks + xrow;
-        const int ch = 2 * n2 + (mi >> 1);
-        uint32_t r[4];
-        ldmatrix_x4_trans(r, s_x + row * 128 + ((ch ^ (row & 7)) << 4));
-        mma_f16(conv[2 * n2], af[0], af[1], af[2], af[3], r[0], r[1]);
-        mma_f16(conv[2 * n2 + 1], af[0], af[1], af[2], af[3], r[2], r[3]);
+        for (int n2 = 0; n2 < 4; ++n2) {
+          const int row = 16 * ks + xrow;
+          const int ch = 2 * n2 + (mi >> 1);
+          uint32_t r[4];
+          ldmatrix_x4_trans(r, s_x + row * 128 + ((ch ^ (row & 7)) << 4));
+          mma_f16(conv[2 * n2], af[0], af[1], af[2], af[3], r[0], r[1]);
+          mma_f16(conv[2 * n2 + 1], af[0], af[1], af[2], af[3], r[2], r[3]);
+        }
       }
     }
     // ---- combine, D*x residual, store fp16
@@ -519,7 +552,7 @@ __global__ void __launch_bounds__(256) ssd_chunk_scan_kernel(lq_ssd_problem p) {
         oa[e] = __fadd_rn(accf[nt][e], conv[nt][e]);
         ob[e] = __fadd_rn(accf[nt][2 + e], conv[nt][2 + e]);
         if (p.D != nullptr) {
-          const float Dv = p.D_has_hdim ? p.D[h * P + pc + e] : p.D[h];
+          const float Dv = s_D[pc + e];
           oa[e] = __fadd_rn(oa[e], __fmul_rn(xav[e], Dv));
           ob[e] = __fadd_rn(ob[e], __fmul_rn(xbv[e], Dv));
         }
@@ -730,8 +763,9 @@ extern "C" int lq_ssd_bmm_chunk(const lq_ssd_problem* p, int b_is_fp, lq_stream 
 
 template <typename T, int N>
 static int launch_scan(const lq_ssd_problem* p, cudaStream_t st) {
-  const size_t smem = (size_t)p->chunk * 128 + 10 * sizeof(float) * p->chunk;
+  const size_t smem = (size_t)p->chunk * 128 + 10 * sizeof(float) * p->chunk + (size_t)(p->chunk + 64) * N + 128 * sizeof(float);
   dim3 grid(p->L / p->chunk, p->H, p->B);
+  cudaFuncSetAttribute(ssd_chunk_scan_kernel<T, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
   ssd_chunk_scan_kernel<T, N><<<grid, 256, smem, st>>>(*p);
   return check_launch("ssd_chunk_scan_kernel");
 }

@@ -20,6 +20,7 @@ struct OutputArgs {
   const int8_t *qq, *kl, *vlT, *hT;
   const float *gc, *sq, *sk, *svl, *ss;
   const __half* amat;  // diagonal decay: [BH,NT,C,C] intra-chunk matrix A, already masked and in fp16
+  const __half* unrot_t;  // canonical storage: [V,V] fp16, element [v'][v] = M[v][v'] of the un-rotation o_local . M
   void* o;
   int T, H, NT;
 };
@@ -50,9 +51,9 @@ __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* dst, const 
                  Act<__nv_bfloat16>::pack2(x[4], x[5]), Act<__nv_bfloat16>::pack2(x[6], x[7]));
 }
 
-template <int K, int V, typename OT, bool DIAG>
+template <int K, int V, typename OT, bool DIAG, bool UNROT>
 __global__ void __launch_bounds__(128) zoo_output_scalar_kernel(OutputArgs a) {
-  constexpr int C = 64;
+  constexpr int C = 64, LDR = V + 8;
   constexpr int KK = K / 64;  // 64-byte reduction blocks per row
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* s_q = smem;
@@ -62,6 +63,7 @@ __global__ void __launch_bounds__(128) zoo_output_scalar_kernel(OutputArgs a) {
   float* s_gc = reinterpret_cast<float*>(s_v + V * C);
   float* s_ss = s_gc + C;
   float* s_svl = s_ss + V;
+  __half* s_rt = reinterpret_cast<__half*>(s_svl + V);  // [V][LDR] un-rotation, input index contiguous (UNROT only)
 
   const int c = blockIdx.x, bh = blockIdx.y;
   const int b = bh / a.H, h = bh % a.H;
@@ -88,6 +90,12 @@ __global__ void __launch_bounds__(128) zoo_output_scalar_kernel(OutputArgs a) {
     for (int i = tid; i < V * 4; i += 128) {
       const int row = i >> 2, ch = i & 3;
       cp_async16(s_v + swz_v(row, ch), gv + (size_t)i * 16);
+    }
+    if (UNROT) {
+      for (int i = tid; i < V * (V / 8); i += 128) {
+        const int row = i / (V / 8), ch = i % (V / 8);
+        cp_async16(s_rt + row * LDR + 8 * ch, a.unrot_t + (size_t)row * V + 8 * ch);
+      }
     }
     cp_async_commit();
     if (tid < C) s_gc[tid] = DIAG ? 0.f : a.gc[tile * C + tid];
@@ -170,6 +178,39 @@ __global__ void __launch_bounds__(128) zoo_output_scalar_kernel(OutputArgs a) {
     }
   }
 
+  // ---- canonical storage: the local product (rotated value basis) is scaled, rounded to fp16 and multiplied by the
+  // un-rotation on the tensor cores (zoo/simple_gla.py:150-153). The accumulator pairs of two n-tiles are the A
+  // fragment of one k16 step; gathering the rows of M^T with the same channel permutation as the value codes makes
+  // the result come out in the column order the combine below expects.
+  if (UNROT) {
+    uint32_t A[V / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < V / 16; ++kk) {
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int nt = 2 * kk + hh;
+        const int cb = 32 * (nt >> 2) + 8 * j + 2 * (nt & 3);
+        const float s0 = s_svl[cb], s1 = s_svl[cb + 1];
+        A[kk][2 * hh] = Act<__half>::pack2(__fmul_rn(acco[nt][0], s0), __fmul_rn(acco[nt][1], s1));
+        A[kk][2 * hh + 1] = Act<__half>::pack2(__fmul_rn(acco[nt][2], s0), __fmul_rn(acco[nt][3], s1));
+      }
+    }
+#pragma unroll
+    for (int nt2 = 0; nt2 < V / 8; ++nt2) {
+      const int vr = 32 * (nt2 >> 2) + 8 * (g >> 1) + 2 * (nt2 & 3) + (g & 1);
+      const __half* row = s_rt + vr * LDR;
+      float u[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int kk = 0; kk < V / 16; ++kk) {
+        const int c0 = 32 * ((2 * kk) >> 2) + 8 * j + 2 * ((2 * kk) & 3);
+        const int c1 = 32 * ((2 * kk + 1) >> 2) + 8 * j + 2 * ((2 * kk + 1) & 3);
+        mma_f16(u, A[kk][0], A[kk][1], A[kk][2], A[kk][3], *reinterpret_cast<const uint32_t*>(row + c0),
+                *reinterpret_cast<const uint32_t*>(row + c1));
+      }
+      acco[nt2][0] = u[0]; acco[nt2][1] = u[1]; acco[nt2][2] = u[2]; acco[nt2][3] = u[3];
+    }
+  }
+
   // ---- S1 against the stored state, combine, store
   const float ega = DIAG ? 1.f : __expf(gia), egb = DIAG ? 1.f : __expf(gib);
   OT* op = reinterpret_cast<OT*>(a.o);
@@ -195,8 +236,8 @@ __global__ void __launch_bounds__(128) zoo_output_scalar_kernel(OutputArgs a) {
         const float ss = s_ss[vc], svl = s_svl[vc];
         const float ra = __fmul_rn(__fmul_rn(__fmul_rn((float)acc[e], sq), ss), ega);
         const float rb = __fmul_rn(__fmul_rn(__fmul_rn((float)acc[2 + e], sq), ss), egb);
-        outa[2 * n4 + e] = fmaf(acco[nt][e], svl, ra);
-        outb[2 * n4 + e] = fmaf(acco[nt][2 + e], svl, rb);
+        outa[2 * n4 + e] = UNROT ? __fadd_rn(acco[nt][e], ra) : fmaf(acco[nt][e], svl, ra);
+        outb[2 * n4 + e] = UNROT ? __fadd_rn(acco[nt][2 + e], rb) : fmaf(acco[nt][2 + e], svl, rb);
       }
     }
     store8<OT>(op + rowa + 32 * ng + 8 * j, outa);
@@ -207,16 +248,26 @@ __global__ void __launch_bounds__(128) zoo_output_scalar_kernel(OutputArgs a) {
 template <int K, int V>
 static int launch_output(const lq_zoo_problem* p, const OutputArgs& a, cudaStream_t st) {
   dim3 grid(a.NT, p->B * p->H), block(128);
-  const size_t smem = (size_t)64 * K * 2 + (size_t)V * K + (size_t)V * 64 + sizeof(float) * (64 + 2 * V);
-  const bool diag = p->decay == LQ_DECAY_DIAGONAL;
-#define LQ_LAUNCH_OUT(OT_)                                                                 \
-  if (diag) zoo_output_scalar_kernel<K, V, OT_, true><<<grid, block, smem, st>>>(a);       \
-  else zoo_output_scalar_kernel<K, V, OT_, false><<<grid, block, smem, st>>>(a)
+  const bool diag = p->decay == LQ_DECAY_DIAGONAL, unrot = a.unrot_t != nullptr;
+  const size_t smem = (size_t)64 * K * 2 + (size_t)V * K + (size_t)V * 64 + sizeof(float) * (64 + 2 * V) +
+                      (unrot ? sizeof(__half) * (size_t)V * (V + 8) : 0);
+#define LQ_LAUNCH_ONE(OT_, DIAG_, UNROT_)                                                                              \
+  do {                                                                                                                 \
+    auto kern = zoo_output_scalar_kernel<K, V, OT_, DIAG_, UNROT_>;                                                    \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+    kern<<<grid, block, smem, st>>>(a);                                                                                \
+  } while (0)
+#define LQ_LAUNCH_OUT(OT_)                                 \
+  if (diag && unrot) LQ_LAUNCH_ONE(OT_, true, true);       \
+  else if (diag) LQ_LAUNCH_ONE(OT_, true, false);          \
+  else if (unrot) LQ_LAUNCH_ONE(OT_, false, true);         \
+  else LQ_LAUNCH_ONE(OT_, false, false)
   if (p->out_dtype == LQ_F16) { LQ_LAUNCH_OUT(__half); }
   else if (p->out_dtype == LQ_BF16) { LQ_LAUNCH_OUT(__nv_bfloat16); }
   else if (p->out_dtype == LQ_F32) { LQ_LAUNCH_OUT(float); }
   else return fail(LQ_ERR_UNSUPPORTED, "output: out dtype must be f16, bf16 or f32");
 #undef LQ_LAUNCH_OUT
+#undef LQ_LAUNCH_ONE
   return check_launch("zoo_output_scalar_kernel");
 }
 
@@ -229,11 +280,13 @@ int run_output_scalar(const lq_zoo_problem* p, const lq_zoo_workspace* ws, const
                       cudaStream_t st) {
   // K = 128 with none / scalar decay runs on the tcgen05 + TMA kernel; other shapes and the diagonal-decay variant
   // (A precomputed, no q.k^T product) on the warp-level MMA kernel below
-  if (p->K == 128 && p->decay != LQ_DECAY_DIAGONAL && ws->status != nullptr) return run_output_tc(p, ws, s_local_value, st);
+  if (p->K == 128 && p->decay != LQ_DECAY_DIAGONAL && ws->status != nullptr && p->unrot_t == nullptr)
+    return run_output_tc(p, ws, s_local_value, st);
   OutputArgs a;
   a.qq = ws->qq; a.kl = ws->kl; a.vlT = ws->vlT; a.hT = ws->hT; a.gc = ws->gc;
   a.sq = p->sq; a.sk = p->sk; a.svl = s_local_value; a.ss = p->sstate; a.o = p->o;
   a.amat = reinterpret_cast<const __half*>(ws->amat);
+  a.unrot_t = reinterpret_cast<const __half*>(p->unrot_t);
   a.T = p->T; a.H = p->H; a.NT = p->T / p->chunk;
   if (p->K == 64 && p->V == 64) return launch_output<64, 64>(p, a, st);
   if (p->K == 64 && p->V == 128) return launch_output<64, 128>(p, a, st);

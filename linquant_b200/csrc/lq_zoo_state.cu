@@ -152,7 +152,10 @@ __global__ void __launch_bounds__(128) zoo_state_linear_kernel(StateArgs a) {
 
 int validate_zoo_problem(const lq_zoo_problem* p, bool delta, bool diagonal);
 
+int run_state_linear_unrot(const lq_zoo_problem* p, const lq_zoo_workspace* ws, cudaStream_t st);
+
 int run_state_linear(const lq_zoo_problem* p, const lq_zoo_workspace* ws, cudaStream_t st) {
+  if (p->unrot_t != nullptr) return run_state_linear_unrot(p, ws, st);  // canonical storage: CTA spans all value channels
   StateArgs a;
   a.kwT = ws->kwT; a.vwT = ws->vwT; a.gc = ws->gc; a.skw = p->skw; a.svw = p->svw; a.ss = p->sstate;
   a.hT = ws->hT; a.final_state = p->final_state; a.initial_state = p->initial_state; a.H = p->H; a.NT = p->T / p->chunk;

@@ -35,7 +35,7 @@ def _sylvester(n):
 
 
 def make_problem(q, k, v, g, beta, scales, *, decay, eta, sigma, tau, scale, chunk_size, bits, out, final_state,
-                 rot_signs, dqk, keep, initial_state=None):
+                 rot_signs, dqk, keep, initial_state=None, unrot=None):
     """Builds the C descriptor. ``keep`` collects every temporary tensor whose storage the descriptor points to."""
     B, T, H, K = q.shape
     V = v.shape[-1]
@@ -61,6 +61,10 @@ def make_problem(q, k, v, g, beta, scales, *, decay, eta, sigma, tau, scale, chu
     put("o", out)
     put("final_state", final_state)
     put("initial_state", None if initial_state is None else initial_state.to(device=dev, dtype=torch.float32).contiguous())
+    if unrot is not None:  # the kernels want the fp16 matrix with the input index contiguous: element [v'][v] = unrot[v][v']
+        assert tuple(unrot.shape) == (V, V), f"unrot must be ({V},{V})"
+        unrot = unrot.to(device=dev, dtype=torch.float16).t().contiguous()
+    put("unrot_t", unrot)
     return P
 
 

@@ -17,12 +17,11 @@ def chunk_gla_int8(q, k, v, g, scales, *, eta=0.0, scale=None, chunk_size=64, ou
                    rot=None, bits=8, out_dtype=None, _debug=None):
     """q,k [B,T,H,K], v [B,T,H,V] (fp16/bf16), g [B,T,H,K] fp32 per-channel log-decay.
     scales: 'q' (H,) [on q*scale, tied read/local], 'k' (H,), 'kw' (H,K), 'vw' (H,V), 'vl' (H,V), 'state' (H,V).
+    unrot: optional (V,V) R_V^T (canonical storage, v arrives rotated).
     rot: optional signed-Hadamard R_QK ((K,K) matrix or (K,) signs) applied to the anchored local operands only.
     Returns (o [B,T,H,V] in v.dtype or out_dtype, final fp32 state [B,H,K,V] or None)."""
     if not q.is_cuda:
         raise _cabi.LinQuantError("chunk_gla_int8 runs on CUDA tensors only (no CPU path)")
-    if unrot is not None:
-        raise NotImplementedError("canonical R_V storage (unrot) is not implemented in this build")
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     B, T, H, K = q.shape
     V = v.shape[-1]
@@ -33,6 +32,6 @@ def chunk_gla_int8(q, k, v, g, scales, *, eta=0.0, scale=None, chunk_size=64, ou
     keep = []
     P = _common.make_problem(q, k, v, g, None, scales, decay=_cabi.DECAY_DIAGONAL, eta=eta, sigma=1.0, tau=1.0,
                              scale=scale, chunk_size=chunk_size, bits=bits, out=o, final_state=ht,
-                             rot_signs=_common.signs_of(rot, K, q.device), dqk=None, keep=keep)
+                             rot_signs=_common.signs_of(rot, K, q.device), dqk=None, keep=keep, unrot=unrot)
     _common.run("lq_gla_fwd", P, False, q, _debug)
     return o, ht

@@ -31,14 +31,14 @@ class OracleRun:
     output, the exact-arithmetic output (noise floor) and the recorded codes."""
 
     def __init__(self, q, k, v, g, beta, *, family, decay, policy="kernel_static", bits=8, eta=1.0, sigma=1.0, tau=1.0,
-                 rot_qk=None, scale=None, chunk=64, dqk=None):
+                 rot_qk=None, scale=None, chunk=64, dqk=None, rot_v=None, storage="rotated"):
         K = q.shape[-1]
         self.qz = zo.RoleQuantizer(policy, bits, 8, True)
         qd, kd = q, k
         if dqk is not None:  # harness.py:81-88: q*D, k/D in float64 ahead of chunk_core
             qd, kd = q.double() * dqk.double(), k.double() / dqk.double()
         self.kw = dict(family=family, decay=decay, scale=K**-0.5 if scale is None else scale, qz=self.qz, rot_qk=rot_qk,
-                       eta=eta, sigma=sigma, tau=tau, chunk=chunk, read_post=True, out_dtype=torch.float64,
+                       rot_v=rot_v, storage=storage, eta=eta, sigma=sigma, tau=tau, chunk=chunk, read_post=True, out_dtype=torch.float64,
                        act_dtype=q.dtype)
         self.args = (qd, kd, v, g, beta)
         zo.calibrate(self.qz, self.run)

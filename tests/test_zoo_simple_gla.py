@@ -148,3 +148,37 @@ def test_host_pipeline_matches_device_call():
         pipe(q.pin_memory(), k.pin_memory(), v.pin_memory(), g.pin_memory(), sc, ho)
         torch.cuda.synchronize()
         assert torch.equal(ho, want.cpu())
+
+
+@pytest.mark.parametrize("decay", [False, True])
+@pytest.mark.parametrize("n,Vd,dtype", [(128, 128, torch.float16), (512, 128, torch.float16), (256, 64, torch.bfloat16)])
+def test_canonical_storage_rv(decay, n, Vd, dtype):
+    """R_V with canonical storage (tests/test_kernel_simple_gla.py:84-104 of the reference): v is rotated in torch, the
+    kernels un-rotate the write product before the fp32 carry and the local product before the output, so the stored
+    INT8 state and the output are canonical."""
+    from linquant_b200.kernels.zoo.simple_gla import chunk_simple_gla_int8
+    from oracle import zoo_oracle as zo
+
+    q, k, v, g, _ = zoo_inputs(B, n, H, K, Vd, decay="scalar" if decay else "none", dtype=dtype)
+    R, _ = zo.signed_hadamard(Vd, 7)
+    orc = OracleRun(q, k, v, g, None, family="linear", decay="scalar" if decay else "none", eta=1.0, rot_v=R,
+                    storage="canonical")
+    ref, ref_state = orc.lineage()
+    exact = orc.exact()
+    vr = (v.double() @ R).to(dtype)
+    dbg = {}
+    out, ht = chunk_simple_gla_int8(q.cuda(), k.cuda(), vr.cuda(), None if g is None else g.cuda(), orc.scales("cuda"),
+                                    eta=1.0, scale=K**-0.5, chunk_size=64, output_final_state=True, unrot=R.T.cuda(),
+                                    _debug=dbg)
+    torch.cuda.synchronize()
+    ws = dbg["workspace"]
+    NT = n // 64
+    hT = ws.view("hT").view(B, H, NT, Vd, K).transpose(-1, -2)
+    st = orc.codes("state")
+    assert int(hT[:, :, 0].abs().max()) == 0
+    code_mismatch(hT[:, :, 1:], st[:, :, :-1], "canonical stored state codes", budget=2e-3)
+    label = f"canonical R_V decay={decay} T={n} V={Vd}"
+    err = rel_l2(out, ref)
+    assert err <= 2e-3, f"{label}: output rel-L2 {err:.3e}"
+    reference_check(out, ref, exact, label)
+    assert rel_l2(ht, ref_state) <= 1e-3, f"{label}: final fp32 carry {rel_l2(ht, ref_state):.2e}"
