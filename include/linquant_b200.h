@@ -179,6 +179,8 @@ typedef struct {
   const float* D;       /* [H] or [H,P] (already multiplied by its scale) or null */
   int D_has_hdim;
   void* out;
+  int* status;          /* optional device int32: set to 1 by a kernel whose bounded wait on a TMA / MMA barrier ran out
+                           (its output is then not valid); the caller zeroes it and reads it after synchronising */
 } lq_ssd_problem;
 
 /* dt = clamp(softplus(dt_scale*dt + bias)), dA = dt * -exp(A_log_scale*A_log), chunk-local cumsum.

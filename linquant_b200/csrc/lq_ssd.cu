@@ -685,6 +685,9 @@ extern "C" int lq_ssd_state_passing(const lq_ssd_problem* p, lq_stream stream) {
   return check_launch("ssd_state_passing_kernel");
 }
 
+namespace lq {
+int run_chunk_state_value_tc(const lq_ssd_problem* p, int* status, cudaStream_t st);
+}
 static int ssd_chunk_state(const lq_ssd_problem* p, bool keyside, lq_stream stream) {
   const char* what = keyside ? "chunk_state_key" : "chunk_state_value";
   if (int e = ssd_check(p, what)) return e;
@@ -699,6 +702,8 @@ static int ssd_chunk_state(const lq_ssd_problem* p, bool keyside, lq_stream stre
     if (!p->q_B || !p->q_BT || !p->alpha_hp || !p->bscale_g) return fail(LQ_ERR_NULL, "%s: q_B, q_BT, alpha_hp, bscale_g required", what);
     ssd_transpose_b_kernel<<<dim3(p->L / 64, p->G, p->B), 256, 0, st>>>(p->q_B, p->q_BT, p->L, p->G, p->N, p->chunk);
     if (int e = check_launch("ssd_transpose_b_kernel")) return e;
+    // chunks of 128 or 256 tokens run on tcgen05 + TMA; 64- and 192-token chunks on the warp-level MMA kernel
+    if (p->chunk % 128 == 0) return run_chunk_state_value_tc(p, p->status, st);
     launch_chunk_state<false>(p, grid, st);
   }
   return check_launch("ssd_chunk_state_kernel");

@@ -22,7 +22,26 @@ class SsdProblem(C.Structure):
                 ("cb_scale", C.c_void_p), ("alpha_hp", C.c_void_p), ("x_scale_hp", C.c_void_p), ("state_scale", C.c_void_p),
                 ("b_gate_scale", C.c_void_p), ("bgs_stride", C.c_longlong * 4),
                 ("states", C.c_void_p), ("passed", C.c_void_p), ("final_state", C.c_void_p), ("cb", C.c_void_p),
-                ("D", C.c_void_p), ("D_has_hdim", C.c_int), ("out", C.c_void_p)]
+                ("D", C.c_void_p), ("D_has_hdim", C.c_int), ("out", C.c_void_p), ("status", C.c_void_p)]
+
+
+_STATUS = {}
+
+
+def status_word(device):
+    """One int32 per device that the tcgen05 kernels raise when a bounded barrier wait runs out."""
+    key = torch.device(device).index
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _STATUS[key]
+
+
+def check_status(device):
+    """Synchronises and raises if any SSD kernel on ``device`` reported an expired wait since the last check."""
+    w = status_word(device)
+    if int(w.item()) != 0:
+        w.zero_()
+        raise _cabi.LinQuantError("an SSD kernel gave up waiting on a TMA / MMA barrier; its output is not valid")
 
 
 class Call:
@@ -32,6 +51,7 @@ class Call:
         self.p = SsdProblem()
         self.keep = []
         self.device = device
+        self.p.status = status_word(device).data_ptr()
 
     def dims(self, **kw):
         for k, v in kw.items():
