@@ -687,6 +687,7 @@ extern "C" int lq_ssd_state_passing(const lq_ssd_problem* p, lq_stream stream) {
 
 namespace lq {
 int run_chunk_state_value_tc(const lq_ssd_problem* p, int* status, cudaStream_t st);
+int run_chunk_scan_tc(const lq_ssd_problem* p, int* status, cudaStream_t st);
 }
 static int ssd_chunk_state(const lq_ssd_problem* p, bool keyside, lq_stream stream) {
   const char* what = keyside ? "chunk_state_key" : "chunk_state_value";
@@ -780,6 +781,13 @@ extern "C" int lq_ssd_chunk_scan(const lq_ssd_problem* p, lq_stream stream) {
   if (!p->cb || !p->dt || !p->dA || !p->q_C || !p->C_scale || !p->passed || !p->state_scale || !p->cb_scale || !p->out)
     return fail(LQ_ERR_NULL, "chunk_scan: cb, dt, dA, q_C, C_scale, passed, state_scale, cb_scale, out required");
   cudaStream_t st = (cudaStream_t)stream;
+  // Two kernels: the warp-level MMA kernel (every supported shape) and a tcgen05 + TMA kernel (d_state 128, chunks of
+  // 128 or 256 tokens). Building the decay-masked operand dominates both; at the Mamba-2 2.7B shape the warp-level
+  // kernel, with 16 resident warps hiding each other's latencies, is the faster one on B200 and is the default.
+  const bool tc_ok = p->N == 128 && p->chunk % 128 == 0;
+  if (p->scan_kernel == 2 && !tc_ok) return fail(LQ_ERR_UNSUPPORTED, "chunk_scan: the tcgen05 kernel needs d_state 128 and chunk 128 or 256");
+  if (p->scan_kernel < 0 || p->scan_kernel > 2) return fail(LQ_ERR_SHAPE, "chunk_scan: scan_kernel must be 0, 1 or 2");
+  if (p->scan_kernel == 2) return run_chunk_scan_tc(p, p->status, st);
   if (p->x_dtype == LQ_F16) return p->N == 128 ? launch_scan<__half, 128>(p, st) : launch_scan<__half, 64>(p, st);
   return p->N == 128 ? launch_scan<__nv_bfloat16, 128>(p, st) : launch_scan<__nv_bfloat16, 64>(p, st);
 }

@@ -141,8 +141,7 @@ __global__ void __launch_bounds__(128) ssd_chunk_state_tc_kernel(const __grid_co
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar_mma) : "memory");
     }
   }
-  ok = __syncthreads_and(ok ? 1 : 0) != 0;
-  if (ok) ok = mbar_wait_bounded(bar_mma, 0);
+  if (tid == 0 && ok) ok = mbar_wait_bounded(bar_mma, 0);  // one poller; the block barrier releases the rest
   ok = __syncthreads_and(ok ? 1 : 0) != 0;
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 

@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(128) zoo_output_tc_kernel(const __grid_constan
   // ---- S2 -> P (fp16 A fragments). S2 column n is row n of the k_local tile = token 16*(n/16) + 4j + 2*half + e
   // for n = 16ks + 8*half + 2j + e.
   uint32_t P[4][4];
-  if (ok) ok = mbar_wait_bounded(bar_s2, 0);
+  if (tid == 0 && ok) ok = mbar_wait_bounded(bar_s2, 0);  // one poller per barrier; the block barrier releases the rest
   ok = __syncthreads_and(ok ? 1 : 0) != 0;
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll
@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(128) zoo_output_tc_kernel(const __grid_constan
   }
 
   // ---- S1 from TMEM, combine, store. S1 column n is row n of the state tile = channel 32*(n/32) + 8j + 2*n4 + e.
-  if (ok) ok = mbar_wait_bounded(bar_s1, 0);
+  if (tid == 0 && ok) ok = mbar_wait_bounded(bar_s1, 0);
   ok = __syncthreads_and(ok ? 1 : 0) != 0;
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   if (ok) {

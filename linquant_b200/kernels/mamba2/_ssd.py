@@ -22,7 +22,7 @@ class SsdProblem(C.Structure):
                 ("cb_scale", C.c_void_p), ("alpha_hp", C.c_void_p), ("x_scale_hp", C.c_void_p), ("state_scale", C.c_void_p),
                 ("b_gate_scale", C.c_void_p), ("bgs_stride", C.c_longlong * 4),
                 ("states", C.c_void_p), ("passed", C.c_void_p), ("final_state", C.c_void_p), ("cb", C.c_void_p),
-                ("D", C.c_void_p), ("D_has_hdim", C.c_int), ("out", C.c_void_p), ("status", C.c_void_p)]
+                ("D", C.c_void_p), ("D_has_hdim", C.c_int), ("out", C.c_void_p), ("scan_kernel", C.c_int), ("status", C.c_void_p)]
 
 
 _STATUS = {}

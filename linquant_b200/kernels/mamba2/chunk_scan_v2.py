@@ -5,16 +5,21 @@ import torch
 from . import _ssd
 
 
-def _quant_chunk_scan_fwd(cb_i8, x_fp, dt, dA_cumsum, q_C, C_scale, states, q_D, D_scale, state_dequant_scale, cb_scale):
+SCAN_KERNELS = {None: 0, "auto": 0, "warp_mma": 1, "tcgen05": 2}
+
+
+def _quant_chunk_scan_fwd(cb_i8, x_fp, dt, dA_cumsum, q_C, C_scale, states, q_D, D_scale, state_dequant_scale, cb_scale,
+                          kernel=None):
     """cb_i8 (B,NC,G,C,C) int8 on cb_scale (G,); x_fp (B,L,H,P); q_C (B,L,G,N) int8 on C_scale (G,); states
     (B,NC,H,P,N) int8 entering each chunk on state_dequant_scale (H,P); q_D (H,) or (H,P) with scalar D_scale, or None.
-    Returns out (B,L,H,P) fp16."""
+    ``kernel`` (not in the reference signature): None / "auto" = the library's choice, "warp_mma", or "tcgen05"
+    (d_state 128 with chunk 128 or 256). Returns out (B,L,H,P) fp16."""
     _ssd.require_cuda(x_fp, "_quant_chunk_scan_fwd")
     _, _, nc, chunk = dt.shape
     _, _, G, N = q_C.shape
     B, L, H, P = x_fp.shape
     dev = x_fp.device
-    call = _ssd.Call(dev).dims(B=B, L=L, H=H, P=P, G=G, N=N, chunk=chunk)
+    call = _ssd.Call(dev).dims(B=B, L=L, H=H, P=P, G=G, N=N, chunk=chunk, scan_kernel=SCAN_KERNELS[kernel])
     call.x(x_fp)
     call.put("cb", cb_i8.contiguous())
     call.f32("dt", dt)
