@@ -317,6 +317,93 @@ def run_reference(args):
     }), flush=True)
 
 
+STAGE_WORKLOADS = {
+    # name: (B, T, H, K, V, delta, diagonal, stage entry points); per-GPU slices of the benchmark configurations
+    "simple_gla": (4, 4096, 16, 128, 128, False, False, ("lq_zoo_prologue_linear", "lq_zoo_state_linear", "lq_zoo_output_scalar")),
+    "gated_deltanet": (4, 8192, 16, 128, 128, True, False, ("lq_zoo_prologue_delta", "lq_zoo_state_delta", "lq_zoo_output_scalar")),
+    "kda_b2": (2, 8192, 32, 128, 128, True, True,
+               ("lq_zoo_diag_rows", "lq_zoo_diag_amat", "lq_zoo_kda_wy", "lq_zoo_state_delta", "lq_zoo_output_scalar")),
+    "gla_b2": (2, 8192, 32, 128, 128, False, True, ("lq_zoo_diag_rows", "lq_zoo_diag_amat", "lq_zoo_state_linear", "lq_zoo_output_scalar")),
+}
+
+
+def _time_us(fn, reps):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps * 1e3
+
+
+def run_stages(args):
+    """Per-kernel CUDA-event times of one workload (`--stages NAME`), device-resident inputs, constant scales (timing
+    does not depend on their values). `mamba2_b2` = one layer of the Mamba-2 2.7B-shaped SSD stack at B=2 of 8."""
+    from linquant_b200 import _cabi
+    from linquant_b200.kernels.zoo import _common
+
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    f = lambda *s, val=1.0: torch.full(s, val, device=dev)  # noqa: E731
+    res = {}
+    if args.stages in STAGE_WORKLOADS:
+        B, T, H, K, V, delta, diag, stages = STAGE_WORKLOADS[args.stages]
+        nrm = torch.nn.functional.normalize
+        q = nrm(torch.randn(B, T, H, K, device=dev), dim=-1).bfloat16()
+        k = nrm(torch.randn(B, T, H, K, device=dev), dim=-1).bfloat16()
+        v = torch.randn(B, T, H, V, device=dev, dtype=torch.bfloat16)
+        g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, *((K,) if diag else ()), device=dev) + 3)
+        beta = torch.sigmoid(torch.randn(B, T, H, device=dev)) if delta else None
+        sc = {"q": f(H, val=K**-0.5 / 127), "k": f(H, val=1 / 127), "kw": f(H, K, val=1 / 127), "vw": f(H, V, val=4 / 127),
+              "vl": f(H, V, val=4 / 127), "state": f(H, V, val=2 / 127), "w": f(H, val=1 / 127), "el": f(H, V, val=4 / 127),
+              "ew": f(H, V, val=4 / 127)}
+        o, keep = torch.empty_like(v), []
+        P = _common.make_problem(q, k, v, g, beta, sc, decay=2 if diag else 1, eta=0.0 if diag else 1.0, sigma=0.5 if delta else 1.0,
+                                 tau=1.0, scale=K**-0.5, chunk_size=64, bits=8, out=o, final_state=None,
+                                 rot_signs=torch.ones(K, device=dev), dqk=(f(H, K) if (delta and not diag) else None), keep=keep)
+        ws = _cabi.Workspace(P, delta, dev)
+        for st in stages:
+            res[st] = _time_us(lambda: _common.run_stage(st, P, ws, q), args.steps)
+        ws.check_status()
+        tokens = B * T
+    elif args.stages == "mamba2_b2":
+        from linquant_b200.kernels.mamba2 import _ssd
+        from linquant_b200.kernels.mamba2 import ssd_combined as sc2
+
+        B, L, H, Pd, G, N, C = 2, 16384, 80, 64, 1, 128, 256
+        x = torch.randn(B, L, H, Pd, device=dev).half()
+        qB = torch.randint(-127, 128, (B, L, G, N), device=dev, dtype=torch.int8)
+        qC = torch.randint(-127, 128, (B, L, G, N), device=dev, dtype=torch.int8)
+        dtr, A_log = torch.randn(B, L, H, device=dev) * 0.5 - 2, torch.rand(H, device=dev) * 2.7
+        a_hp, s_g, s_hp, cbs, Dv = f(H, Pd, val=0.01), f(G, val=0.03), f(H, Pd, val=0.5), f(G, val=0.3), f(H)
+        dA, dt = sc2._quant_chunk_cumsum_fwd(dtr, 1.0, A_log, 1.0, C, None, True)
+        st = sc2._quant_chunk_state_fwd_xfp_static_int8(x, qB, dt, dA, a_hp, s_g, s_hp)
+        sp, _ = sc2._fixedpoint_state_passing_fwd(st.reshape(B, -1, H, Pd * N), dA[..., -1])
+        cb = sc2._quant_bmm_chunk_fwd(qC, s_g, qB, s_g, C, cbs)
+        spv = sp.reshape(B, -1, H, Pd, N)
+        ops = {
+            "chunk_cumsum": lambda: sc2._quant_chunk_cumsum_fwd(dtr, 1.0, A_log, 1.0, C, None, True),
+            "chunk_state (transpose + tcgen05)": lambda: sc2._quant_chunk_state_fwd_xfp_static_int8(x, qB, dt, dA, a_hp, s_g, s_hp),
+            "state_passing": lambda: sc2._fixedpoint_state_passing_fwd(st.reshape(B, -1, H, Pd * N), dA[..., -1]),
+            "bmm_chunk": lambda: sc2._quant_bmm_chunk_fwd(qC, s_g, qB, s_g, C, cbs),
+            "chunk_scan (warp_mma, default)": lambda: sc2._chunk_scan_v2(cb, x, dt, dA, qC, s_g, spv, Dv, 1.0, s_hp, cbs),
+            "chunk_scan (tcgen05)": lambda: sc2._chunk_scan_v2(cb, x, dt, dA, qC, s_g, spv, Dv, 1.0, s_hp, cbs, kernel="tcgen05"),
+        }
+        for name, fn in ops.items():
+            res[name] = _time_us(fn, args.steps)
+        _ssd.check_status(dev)
+        tokens = B * L
+    else:
+        raise SystemExit(f"--stages: unknown workload {args.stages}; one of {sorted(STAGE_WORKLOADS) + ['mamba2_b2']}")
+    total = sum(v for n, v in res.items() if "tcgen05)" not in n or "chunk_state" in n)
+    print(json.dumps({"stages": args.stages, "stage_us": {n: round(v, 1) for n, v in res.items()}, "default_path_us": round(total, 1),
+                      "Mtokens_per_s": round(tokens / total, 2)}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -326,7 +413,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernels-only", action="store_true",
                     help="device-resident stage loop only (no host-buffer leg, no CPU baseline): the command profiled by ncu")
+    ap.add_argument("--stages", default=None, metavar="WORKLOAD",
+                    help="per-kernel times of another workload (simple_gla, gated_deltanet, kda_b2, gla_b2, mamba2_b2) instead of the bench line")
     args = ap.parse_args()
+    if args.stages:
+        return run_stages(args)
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:  # plain `python bench.py --gpus N`: become N ranks
         os.execv(sys.executable, [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                                   "--master-addr", "127.0.0.1", "--master-port", "29517", os.path.abspath(__file__),

@@ -29,6 +29,20 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
   return __byte_perm(lo, hi, 0x5410);
 }
 
+// two int32 codes -> two saturated INT8 in the low half of the result, `upper` shifted into the high half
+// (cvt.pack.sat.s8.s32.b32 d, a, b, c:  d = sat8(a) << 8 | sat8(b) | c << 16)
+__device__ __forceinline__ uint32_t pack_sat_s8x2(int hi, int lo, uint32_t upper) {
+  uint32_t d;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;\n" : "=r"(d) : "r"(hi), "r"(lo), "r"(upper));
+  return d;
+}
+// Byte I of w, where w holds four INT8 codes XOR 0x80 (code + 128 as an unsigned byte), as an exact float: the byte
+// becomes the low mantissa bits of 2^23 and the offset is subtracted -- no trip through the conversion unit.
+template <int I>
+__device__ __forceinline__ float s8_to_float(uint32_t w_xor80) {
+  return __fsub_rn(__uint_as_float(__byte_perm(w_xor80, 0x4B000000u, 0x7540 | I)), 8388736.0f);
+}
+
 // ---- row orders of the two tiles that are B operands of the output contractions
 // The k_local tile and the stored-state tile are laid out so that MMA column n of the output kernel is simply row n
 // of the tile, while a thread's accumulator fragment still covers four consecutive tokens (k_local) or eight

@@ -509,10 +509,13 @@ __global__ void __launch_bounds__(256) ssd_chunk_scan_kernel(lq_ssd_problem p) {
         if (ks < mt) {
           const float4 t4 = *reinterpret_cast<const float4*>(tab + k0);
           const float tv[4] = {t4.x, t4.y, t4.z, t4.w};
+          const uint32_t ua = wa ^ 0x80808080u, ub = wb ^ 0x80808080u;
+          const float fa[4] = {s8_to_float<0>(ua), s8_to_float<1>(ua), s8_to_float<2>(ua), s8_to_float<3>(ua)};
+          const float fb[4] = {s8_to_float<0>(ub), s8_to_float<1>(ub), s8_to_float<2>(ub), s8_to_float<3>(ub)};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            va[e] = __fmul_rn(__fmul_rn((float)(int8_t)(wa >> (8 * e)), ea), tv[e]);
-            vb[e] = __fmul_rn(__fmul_rn((float)(int8_t)(wb >> (8 * e)), eb), tv[e]);
+            va[e] = __fmul_rn(__fmul_rn(fa[e], ea), tv[e]);
+            vb[e] = __fmul_rn(__fmul_rn(fb[e], eb), tv[e]);
           }
         } else {
 #pragma unroll

@@ -23,13 +23,6 @@
 
 namespace lq {
 
-// Byte i of w, where w holds four INT8 codes XOR 0x80 (i.e. code + 128 as an unsigned byte), as an exact float:
-// the byte becomes the low mantissa bits of 2^23 and the offset is subtracted (no integer-to-float conversion unit).
-template <int I>
-__device__ __forceinline__ float s8_to_float(uint32_t w_xor80) {
-  return __fsub_rn(__uint_as_float(__byte_perm(w_xor80, 0x4B000000u, 0x7540 | I)), 8388736.0f);
-}
-
 template <typename T>
 __global__ void __launch_bounds__(256) ssd_chunk_scan_tc_kernel(const __grid_constant__ CUtensorMap tm_qc,
                                                                 const __grid_constant__ CUtensorMap tm_s, lq_ssd_problem p,

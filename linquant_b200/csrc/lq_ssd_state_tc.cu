@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(128) ssd_chunk_state_tc_kernel(const __grid_co
     for (int i = 0; i < 4; ++i) gk[i] = s_gate[t0 + i];
 #pragma unroll
     for (int pg = 0; pg < 8; ++pg) {
-      uint32_t w0 = 0u, w1 = 0u;
+      int c0v[4], c1v[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const uint32_t raw = *reinterpret_cast<const uint32_t*>(s_raw + (t0 + i) * 128 + ((pg ^ tq) << 4) + 4 * cp);
@@ -104,11 +104,14 @@ __global__ void __launch_bounds__(128) ssd_chunk_state_tc_kernel(const __grid_co
         } else {
           x0 = __uint_as_float(raw << 16); x1 = __uint_as_float(raw & 0xffff0000u);
         }
-        const int c0 = ssd_half_away(__fmul_rn(__fmul_rn(x0, xinv[pg][0]), gk[i]), 127.f);
-        const int c1 = ssd_half_away(__fmul_rn(__fmul_rn(x1, xinv[pg][1]), gk[i]), 127.f);
-        w0 |= ((uint32_t)c0 & 0xffu) << (8 * i);
-        w1 |= ((uint32_t)c1 & 0xffu) << (8 * i);
+        // half away from zero; the lower clamp here, the upper one in the saturating pack below
+        const float y0 = fmaxf(__fmul_rn(__fmul_rn(x0, xinv[pg][0]), gk[i]), -127.f);
+        const float y1 = fmaxf(__fmul_rn(__fmul_rn(x1, xinv[pg][1]), gk[i]), -127.f);
+        c0v[i] = __float2int_rz(__fadd_rn(y0, copysignf(0.5f, y0)));
+        c1v[i] = __float2int_rz(__fadd_rn(y1, copysignf(0.5f, y1)));
       }
+      const uint32_t w0 = pack_sat_s8x2(c0v[1], c0v[0], pack_sat_s8x2(c0v[3], c0v[2], 0u));
+      const uint32_t w1 = pack_sat_s8x2(c1v[1], c1v[0], pack_sat_s8x2(c1v[3], c1v[2], 0u));
       const int r0 = 2 * cp, r1 = 2 * cp + 1;  // row within the 8-row group pg
       uint8_t* grp8 = s_A + kb * 8192 + pg * 1024;
       *reinterpret_cast<uint32_t*>(grp8 + r0 * 128 + ((ch16 ^ r0) << 4) + off) = w0;

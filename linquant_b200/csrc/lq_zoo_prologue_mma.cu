@@ -16,11 +16,7 @@
 
 namespace lq {
 
-__device__ __forceinline__ uint32_t pack_sat2(int hi, int lo, uint32_t upper) {
-  uint32_t d;
-  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;\n" : "=r"(d) : "r"(hi), "r"(lo), "r"(upper));
-  return d;
-}
+__device__ __forceinline__ uint32_t pack_sat2(int hi, int lo, uint32_t upper) { return pack_sat_s8x2(hi, lo, upper); }
 // code before the final saturation: with Q127 the upper clamp is left to the saturating pack
 template <bool Q127>
 __device__ __forceinline__ int code32(float x, float inv, float qmax) {
