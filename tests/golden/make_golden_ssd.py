@@ -29,7 +29,9 @@ import triton
 import triton.language as tl
 
 assert os.environ.get("TRITON_INTERPRET") == "1", "run with TRITON_INTERPRET=1"
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: TRITON_INTERPRET=1 python tests/golden/make_golden_ssd.py /path/to/reference")
+REF = sys.argv[1]
 sys.path.insert(0, REF)
 torch.cuda.device = lambda *a, **k: contextlib.nullcontext()
 import triton.runtime.autotuner as _ta  # noqa: E402
