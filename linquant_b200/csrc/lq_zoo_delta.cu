@@ -77,16 +77,23 @@ __global__ void __launch_bounds__(256) zoo_prologue_delta_kernel(DeltaPrepArgs d
   }
   __syncthreads();
 
-  prologue_qk_rows<T, K>(a, b, c, h, tile, s_fk, e_hw != 0.f ? s_hw : nullptr, s_kf, LDK, s_kw);
-  {
-    const T* vp = reinterpret_cast<const T*>(a.v);
-    for (int i = tid; i < C * (V / 8); i += 256) {
-      const int t = i / (V / 8), seg = i % (V / 8);
-      float x[8];
-      Act<T>::unpack8(*reinterpret_cast<const uint4*>(vp + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * V + 8 * seg), x);
+  // the v rows are requested before the q / k rows are processed, and staged afterwards
+  const T* vp = reinterpret_cast<const T*>(a.v);
+  constexpr int NV = C * (V / 8) / 256;
+  uint4 rv[NV];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) s_vf[t * LDV + 8 * seg + e] = x[e];
-    }
+  for (int u = 0; u < NV; ++u) {
+    const int i = tid + 256 * u, t = i / (V / 8), seg = i % (V / 8);
+    rv[u] = __ldg(reinterpret_cast<const uint4*>(vp + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * V + 8 * seg));
+  }
+  prologue_qk_rows<T, K>(a, b, c, h, tile, s_fk, e_hw != 0.f ? s_hw : nullptr, s_kf, LDK, s_kw);
+#pragma unroll
+  for (int u = 0; u < NV; ++u) {
+    const int i = tid + 256 * u, t = i / (V / 8), seg = i % (V / 8);
+    float x[8];
+    Act<T>::unpack8(rv[u], x);
+    *reinterpret_cast<float4*>(s_vf + t * LDV + 8 * seg) = make_float4(x[0], x[1], x[2], x[3]);
+    *reinterpret_cast<float4*>(s_vf + t * LDV + 8 * seg + 4) = make_float4(x[4], x[5], x[6], x[7]);
   }
   __syncthreads();
 

@@ -69,14 +69,22 @@ __device__ __forceinline__ void prologue_qk_rows(const PrologueArgs& a, int b, i
     uint32_t kwp[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) kwp[j] = 0u;
+    // all eight row loads of the group are in flight before the first is used (the code stores below would
+    // otherwise order them one DRAM round trip after another)
+    uint4 rq[4], rk[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const size_t row = (((size_t)b * a.T + (size_t)c * C + 4 * tg + i) * a.H + h) * K + 8 * r;
+      rq[i] = __ldg(reinterpret_cast<const uint4*>(qp + row));
+      rk[i] = __ldg(reinterpret_cast<const uint4*>(kp + row));
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int t = 4 * tg + i;
-      const size_t row = (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K + 8 * r;
       const size_t orow = (tile * C + t) * K + 8 * r;
       float x[8];
       int cd[8];
-      Act<T>::unpack8(*reinterpret_cast<const uint4*>(qp + row), x);
+      Act<T>::unpack8(rq[i], x);
       if (a.dqk) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(x[j], dmul[j]);
@@ -90,7 +98,7 @@ __device__ __forceinline__ void prologue_qk_rows(const PrologueArgs& a, int b, i
       for (int j = 0; j < 8; ++j) cd[j] = q8(__fmul_rn(x[j], a.scale), inv_sq, a.qmax);
       *reinterpret_cast<uint2*>(a.qq + orow) =
           make_uint2(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4], cd[5], cd[6], cd[7]));
-      Act<T>::unpack8(*reinterpret_cast<const uint4*>(kp + row), x);
+      Act<T>::unpack8(rk[i], x);
       if (a.dqk) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(x[j], dinv[j]);
