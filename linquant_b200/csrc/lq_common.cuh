@@ -113,11 +113,11 @@ __device__ __forceinline__ void fwht8(float (&x)[8], int r) {
   }
 #pragma unroll
   for (int m = 1; m < LPR; m <<= 1) {
-    const bool upper = (r & m) != 0;
+    const float s = (r & m) ? -1.0f : 1.0f;  // upper half of the butterfly: other - x, lower: x + other (one fma, exact)
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       float other = __shfl_xor_sync(0xffffffffu, x[i], m);
-      x[i] = upper ? (other - x[i]) : (x[i] + other);
+      x[i] = fmaf(x[i], s, other);
     }
   }
 }

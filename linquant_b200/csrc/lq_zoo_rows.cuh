@@ -67,8 +67,6 @@ __device__ __forceinline__ void prologue_qk_rows(const PrologueArgs& a, int b, i
   const T* kp = reinterpret_cast<const T*>(a.k);
   for (int tg = warp * G + grp; tg < C / 4; tg += nwarps * G) {
     uint32_t kwp[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) kwp[j] = 0u;
     // all eight row loads of the group are in flight before the first is used (the code stores below would
     // otherwise order them one DRAM round trip after another)
     uint4 rq[4], rk[4];
@@ -78,8 +76,12 @@ __device__ __forceinline__ void prologue_qk_rows(const PrologueArgs& a, int b, i
       rq[i] = __ldg(reinterpret_cast<const uint4*>(qp + row));
       rk[i] = __ldg(reinterpret_cast<const uint4*>(kp + row));
     }
+    // tokens in the order 2, 3, 0, 1: the saturating pack takes two codes and an upper half, so the pair (2,3) is
+    // packed first and rides along as the upper half when the pair (0,1) is packed
+    int kprev[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int ii = 0; ii < 4; ++ii) {
+      const int i = (ii + 2) & 3;
       const int t = 4 * tg + i;
       const size_t orow = (tile * C + t) * K + 8 * r;
       float x[8];
@@ -123,8 +125,11 @@ __device__ __forceinline__ void prologue_qk_rows(const PrologueArgs& a, int b, i
           make_uint2(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4], cd[5], cd[6], cd[7]));
       const float fk = s_fk[t];
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        kwp[j] |= ((uint32_t)q8(__fmul_rn(x[j], fk), inv_kw[j], a.qmax) & 0xffu) << (8 * i);
+      for (int j = 0; j < 8; ++j) {
+        const int cw = q8(__fmul_rn(x[j], fk), inv_kw[j], a.qmax);
+        if (i & 1) kwp[j] = pack_sat_s8x2(cw, kprev[j], i == 3 ? 0u : kwp[j]);
+        else kprev[j] = cw;
+      }
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) s_kw[8 * r + j][tg] = kwp[j];
