@@ -16,8 +16,6 @@
 //
 // Reference arithmetic: zoo/gated_delta_rule.py:20-47 (_prep), :51-115 (_delta_state_body);
 // reference.py:202-229 (_chunk_delta).
-#include <type_traits>
-
 #include "lq_wy.cuh"
 #include "lq_zoo_rows.cuh"
 
@@ -184,12 +182,8 @@ __device__ __forceinline__ int swz_row(int row, int chunk) {
   return row * 64 + (chunk << 4);
 }
 
-// Eight warps per CTA. In the read phase (ws = W . S, E, codes) warp w covers tokens 16 (w & 3) .. + 15 and the value
-// channels of half w >> 2; in the write phase (carry update) and in the stored-state phase it covers the value m-tile
-// w >> 2 (16 channels) and the key quarter w & 3. Each phase therefore gives a thread half the work a four-warp CTA
-// would, which shortens the serial step from chunk to chunk.
 template <typename T, int K, int V, bool DIAG>
-__global__ void __launch_bounds__(256) zoo_state_delta_kernel(DeltaStateArgs a) {
+__global__ void __launch_bounds__(128) zoo_state_delta_kernel(DeltaStateArgs a) {
   constexpr int C = 64, BV = 32;
   constexpr int NTK = K / 32;  // key n-tiles per warp in the carry layout
   constexpr int KK = K / 64;
@@ -201,30 +195,27 @@ __global__ void __launch_bounds__(256) zoo_state_delta_kernel(DeltaStateArgs a) 
   const int bh = blockIdx.y, h = bh % a.H;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, j = lane & 3;
-  const int tw = warp & 3, vh = warp >> 2;   // read phase: token block, value half
-  const int kq = warp & 3, mt = warp >> 2;   // write phase: key quarter, value m-tile
-  const int kw0 = kq * (K / 4);
+  const int kw0 = warp * (K / 4);
   const int kown = kw0 + 2 * NTK * j;  // first of the 2*NTK consecutive key channels this thread owns
 
-  // carry rows (value channels 16 mt + g and + 8, local index) and their scales
-  float sew_r[2], iss_r[2];
+  // carry rows (value channels, local index) and their scales
+  float sew_r[4], iss_r[4];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int vl = 16 * mt + g + 8 * i;
+  for (int i = 0; i < 4; ++i) {
+    const int vl = 16 * (i >> 1) + g + 8 * (i & 1);
     sew_r[i] = a.sew[h * V + v0 + vl];
     iss_r[i] = 1.0f / a.ss[h * V + v0 + vl];
   }
   float skw[2 * NTK];
 #pragma unroll
   for (int i = 0; i < 2 * NTK; ++i) skw[i] = a.skw[h * K + kown + i];
-  // E columns: four consecutive value channels v0 + 8j + 4vh .. + 3
-  const int vc0 = 8 * j + 4 * vh;
-  float ss_c[4], isel_c[4], isew_c[4];
+  // E columns: eight consecutive value channels v0 + 8j .. + 7
+  float ss_c[8], isel_c[8], isew_c[8];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    ss_c[i] = a.ss[h * V + v0 + vc0 + i];
-    isel_c[i] = 1.0f / a.sel[h * V + v0 + vc0 + i];
-    isew_c[i] = 1.0f / a.sew[h * V + v0 + vc0 + i];
+  for (int i = 0; i < 8; ++i) {
+    ss_c[i] = a.ss[h * V + v0 + 8 * j + i];
+    isel_c[i] = 1.0f / a.sel[h * V + v0 + 8 * j + i];
+    isew_c[i] = 1.0f / a.sew[h * V + v0 + 8 * j + i];
   }
   const float sw = a.sw[h];
 
@@ -233,17 +224,18 @@ __global__ void __launch_bounds__(256) zoo_state_delta_kernel(DeltaStateArgs a) 
   for (int nt = 0; nt < NTK; ++nt) krow[nt] = kw0 + 2 * NTK * (g >> 1) + 2 * nt + (g & 1);
 
   const size_t base_tile = (size_t)bh * a.NT;
-  const int ta = 16 * tw + g, tb = ta + 8;
+  const int ta = 16 * warp + g, tb = ta + 8;
   const T* up = reinterpret_cast<const T*>(a.u);
 
-  float carry[NTK][4];
+  float carry[2][NTK][4];
 #pragma unroll
-  for (int nt = 0; nt < NTK; ++nt) carry[nt][0] = carry[nt][1] = carry[nt][2] = carry[nt][3] = 0.f;
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NTK; ++nt) carry[mt][nt][0] = carry[mt][nt][1] = carry[mt][nt][2] = carry[mt][nt][3] = 0.f;
 
-  uint4 wa[KK], wb[KK], kb[NTK];
-  uint2 ua, ub;
+  uint4 wa[KK], wb[KK], ua, ub, kb[NTK];
   float fwa, fwb, gca, gcb, glast;
-  auto fetch = [&](int c, uint4 (&wa_)[KK], uint4 (&wb_)[KK], uint2& ua_, uint2& ub_, uint4 (&kb_)[NTK], float& fwa_,
+  auto fetch = [&](int c, uint4 (&wa_)[KK], uint4 (&wb_)[KK], uint4& ua_, uint4& ub_, uint4 (&kb_)[NTK], float& fwa_,
                    float& fwb_, float& gca_, float& gcb_, float& gl_) {
     const size_t tile = base_tile + c;
     const int8_t* wqc = a.wq + tile * (size_t)(C * K);
@@ -252,8 +244,8 @@ __global__ void __launch_bounds__(256) zoo_state_delta_kernel(DeltaStateArgs a) 
       wa_[kk] = __ldg(reinterpret_cast<const uint4*>(wqc + ta * K + 64 * kk + 16 * j));
       wb_[kk] = __ldg(reinterpret_cast<const uint4*>(wqc + tb * K + 64 * kk + 16 * j));
     }
-    ua_ = __ldg(reinterpret_cast<const uint2*>(up + (tile * C + ta) * V + v0 + vc0));
-    ub_ = __ldg(reinterpret_cast<const uint2*>(up + (tile * C + tb) * V + v0 + vc0));
+    ua_ = __ldg(reinterpret_cast<const uint4*>(up + (tile * C + ta) * V + v0 + 8 * j));
+    ub_ = __ldg(reinterpret_cast<const uint4*>(up + (tile * C + tb) * V + v0 + 8 * j));
     const int8_t* kwc = a.kwT + tile * (size_t)(K * C);
 #pragma unroll
     for (int nt = 0; nt < NTK; ++nt) kb_[nt] = __ldg(reinterpret_cast<const uint4*>(kwc + krow[nt] * C + 16 * j));
@@ -273,8 +265,7 @@ __global__ void __launch_bounds__(256) zoo_state_delta_kernel(DeltaStateArgs a) 
 
   for (int c = 0; c < a.NT; ++c) {
     const size_t tile = base_tile + c;
-    uint4 nwa[KK], nwb[KK], nkb[NTK];
-    uint2 nua = ua, nub = ub;
+    uint4 nwa[KK], nwb[KK], nua = ua, nub = ub, nkb[NTK];
     float nfwa = 0.f, nfwb = 0.f, ngca = 0.f, ngcb = 0.f, ngl = 0.f;
 #pragma unroll
     for (int kk = 0; kk < KK; ++kk) { nwa[kk] = wa[kk]; nwb[kk] = wb[kk]; }
@@ -286,13 +277,14 @@ __global__ void __launch_bounds__(256) zoo_state_delta_kernel(DeltaStateArgs a) 
     {
       int8_t* hc = a.hT + tile * (size_t)(V * K);
 #pragma unroll
-      for (int hi = 0; hi < 2; ++hi) {
+      for (int i = 0; i < 4; ++i) {
+        const int mt = i >> 1, hi = i & 1;
         const int vl = 16 * mt + g + 8 * hi;
         int cd[2 * NTK];
 #pragma unroll
         for (int nt = 0; nt < NTK; ++nt) {
-          cd[2 * nt] = q8(carry[nt][2 * hi], iss_r[hi], 127.f);
-          cd[2 * nt + 1] = q8(carry[nt][2 * hi + 1], iss_r[hi], 127.f);
+          cd[2 * nt] = q8(carry[mt][nt][2 * hi], iss_r[i], 127.f);
+          cd[2 * nt + 1] = q8(carry[mt][nt][2 * hi + 1], iss_r[i], 127.f);
         }
         uint8_t* sdst = s_h + swz_row<K>(vl, kown >> 4) + (kown & 15);
         int8_t* gdst = hc + (size_t)state_row_of_channel(v0 + vl) * K + kown;
@@ -310,43 +302,33 @@ __global__ void __launch_bounds__(256) zoo_state_delta_kernel(DeltaStateArgs a) 
     }
     __syncthreads();
 
-    // ---- 2. ws = wq . hq ; E ; e_local / e_write codes (tokens of block tw, value half vh)
+    // ---- 2. ws = wq . hq ; E ; e_local / e_write codes
     {
-      int acc[2][4];
+      int acc[4][4];
 #pragma unroll
-      for (int n2 = 0; n2 < 2; ++n2) {
-        const int nt = 2 * vh + n2;
-        acc[n2][0] = acc[n2][1] = acc[n2][2] = acc[n2][3] = 0;
+      for (int nt = 0; nt < 4; ++nt) {
+        acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0;
         const int vr = 8 * (g >> 1) + 2 * nt + (g & 1);
 #pragma unroll
         for (int kk = 0; kk < KK; ++kk) {
           const uint4 bs = *reinterpret_cast<const uint4*>(s_h + swz_row<K>(vr, 4 * kk + j));
-          mma_s8(acc[n2], wa[kk].x, wb[kk].x, wa[kk].y, wb[kk].y, bs.x, bs.y);
-          mma_s8(acc[n2], wa[kk].z, wb[kk].z, wa[kk].w, wb[kk].w, bs.z, bs.w);
+          mma_s8(acc[nt], wa[kk].x, wb[kk].x, wa[kk].y, wb[kk].y, bs.x, bs.y);
+          mma_s8(acc[nt], wa[kk].z, wb[kk].z, wa[kk].w, wb[kk].w, bs.z, bs.w);
         }
       }
-      float Ua[4], Ub[4];
-      if (std::is_same<T, __half>::value) {
-        const float2 a0 = __half22float2(*reinterpret_cast<const __half2*>(&ua.x)), a1 = __half22float2(*reinterpret_cast<const __half2*>(&ua.y));
-        const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&ub.x)), b1 = __half22float2(*reinterpret_cast<const __half2*>(&ub.y));
-        Ua[0] = a0.x; Ua[1] = a0.y; Ua[2] = a1.x; Ua[3] = a1.y;
-        Ub[0] = b0.x; Ub[1] = b0.y; Ub[2] = b1.x; Ub[3] = b1.y;
-      } else {
-        Ua[0] = __uint_as_float(ua.x << 16); Ua[1] = __uint_as_float(ua.x & 0xffff0000u);
-        Ua[2] = __uint_as_float(ua.y << 16); Ua[3] = __uint_as_float(ua.y & 0xffff0000u);
-        Ub[0] = __uint_as_float(ub.x << 16); Ub[1] = __uint_as_float(ub.x & 0xffff0000u);
-        Ub[2] = __uint_as_float(ub.y << 16); Ub[3] = __uint_as_float(ub.y & 0xffff0000u);
-      }
+      float Ua[8], Ub[8];
+      Act<T>::unpack8(ua, Ua);
+      Act<T>::unpack8(ub, Ub);
       const float fva = DIAG ? expf(a.eta * gca) : (a.use_g ? expf(a.eta * (glast - gca)) : 1.f);
       const float fvb = DIAG ? expf(a.eta * gcb) : (a.use_g ? expf(a.eta * (glast - gcb)) : 1.f);
 #pragma unroll
-      for (int n2 = 0; n2 < 2; ++n2) {
+      for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const int i = 2 * n2 + e;
-          const int vl = vc0 + i;
-          const float wsa = __fmul_rn(__fmul_rn((float)acc[n2][e], sw), ss_c[i]);
-          const float wsb = __fmul_rn(__fmul_rn((float)acc[n2][2 + e], sw), ss_c[i]);
+          const int i = 2 * nt + e;
+          const int vl = 8 * j + i;
+          const float wsa = __fmul_rn(__fmul_rn((float)acc[nt][e], sw), ss_c[i]);
+          const float wsb = __fmul_rn(__fmul_rn((float)acc[nt][2 + e], sw), ss_c[i]);
           const float Ea = __fmul_rn(__fsub_rn(Ua[i], wsa), fwa);
           const float Eb = __fmul_rn(__fsub_rn(Ub[i], wsb), fwb);
           s_el[vl * C + ta] = (uint8_t)q8(Act<T>::round(Ea), isel_c[i], a.qmax);
@@ -358,10 +340,9 @@ __global__ void __launch_bounds__(256) zoo_state_delta_kernel(DeltaStateArgs a) 
     }
     __syncthreads();
 
-    // ---- 3. write product and carry update (value m-tile mt, key quarter kq); e_local tile out
+    // ---- 3. write product and carry update; e_local tile out
     {
-      if (tid < BV * C / 16)
-        reinterpret_cast<uint4*>(a.elT + tile * (size_t)(V * C) + (size_t)v0 * C)[tid] = reinterpret_cast<const uint4*>(s_el)[tid];
+      reinterpret_cast<uint4*>(a.elT + tile * (size_t)(V * C) + (size_t)v0 * C)[tid] = reinterpret_cast<const uint4*>(s_el)[tid];
       float gamv[2 * NTK];
       if (DIAG) {
 #pragma unroll
@@ -371,19 +352,22 @@ __global__ void __launch_bounds__(256) zoo_state_delta_kernel(DeltaStateArgs a) 
 #pragma unroll
         for (int i = 0; i < 2 * NTK; ++i) gamv[i] = gs;
       }
-      const uint4 ea = *reinterpret_cast<const uint4*>(s_ew + (16 * mt + g) * C + 16 * j);
-      const uint4 eb = *reinterpret_cast<const uint4*>(s_ew + (16 * mt + g + 8) * C + 16 * j);
 #pragma unroll
-      for (int nt = 0; nt < NTK; ++nt) {
-        int acc[4] = {0, 0, 0, 0};
-        mma_s8(acc, ea.x, eb.x, ea.y, eb.y, kb[nt].x, kb[nt].y);
-        mma_s8(acc, ea.z, eb.z, ea.w, eb.w, kb[nt].z, kb[nt].w);
+      for (int mt = 0; mt < 2; ++mt) {
+        const uint4 ea = *reinterpret_cast<const uint4*>(s_ew + (16 * mt + g) * C + 16 * j);
+        const uint4 eb = *reinterpret_cast<const uint4*>(s_ew + (16 * mt + g + 8) * C + 16 * j);
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const float ta_ = __fmul_rn(__fmul_rn((float)acc[e], skw[2 * nt + e]), sew_r[0]);
-          const float tb_ = __fmul_rn(__fmul_rn((float)acc[2 + e], skw[2 * nt + e]), sew_r[1]);
-          carry[nt][e] = fmaf(carry[nt][e], gamv[2 * nt + e], ta_);
-          carry[nt][2 + e] = fmaf(carry[nt][2 + e], gamv[2 * nt + e], tb_);
+        for (int nt = 0; nt < NTK; ++nt) {
+          int acc[4] = {0, 0, 0, 0};
+          mma_s8(acc, ea.x, eb.x, ea.y, eb.y, kb[nt].x, kb[nt].y);
+          mma_s8(acc, ea.z, eb.z, ea.w, eb.w, kb[nt].z, kb[nt].w);
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float ta_ = __fmul_rn(__fmul_rn((float)acc[e], skw[2 * nt + e]), sew_r[2 * mt]);
+            const float tb_ = __fmul_rn(__fmul_rn((float)acc[2 + e], skw[2 * nt + e]), sew_r[2 * mt + 1]);
+            carry[mt][nt][e] = fmaf(carry[mt][nt][e], gamv[2 * nt + e], ta_);
+            carry[mt][nt][2 + e] = fmaf(carry[mt][nt][2 + e], gamv[2 * nt + e], tb_);
+          }
         }
       }
     }
@@ -397,13 +381,15 @@ __global__ void __launch_bounds__(256) zoo_state_delta_kernel(DeltaStateArgs a) 
   if (a.final_state != nullptr) {
     float* fs = a.final_state + (size_t)bh * K * V;
 #pragma unroll
-    for (int nt = 0; nt < NTK; ++nt)
+    for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int kk_ = kown + 2 * nt + e;
-        fs[(size_t)kk_ * V + v0 + 16 * mt + g] = carry[nt][e];
-        fs[(size_t)kk_ * V + v0 + 16 * mt + g + 8] = carry[nt][2 + e];
-      }
+      for (int nt = 0; nt < NTK; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int kk_ = kown + 2 * nt + e;
+          fs[(size_t)kk_ * V + v0 + 16 * mt + g] = carry[mt][nt][e];
+          fs[(size_t)kk_ * V + v0 + 16 * mt + g + 8] = carry[mt][nt][2 + e];
+        }
   }
 }
 
@@ -440,7 +426,7 @@ int run_prologue_delta(const lq_zoo_problem* p, const lq_zoo_workspace* ws, cuda
 
 template <typename T>
 static int dispatch_delta_state(const lq_zoo_problem* p, const DeltaStateArgs& a, cudaStream_t st) {
-  dim3 grid(p->V / 32, p->B * p->H), block(256);
+  dim3 grid(p->V / 32, p->B * p->H), block(128);
   const bool diag = p->decay == LQ_DECAY_DIAGONAL;
 #define LQ_LAUNCH_DSTATE(KK_, VV_)                                                         \
   if (diag) zoo_state_delta_kernel<T, KK_, VV_, true><<<grid, block, 0, st>>>(a);          \
