@@ -72,8 +72,8 @@ typedef struct {
   const float* initial_state; /* [B,H,K,V] fp32 carry entering the first chunk (linear family), or null = zero */
   const void* unrot_t;        /* canonical storage under a value rotation (the reference's unrot=, zoo/simple_gla.py:31-33,
                                  :150-153): [V,V] fp16, TRANSPOSED, element [v'][v] = unrot[v][v']; v arrives rotated and
-                                 every value-side product is multiplied by unrot before it joins the carry / the output.
-                                 Linear family only; null = off */
+                                 every value-side product is multiplied by unrot before it joins the carry / the output
+                                 (the delta family also takes the state read into the rotated basis); null = off */
 } lq_zoo_problem;
 
 /* Bytes of workspace the zoo entries need for this problem (a host-side computation). */

@@ -16,6 +16,8 @@
 //
 // Reference arithmetic: zoo/gated_delta_rule.py:20-47 (_prep), :51-115 (_delta_state_body);
 // reference.py:202-229 (_chunk_delta).
+#include <type_traits>
+
 #include "lq_wy.cuh"
 #include "lq_zoo_rows.cuh"
 
@@ -393,6 +395,255 @@ __global__ void __launch_bounds__(128) zoo_state_delta_kernel(DeltaStateArgs a) 
   }
 }
 
+// ------------------------------------------------------------------------------------------------ state pass, canonical storage
+// Delta-rule state pass when v arrives rotated by R_V and the state is stored canonical (zoo/gated_delta_rule.py,
+// zoo/kda.py with unrot=; reference.py:218-227). Per chunk:
+//   ws   = fp16(dequant(W_q . S_q)) . R_V            the canonical state read, taken into the rotated value basis
+//   E    = (U - ws) * fw,   e_local / e_write codes   (E stays rotated)
+//   carry <- gamma carry + fp16(dequant(kw_q^T . ew_q)) . R_V^T     the write product, un-rotated
+// Both basis changes mix all value channels and the read contracts over all key channels, so one CTA owns the whole
+// K x V state of a (batch, head): eight warps, warp w keeping key rows 16w .. 16w+15 x all value channels of the fp32
+// carry in the accumulator layout of the un-rotation MMA. The fp16 products go through shared memory; R_V and R_V^T
+// both sit in shared memory with the contraction index contiguous. This path trades parallelism (B*H CTAs) for
+// exactness of the reference's rounding points.
+template <typename T, int K, int V, bool DIAG>
+__global__ void __launch_bounds__(256) zoo_state_delta_unrot_kernel(DeltaStateArgs a, const __half* unrot_t) {
+  constexpr int C = 64, LDH = V + 8, KK = K / 64, KW = K / 16;
+  constexpr int NT2 = V / 16;                 // value n-tiles per warp in the read phase (two value halves)
+  constexpr int MTV = V / 16, NHALF = 8 / MTV, NTW = (K / 8) / NHALF;  // write product: value m-tile, key n-tiles per warp
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  uint8_t* s_h = smem_raw;                                   // [V][K]   INT8 state, B operand of the read
+  uint8_t* s_ew = s_h + V * K;                               // [V][C]   e_write codes (token index contiguous)
+  uint8_t* s_el = s_ew + V * C;                              // [V][C]   e_local codes
+  uint8_t* s_kw = s_el + V * C;                              // [K][C]   k_write codes of the chunk
+  __half* s_r = reinterpret_cast<__half*>(s_kw + K * C);     // [V][LDH] unrot   : B operand of the read rotation (rows v', v contiguous)
+  __half* s_rt = s_r + V * LDH;                              // [V][LDH] unrot^T : B operand of the write un-rotation
+  __half* s_x = s_rt + V * LDH;                              // [K][LDH] fp16 products: ws [64][LDH], then the write product [K][LDH]
+  float* s_ss = reinterpret_cast<float*>(s_x + K * LDH);     // [V] state scale, then 1/state, 1/sel, 1/sew, sew
+  float* s_iss = s_ss + V;
+  float* s_isel = s_iss + V;
+  float* s_isew = s_isel + V;
+  float* s_sew = s_isew + V;
+  float* s_skw = s_sew + V;                                  // [K]
+
+  const int bh = blockIdx.x, h = bh % a.H;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, j = lane & 3;
+  const int tw = warp & 3, vh = warp >> 2;
+  const int ta = 16 * tw + g, tb = ta + 8;
+  const int ka = 16 * warp + g, kb_ = ka + 8;   // carry rows (warps below KW)
+  const bool owner = warp < KW;
+
+  for (int i = tid; i < V * (V / 8); i += 256) {
+    const int row = i / (V / 8), ch = i % (V / 8);
+    const uint4 w = __ldg(reinterpret_cast<const uint4*>(unrot_t + (size_t)row * V) + ch);
+    *reinterpret_cast<uint4*>(s_rt + row * LDH + 8 * ch) = w;
+    const __half* hv = reinterpret_cast<const __half*>(&w);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s_r[(8 * ch + e) * LDH + row] = hv[e];  // transposed copy
+  }
+  for (int i = tid; i < V; i += 256) {
+    s_ss[i] = a.ss[h * V + i];
+    s_iss[i] = 1.0f / a.ss[h * V + i];
+    s_isel[i] = 1.0f / a.sel[h * V + i];
+    s_isew[i] = 1.0f / a.sew[h * V + i];
+    s_sew[i] = a.sew[h * V + i];
+  }
+  for (int i = tid; i < K; i += 256) s_skw[i] = a.skw[h * K + i];
+  const float sw = a.sw[h];
+  const size_t base_tile = (size_t)bh * a.NT;
+  const T* up = reinterpret_cast<const T*>(a.u);
+
+  float carry[V / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < V / 8; ++nt) carry[nt][0] = carry[nt][1] = carry[nt][2] = carry[nt][3] = 0.f;
+
+  auto stage_kw = [&](int c) {
+    const int8_t* kwc = a.kwT + (base_tile + c) * (size_t)(K * C);
+    for (int i = tid; i < K * C / 16; i += 256) cp_async16(s_kw + 16 * i, kwc + 16 * i);
+    cp_async_commit();
+  };
+  stage_kw(0);
+  __syncthreads();
+
+  for (int c = 0; c < a.NT; ++c) {
+    const size_t tile = base_tile + c;
+    // operands of the read phase (token rows ta, tb)
+    uint4 wa[KK], wb[KK];
+    {
+      const int8_t* wqc = a.wq + tile * (size_t)(C * K);
+#pragma unroll
+      for (int kk = 0; kk < KK; ++kk) {
+        wa[kk] = __ldg(reinterpret_cast<const uint4*>(wqc + ta * K + 64 * kk + 16 * j));
+        wb[kk] = __ldg(reinterpret_cast<const uint4*>(wqc + tb * K + 64 * kk + 16 * j));
+      }
+    }
+    const float fwa = __ldg(a.fw + tile * C + ta), fwb = __ldg(a.fw + tile * C + tb);
+    float gca, gcb, glast = 0.f;
+    if (DIAG) {
+      gca = __ldg(a.genv + tile * C + ta);
+      gcb = __ldg(a.genv + tile * C + tb);
+    } else {
+      gca = a.use_g ? __ldg(a.gc + tile * C + ta) : 0.f;
+      gcb = a.use_g ? __ldg(a.gc + tile * C + tb) : 0.f;
+      glast = a.use_g ? __ldg(a.gc + tile * C + C - 1) : 0.f;
+    }
+
+    // ---- 1. INT8 copy of the canonical carry entering the chunk
+    if (owner) {
+#pragma unroll
+      for (int nt = 0; nt < V / 8; ++nt) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int vc = 8 * nt + 2 * j + (i & 1), kr = (i >> 1) ? kb_ : ka;
+          s_h[swz_row<K>(vc, kr >> 4) + (kr & 15)] = (uint8_t)q8(carry[nt][i], s_iss[vc], 127.f);
+        }
+      }
+    }
+    __syncthreads();
+    {
+      int8_t* hc = a.hT + tile * (size_t)(V * K);
+      for (int i = tid; i < V * (K / 16); i += 256) {
+        const int vr = i / (K / 16), ch = i % (K / 16);
+        *reinterpret_cast<uint4*>(hc + (size_t)state_row_of_channel(vr) * K + 16 * ch) =
+            *reinterpret_cast<const uint4*>(s_h + swz_row<K>(vr, ch));
+      }
+    }
+
+    // ---- 2. ws = wq . hq, dequantised, fp16, token-major
+    {
+#pragma unroll
+      for (int n2 = 0; n2 < NT2; ++n2) {
+        const int nt = NT2 * vh + n2;
+        int acc[4] = {0, 0, 0, 0};
+        const int vr = 8 * nt + g;
+#pragma unroll
+        for (int kk = 0; kk < KK; ++kk) {
+          const uint4 bs = *reinterpret_cast<const uint4*>(s_h + swz_row<K>(vr, 4 * kk + j));
+          mma_s8(acc, wa[kk].x, wb[kk].x, wa[kk].y, wb[kk].y, bs.x, bs.y);
+          mma_s8(acc, wa[kk].z, wb[kk].z, wa[kk].w, wb[kk].w, bs.z, bs.w);
+        }
+        const int vc = 8 * nt + 2 * j;
+        const float s0 = s_ss[vc], s1 = s_ss[vc + 1];
+        *reinterpret_cast<uint32_t*>(s_x + ta * LDH + vc) =
+            Act<__half>::pack2(__fmul_rn(__fmul_rn((float)acc[0], sw), s0), __fmul_rn(__fmul_rn((float)acc[1], sw), s1));
+        *reinterpret_cast<uint32_t*>(s_x + tb * LDH + vc) =
+            Act<__half>::pack2(__fmul_rn(__fmul_rn((float)acc[2], sw), s0), __fmul_rn(__fmul_rn((float)acc[3], sw), s1));
+      }
+    }
+    __syncthreads();
+
+    // ---- 3. read rotation, E, codes
+    {
+      const float fva = DIAG ? expf(a.eta * gca) : (a.use_g ? expf(a.eta * (glast - gca)) : 1.f);
+      const float fvb = DIAG ? expf(a.eta * gcb) : (a.use_g ? expf(a.eta * (glast - gcb)) : 1.f);
+#pragma unroll
+      for (int n2 = 0; n2 < NT2; ++n2) {
+        const int nt = NT2 * vh + n2;
+        float u[4] = {0.f, 0.f, 0.f, 0.f};
+        const __half* brow = s_r + (8 * nt + g) * LDH;
+#pragma unroll
+        for (int kk = 0; kk < V / 16; ++kk) {
+          const uint32_t a0 = *reinterpret_cast<const uint32_t*>(s_x + ta * LDH + 16 * kk + 2 * j);
+          const uint32_t a1 = *reinterpret_cast<const uint32_t*>(s_x + tb * LDH + 16 * kk + 2 * j);
+          const uint32_t a2 = *reinterpret_cast<const uint32_t*>(s_x + ta * LDH + 16 * kk + 8 + 2 * j);
+          const uint32_t a3 = *reinterpret_cast<const uint32_t*>(s_x + tb * LDH + 16 * kk + 8 + 2 * j);
+          mma_f16(u, a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(brow + 16 * kk + 2 * j),
+                  *reinterpret_cast<const uint32_t*>(brow + 16 * kk + 8 + 2 * j));
+        }
+        const int vc = 8 * nt + 2 * j;
+        const uint32_t ura = __ldg(reinterpret_cast<const uint32_t*>(up + (tile * C + ta) * V + vc));
+        const uint32_t urb = __ldg(reinterpret_cast<const uint32_t*>(up + (tile * C + tb) * V + vc));
+        float Ua[2], Ub[2];
+        if (std::is_same<T, __half>::value) {
+          const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&ura)), fb = __half22float2(*reinterpret_cast<const __half2*>(&urb));
+          Ua[0] = fa.x; Ua[1] = fa.y; Ub[0] = fb.x; Ub[1] = fb.y;
+        } else {
+          Ua[0] = __uint_as_float(ura << 16); Ua[1] = __uint_as_float(ura & 0xffff0000u);
+          Ub[0] = __uint_as_float(urb << 16); Ub[1] = __uint_as_float(urb & 0xffff0000u);
+        }
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int vl = vc + e;
+          const float Ea = __fmul_rn(__fsub_rn(Ua[e], u[e]), fwa);
+          const float Eb = __fmul_rn(__fsub_rn(Ub[e], u[2 + e]), fwb);
+          s_el[vl * C + ta] = (uint8_t)q8(Act<T>::round(Ea), s_isel[vl], a.qmax);
+          s_el[vl * C + tb] = (uint8_t)q8(Act<T>::round(Eb), s_isel[vl], a.qmax);
+          s_ew[vl * C + ta] = (uint8_t)q8(__fmul_rn(Ea, fva), s_isew[vl], a.qmax);
+          s_ew[vl * C + tb] = (uint8_t)q8(__fmul_rn(Eb, fvb), s_isew[vl], a.qmax);
+        }
+      }
+    }
+    cp_async_wait<0>();  // this chunk's k_write tile
+    __syncthreads();
+
+    // ---- 4. e_local tile out; write product in the rotated basis, dequantised, fp16, key-major
+    {
+      uint4* eout = reinterpret_cast<uint4*>(a.elT + tile * (size_t)(V * C));
+      for (int i = tid; i < V * C / 16; i += 256) eout[i] = reinterpret_cast<const uint4*>(s_el)[i];
+      const int mtv = warp % MTV, nhf = warp / MTV;
+      const int va = 16 * mtv + g, vb = va + 8;
+      const uint4 ea = *reinterpret_cast<const uint4*>(s_ew + va * C + 16 * j);
+      const uint4 eb = *reinterpret_cast<const uint4*>(s_ew + vb * C + 16 * j);
+      const float sewa = s_sew[va], sewb = s_sew[vb];
+#pragma unroll
+      for (int n2 = 0; n2 < NTW; ++n2) {
+        const int nt = NTW * nhf + n2;
+        const uint4 kq = *reinterpret_cast<const uint4*>(s_kw + (8 * nt + g) * C + 16 * j);
+        int acc[4] = {0, 0, 0, 0};
+        mma_s8(acc, ea.x, eb.x, ea.y, eb.y, kq.x, kq.y);
+        mma_s8(acc, ea.z, eb.z, ea.w, eb.w, kq.z, kq.w);
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int kc = 8 * nt + 2 * j + e;
+          const float sk = s_skw[kc];
+          s_x[kc * LDH + va] = __float2half_rn(__fmul_rn(__fmul_rn((float)acc[e], sk), sewa));
+          s_x[kc * LDH + vb] = __float2half_rn(__fmul_rn(__fmul_rn((float)acc[2 + e], sk), sewb));
+        }
+      }
+    }
+    __syncthreads();
+    if (c + 1 < a.NT) stage_kw(c + 1);  // the k_write tile of the next chunk travels during the un-rotation
+
+    // ---- 5. un-rotation of the write product, folded into the canonical carry
+    if (owner) {
+      float gam[2] = {1.f, 1.f};
+      if (DIAG) {
+        gam[0] = expf(__ldg(a.gcl + tile * K + ka));
+        gam[1] = expf(__ldg(a.gcl + tile * K + kb_));
+      } else if (a.use_g) {
+        gam[0] = gam[1] = expf(glast);
+      }
+#pragma unroll
+      for (int nt = 0; nt < V / 8; ++nt) {
+        float u[4] = {0.f, 0.f, 0.f, 0.f};
+        const __half* brow = s_rt + (8 * nt + g) * LDH;
+#pragma unroll
+        for (int kk = 0; kk < V / 16; ++kk) {
+          const uint32_t a0 = *reinterpret_cast<const uint32_t*>(s_x + ka * LDH + 16 * kk + 2 * j);
+          const uint32_t a1 = *reinterpret_cast<const uint32_t*>(s_x + kb_ * LDH + 16 * kk + 2 * j);
+          const uint32_t a2 = *reinterpret_cast<const uint32_t*>(s_x + ka * LDH + 16 * kk + 8 + 2 * j);
+          const uint32_t a3 = *reinterpret_cast<const uint32_t*>(s_x + kb_ * LDH + 16 * kk + 8 + 2 * j);
+          mma_f16(u, a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(brow + 16 * kk + 2 * j),
+                  *reinterpret_cast<const uint32_t*>(brow + 16 * kk + 8 + 2 * j));
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) carry[nt][i] = fmaf(carry[nt][i], gam[i >> 1], u[i]);
+      }
+    }
+    __syncthreads();
+  }
+
+  if (a.final_state != nullptr && owner) {
+    float* fs = a.final_state + (size_t)bh * K * V;
+#pragma unroll
+    for (int nt = 0; nt < V / 8; ++nt) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) fs[(size_t)((i >> 1) ? kb_ : ka) * V + 8 * nt + 2 * j + (i & 1)] = carry[nt][i];
+    }
+  }
+}
+
 int validate_zoo_problem(const lq_zoo_problem* p, bool delta, bool diagonal);
 void fill_prologue_args(const lq_zoo_problem* p, const lq_zoo_workspace* ws, PrologueArgs& a);
 
@@ -424,8 +675,32 @@ int run_prologue_delta(const lq_zoo_problem* p, const lq_zoo_workspace* ws, cuda
   return fail(LQ_ERR_UNSUPPORTED, "delta prologue: activation dtype must be f16 or bf16");
 }
 
+template <typename T, int K, int V>
+static int launch_delta_state_unrot(const lq_zoo_problem* p, const DeltaStateArgs& a, cudaStream_t st) {
+  const size_t smem = (size_t)V * K + 2 * (size_t)V * 64 + (size_t)K * 64 + sizeof(__half) * (size_t)(2 * V + K) * (V + 8) +
+                      sizeof(float) * (5 * V + K);
+  const __half* rt = reinterpret_cast<const __half*>(p->unrot_t);
+  cudaError_t e;
+  if (p->decay == LQ_DECAY_DIAGONAL) {
+    e = cudaFuncSetAttribute(zoo_state_delta_unrot_kernel<T, K, V, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) zoo_state_delta_unrot_kernel<T, K, V, true><<<p->B * p->H, 256, smem, st>>>(a, rt);
+  } else {
+    e = cudaFuncSetAttribute(zoo_state_delta_unrot_kernel<T, K, V, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) zoo_state_delta_unrot_kernel<T, K, V, false><<<p->B * p->H, 256, smem, st>>>(a, rt);
+  }
+  if (e != cudaSuccess) return fail(LQ_ERR_LAUNCH, "delta state (canonical storage): shared memory opt-in failed: %s", cudaGetErrorString(e));
+  return check_launch("zoo_state_delta_unrot_kernel");
+}
+
 template <typename T>
 static int dispatch_delta_state(const lq_zoo_problem* p, const DeltaStateArgs& a, cudaStream_t st) {
+  if (p->unrot_t != nullptr) {  // canonical storage: one CTA per (batch, head) owns the whole state
+    if (p->K == 64 && p->V == 64) return launch_delta_state_unrot<T, 64, 64>(p, a, st);
+    if (p->K == 64 && p->V == 128) return launch_delta_state_unrot<T, 64, 128>(p, a, st);
+    if (p->K == 128 && p->V == 64) return launch_delta_state_unrot<T, 128, 64>(p, a, st);
+    if (p->K == 128 && p->V == 128) return launch_delta_state_unrot<T, 128, 128>(p, a, st);
+    return fail(LQ_ERR_UNSUPPORTED, "delta state: K and V must be 64 or 128");
+  }
   dim3 grid(p->V / 32, p->B * p->H), block(128);
   const bool diag = p->decay == LQ_DECAY_DIAGONAL;
 #define LQ_LAUNCH_DSTATE(KK_, VV_)                                                         \

@@ -17,13 +17,12 @@ def chunk_delta_int8(q, k, v, g, beta, scales, *, sigma=1.0, tau=1.0, eta=1.0, s
     """q,k [B,T,H,K], v [B,T,H,V] (fp16/bf16), g [B,T,H] fp32 log-decay or None (DeltaNet), beta [B,T,H].
     scales: 'q' (H,) [on q*scale], 'k' (H,) [Hw, local], 'kw' (H,K) [Hw write], 'w' (H,) [W read],
     'el' (H,V) [E local], 'ew' (H,V) [E write], 'state' (H,V).
+    unrot: optional (V,V) R_V^T for canonical storage when v was rotated by R_V (the output comes out canonical).
     ``fla_prep`` is accepted for signature compatibility; the WY prep always runs in this library's own kernel.
     ``rot`` / ``dqk`` fuse the persistent R_QK rotation and the D_QK rescale into the prologue.
     Returns (o, final fp32 state [B,H,K,V] or None)."""
     if not q.is_cuda:
         raise _cabi.LinQuantError("chunk_delta_int8 runs on CUDA tensors only (no CPU path)")
-    if unrot is not None:
-        raise NotImplementedError("canonical R_V storage (unrot) is not implemented in this build")
     q, k, v, beta = q.contiguous(), k.contiguous(), v.contiguous(), beta.contiguous()
     B, T, H, K = q.shape
     V = v.shape[-1]
@@ -34,6 +33,6 @@ def chunk_delta_int8(q, k, v, g, beta, scales, *, sigma=1.0, tau=1.0, eta=1.0, s
     keep = []
     P = _common.make_problem(q, k, v, g, beta, scales, decay=_cabi.DECAY_NONE if g is None else _cabi.DECAY_SCALAR,
                              eta=eta, sigma=sigma, tau=tau, scale=scale, chunk_size=chunk_size, bits=bits, out=o,
-                             final_state=ht, rot_signs=_common.signs_of(rot, K, q.device), dqk=dqk, keep=keep)
+                             final_state=ht, rot_signs=_common.signs_of(rot, K, q.device), dqk=dqk, keep=keep, unrot=unrot)
     _common.run("lq_delta_fwd", P, True, q, _debug)
     return o, ht

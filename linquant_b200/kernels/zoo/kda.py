@@ -21,8 +21,6 @@ def chunk_kda_int8(q, k, v, g, beta, scales, *, sigma=1.0, tau=1.0, eta=0.0, sca
     Returns (o [B,T,H,V] in v.dtype or out_dtype, final fp32 state or None)."""
     if not q.is_cuda:
         raise _cabi.LinQuantError("chunk_kda_int8 runs on CUDA tensors only (no CPU path)")
-    if unrot is not None:
-        raise NotImplementedError("canonical R_V storage (unrot) is not implemented in this build")
     q, k, v, beta = q.contiguous(), k.contiguous(), v.contiguous(), beta.contiguous()
     B, T, H, K = q.shape
     V = v.shape[-1]
@@ -33,6 +31,6 @@ def chunk_kda_int8(q, k, v, g, beta, scales, *, sigma=1.0, tau=1.0, eta=0.0, sca
     keep = []
     P = _common.make_problem(q, k, v, g, beta, scales, decay=_cabi.DECAY_DIAGONAL, eta=eta, sigma=sigma, tau=tau,
                              scale=scale, chunk_size=chunk_size, bits=bits, out=o, final_state=ht,
-                             rot_signs=_common.signs_of(rot, K, q.device), dqk=None, keep=keep)
+                             rot_signs=_common.signs_of(rot, K, q.device), dqk=None, keep=keep, unrot=unrot)
     _common.run("lq_kda_fwd", P, True, q, _debug)
     return o, ht

@@ -129,3 +129,25 @@ def test_gla_canonical_storage_rv(n):
     assert err <= 2e-3, f"{label}: output rel-L2 {err:.3e}"
     reference_check(out, ref, exact, label)
     assert rel_l2(ht, ref_state) <= 1e-3, f"{label}: final fp32 carry {rel_l2(ht, ref_state):.2e}"
+
+
+@pytest.mark.parametrize("n", [128, 512])
+def test_kda_canonical_storage_rv(n):
+    """tests/test_kernel_kda.py:55-70 of the reference: v rotated by R_V, canonical storage, eta = 1."""
+    from linquant_b200.kernels.zoo.kda import chunk_kda_int8
+    from oracle import zoo_oracle as zo
+
+    q, k, v, g, beta = zoo_inputs(B, n, H, K, V, decay="diagonal", delta=True)
+    R, _ = zo.signed_hadamard(V, 7)
+    orc = OracleRun(q, k, v, g, beta, family="delta", decay="diagonal", eta=1.0, rot_v=R, storage="canonical")
+    ref, ref_state = orc.lineage(record=False)
+    exact = orc.exact()
+    vr = (v.double() @ R).to(v.dtype)
+    out, ht = chunk_kda_int8(q.cuda(), k.cuda(), vr.cuda(), g.cuda(), beta.cuda(), orc.scales("cuda"), eta=1.0, scale=K**-0.5,
+                             chunk_size=64, output_final_state=True, unrot=R.T.cuda())
+    torch.cuda.synchronize()
+    label = f"kda canonical R_V T={n}"
+    err = rel_l2(out, ref)
+    assert err <= 2e-3, f"{label}: output rel-L2 {err:.3e}"
+    reference_check(out, ref, exact, label)
+    assert rel_l2(ht, ref_state) <= 1e-3, f"{label}: final fp32 carry {rel_l2(ht, ref_state):.2e}"
