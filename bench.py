@@ -53,7 +53,8 @@ def measured_peak():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs (read-only query)."""
+    """nvidia-smi clocks / throttle reasons sampled every 20 ms from the warm-up to the end of the timed regions
+    (read-only query)."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -65,7 +66,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20"],
                                       stdout=self.f, stderr=subprocess.DEVNULL)
         except Exception:
             self.p = None
@@ -170,13 +171,19 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        step()
+    # the clock sampler needs ~0.1 s to come up: it is started first and the warm-up keeps the GPU under load for at
+    # least 0.3 s, so that samples exist from before the timed region to its end
     sampler = ClockSampler() if rank == 0 else None
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
-    barrier()
     if sampler:
         sampler.start()
+    warm, t_w = 0, time.time()
+    while warm < max(args.warmup, 3) or time.time() - t_w < 0.3:
+        step()
+        warm += 1
+        if warm % 16 == 0:
+            torch.cuda.synchronize()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    barrier()
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
     t0.record()
@@ -245,7 +252,8 @@ def run_ours(args):
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {"workload": "simple_gla_int8 B=4 H=16 dk=dv=128 L=4096 chunk=64 bf16 kernel_pt R_QK int8-state",
-                   "per_gpu_batch": B, "sharding": f"batchxhead x{world}", "l2": "inputs (201 MB) exceed L2; no flush"},
+                   "per_gpu_batch": B, "sharding": f"batchxhead x{world}", "l2": "inputs (201 MB) exceed L2; no flush",
+                   "warmup_steps_run": warm},
         "e2e": {"value": tokens * args.steps / (e2e_ms * 1e-3) / 1e6, "unit": "Mtokens/s",
                 "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in (hq, hk, hv, hg)),
                 "d2h_bytes_per_step": ho.numel() * ho.element_size()},
