@@ -227,15 +227,25 @@ __global__ void __launch_bounds__(256) zoo_diag_amat_kernel(DiagArgs a) {
   const T* kp = reinterpret_cast<const T*>(a.k);
   auto grow = [&](int t) { return (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K + 8 * r; };
 
-  // codes of the bare operands (diagonal blocks)
-  for (int t = warp * G + grp; t < C; t += 8 * G) {
+  // codes of the bare operands (diagonal blocks); every row load of the thread is issued before the first is used
+  constexpr int NIT = C / (8 * G);
+  uint4 rq0[NIT], rk0[NIT];
+#pragma unroll
+  for (int u = 0; u < NIT; ++u) {
+    const int t = warp * G + grp + 8 * G * u;
+    rq0[u] = __ldg(reinterpret_cast<const uint4*>(qp + grow(t)));
+    rk0[u] = __ldg(reinterpret_cast<const uint4*>(kp + grow(t)));
+  }
+#pragma unroll
+  for (int u = 0; u < NIT; ++u) {
+    const int t = warp * G + grp + 8 * G * u;
     float x[8];
     int cd[8];
-    Act<T>::unpack8(*reinterpret_cast<const uint4*>(qp + grow(t)), x);
+    Act<T>::unpack8(rq0[u], x);
 #pragma unroll
     for (int j = 0; j < 8; ++j) cd[j] = q8(__fmul_rn(x[j], a.scale), inv_sq, a.qmax);
     *reinterpret_cast<uint2*>(s_qc + t * K + 8 * r) = make_uint2(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4], cd[5], cd[6], cd[7]));
-    Act<T>::unpack8(*reinterpret_cast<const uint4*>(kp + grow(t)), x);
+    Act<T>::unpack8(rk0[u], x);
     if (use_hw) {
       const float hw = s_hw[t];
 #pragma unroll
@@ -309,7 +319,7 @@ __global__ void __launch_bounds__(256) zoo_diag_amat_kernel(DiagArgs a) {
     __syncthreads();
   }
 
-  // diagonal blocks: 4 x 136 (i >= j) pairs, eight lanes per pair
+  // diagonal blocks: 4 x 136 (i >= j) pairs, eight lanes per pair, four channels per lane and step (128-bit loads)
   for (int pass = 0; pass < 17; ++pass) {
     const int p = pass * 32 + (tid >> 3);
     const int I = p / 136, rem = p % 136;
@@ -320,9 +330,17 @@ __global__ void __launch_bounds__(256) zoo_diag_amat_kernel(DiagArgs a) {
     const int ti = SUB * I + i, tj = SUB * I + jj;
     const int l8 = tid & 7;
     float sum = 0.f;
-    for (int n = l8; n < K; n += 8) {
-      const float w = __expf(s_gc[ti * LD + n] - s_gc[tj * LD + n]);
-      sum = fmaf((float)((int)s_qc[ti * K + n] * (int)s_kc[tj * K + n]), w, sum);
+#pragma unroll
+    for (int n4 = 0; n4 < K / 32; ++n4) {
+      const int n = 4 * l8 + 32 * n4;  // the eight lanes of a pair read 128 consecutive bytes of a gc row
+      const float4 gi = *reinterpret_cast<const float4*>(s_gc + ti * LD + n);
+      const float4 gj = *reinterpret_cast<const float4*>(s_gc + tj * LD + n);
+      const uint32_t qw = *reinterpret_cast<const uint32_t*>(s_qc + ti * K + n) ^ 0x80808080u;
+      const uint32_t kw = *reinterpret_cast<const uint32_t*>(s_kc + tj * K + n) ^ 0x80808080u;
+      sum = fmaf(__fmul_rn(s8_to_float<0>(qw), s8_to_float<0>(kw)), __expf(gi.x - gj.x), sum);
+      sum = fmaf(__fmul_rn(s8_to_float<1>(qw), s8_to_float<1>(kw)), __expf(gi.y - gj.y), sum);
+      sum = fmaf(__fmul_rn(s8_to_float<2>(qw), s8_to_float<2>(kw)), __expf(gi.z - gj.z), sum);
+      sum = fmaf(__fmul_rn(s8_to_float<3>(qw), s8_to_float<3>(kw)), __expf(gi.w - gj.w), sum);
     }
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
