@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(256) zoo_diag_rows_kernel(DiagArgs a) {
         for (int j = 0; j < 8; ++j) gv[j] = s_gc[t * LD + 8 * r + j];
         Act<T>::unpack8(*reinterpret_cast<const uint4*>(qp + row), x);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) cd[j] = q8(__fmul_rn(__fmul_rn(x[j], expf(gv[j])), a.scale), inv_sq, a.qmax);
+        for (int j = 0; j < 8; ++j) cd[j] = q8(__fmul_rn(__fmul_rn(x[j], __expf(gv[j])), a.scale), inv_sq, a.qmax);
         *reinterpret_cast<uint2*>(a.qq + (tile * C + t) * K + 8 * r) =
             make_uint2(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4], cd[5], cd[6], cd[7]));
         Act<T>::unpack8(*reinterpret_cast<const uint4*>(kp + row), x);
@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(256) zoo_diag_rows_kernel(DiagArgs a) {
         const float ele = a.eta * s_le[t];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float w = expf(__fsub_rn(__fsub_rn(gl[j], gv[j]), ele));
+          const float w = __expf(__fsub_rn(__fsub_rn(gl[j], gv[j]), ele));
           kwp[j] |= ((uint32_t)q8(__fmul_rn(x[j], w), inv_kw[j], a.qmax) & 0xffu) << (8 * i);
         }
       }
@@ -268,15 +268,24 @@ __global__ void __launch_bounds__(256) zoo_diag_amat_kernel(DiagArgs a) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) anc[j] = s_gc[(SUB * I) * LD + 8 * r + j];
     const int R = SUB + SUB * I;
-    for (int rr = warp * G + grp; rr < R; rr += 8 * G) {
+    uint4 rrow[NIT];  // this thread's rows of the block row, requested together
+#pragma unroll
+    for (int u = 0; u < NIT; ++u) {
+      const int rr = warp * G + grp + 8 * G * u;
+      if (rr < R) rrow[u] = __ldg(reinterpret_cast<const uint4*>((rr < SUB ? qp : kp) + grow(rr < SUB ? SUB * I + rr : rr - SUB)));
+    }
+#pragma unroll
+    for (int u = 0; u < NIT; ++u) {
+      const int rr = warp * G + grp + 8 * G * u;
+      if (rr >= R) break;
       const bool isq = rr < SUB;
       const int t = isq ? SUB * I + rr : rr - SUB;
       float x[8];
       int cd[8];
-      Act<T>::unpack8(*reinterpret_cast<const uint4*>((isq ? qp : kp) + grow(t)), x);
+      Act<T>::unpack8(rrow[u], x);
       if (isq) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(__fmul_rn(x[j], expf(__fsub_rn(s_gc[t * LD + 8 * r + j], anc[j]))), a.scale);
+        for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(__fmul_rn(x[j], __expf(__fsub_rn(s_gc[t * LD + 8 * r + j], anc[j]))), a.scale);
       } else {
         if (use_hw) {
           const float hw = s_hw[t];
@@ -284,7 +293,7 @@ __global__ void __launch_bounds__(256) zoo_diag_amat_kernel(DiagArgs a) {
           for (int j = 0; j < 8; ++j) x[j] = Act<T>::round(__fmul_rn(x[j], hw));
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(x[j], expf(__fsub_rn(anc[j], s_gc[t * LD + 8 * r + j])));
+        for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(x[j], __expf(__fsub_rn(anc[j], s_gc[t * LD + 8 * r + j])));
       }
       if (rot) {
 #pragma unroll
@@ -386,7 +395,7 @@ __device__ __forceinline__ void kda_scaled_rows(const DiagArgs& a, int b, int c,
     }
     float y[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) y[e] = __fmul_rn(x[e], anchor_row >= 0 ? __expf(gv[e]) : expf(gv[e]));
+    for (int e = 0; e < 8; ++e) y[e] = __fmul_rn(x[e], __expf(gv[e]));
     *reinterpret_cast<float4*>(s_x + (dst_row + rr) * LD + 8 * seg) = make_float4(y[0], y[1], y[2], y[3]);
     *reinterpret_cast<float4*>(s_x + (dst_row + rr) * LD + 8 * seg + 4) = make_float4(y[4], y[5], y[6], y[7]);
   }
@@ -442,10 +451,15 @@ __global__ void __launch_bounds__(256) zoo_kda_wy_kernel(DiagArgs a) {
     const int ti = SUB * I + i, tj = SUB * I + jj;
     const int l8 = tid & 7;
     float sum = 0.f;
-#pragma unroll 4
-    for (int n = l8; n < K; n += 8) {
-      const float w = __expf(s_gc[ti * LD + n] - s_gc[tj * LD + n]);
-      sum = fmaf(s_x[ti * LD + n] * s_x[tj * LD + n], w, sum);
+#pragma unroll
+    for (int n4 = 0; n4 < K / 32; ++n4) {
+      const int n = 4 * l8 + 32 * n4;  // the eight lanes of a pair read 128 consecutive bytes of each row
+      const float4 gi = *reinterpret_cast<const float4*>(s_gc + ti * LD + n), gj = *reinterpret_cast<const float4*>(s_gc + tj * LD + n);
+      const float4 xi = *reinterpret_cast<const float4*>(s_x + ti * LD + n), xj = *reinterpret_cast<const float4*>(s_x + tj * LD + n);
+      sum = fmaf(xi.x * xj.x, __expf(gi.x - gj.x), sum);
+      sum = fmaf(xi.y * xj.y, __expf(gi.y - gj.y), sum);
+      sum = fmaf(xi.z * xj.z, __expf(gi.z - gj.z), sum);
+      sum = fmaf(xi.w * xj.w, __expf(gi.w - gj.w), sum);
     }
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
