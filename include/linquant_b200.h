@@ -39,6 +39,8 @@ typedef enum { LQ_DECAY_NONE = 0, LQ_DECAY_SCALAR = 1, LQ_DECAY_DIAGONAL = 2 } l
 typedef void* lq_stream; /* a cudaStream_t */
 
 int lq_version(void);
+/* sizeof the two descriptor structs as the library was compiled: a binding checks its own layout against these (0 = zoo, 1 = ssd, 2 = workspace) */
+unsigned long long lq_struct_bytes(int which);
 const char* lq_last_error_string(void);
 
 /* ------------------------------------------------------------------------------------------------------------

@@ -92,6 +92,9 @@ int run_diag_stage(const lq_zoo_problem* p, const lq_zoo_workspace* ws, bool del
 }  // namespace lq
 
 extern "C" int lq_version(void) { return 100; }
+extern "C" unsigned long long lq_struct_bytes(int which) {
+  return which == 0 ? sizeof(lq_zoo_problem) : which == 1 ? sizeof(lq_ssd_problem) : which == 2 ? sizeof(lq_zoo_workspace) : 0;
+}
 extern "C" const char* lq_last_error_string(void) { return lq::g_err; }
 
 extern "C" size_t lq_zoo_workspace_bytes(const lq_zoo_problem* p, int delta_family) {

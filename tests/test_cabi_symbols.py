@@ -51,3 +51,16 @@ def test_cuda_ops_refuse_cpu_tensors():
     x = torch.zeros(1, 64, 1, 64, dtype=torch.float16)
     with pytest.raises(_cabi.LinQuantError):
         chunk_simple_gla_int8(x, x, x, None, {})
+
+
+def test_ctypes_layouts_match_the_compiled_structs():
+    """The ctypes mirrors of the three descriptor structs have the size the library was compiled with."""
+    from linquant_b200 import _cabi
+    from linquant_b200.kernels.mamba2 import _ssd
+
+    L = _cabi.lib()
+    L.lq_struct_bytes.restype = ctypes.c_ulonglong
+    L.lq_struct_bytes.argtypes = [ctypes.c_int]
+    assert L.lq_struct_bytes(0) == ctypes.sizeof(_cabi.ZooProblem)
+    assert L.lq_struct_bytes(1) == ctypes.sizeof(_ssd.SsdProblem)
+    assert L.lq_struct_bytes(2) == ctypes.sizeof(_cabi.ZooWorkspace)
