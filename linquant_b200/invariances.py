@@ -129,3 +129,58 @@ def calibrate_linear(sc: StaticScales, q, k, v, g, *, eta=1.0, scale=None, chunk
         carry = carry * gam[:, :, c, None, None] + local if gam is not None else carry + local
         sc.observe("state", carry)
     return sc
+
+
+@torch.no_grad()
+def calibrate_delta(sc: StaticScales, q, k, v, g, beta, *, eta=1.0, sigma=1.0, tau=1.0, scale=None, chunk_size=64,
+                    rot_signs=None, dqk=None):
+    """Observe every role of the delta family with none / scalar decay on one batch: the unquantised WY recurrence of
+    reference.py:202-229 in float64 on the inputs' device (W, U and the readout key rounded to the activation dtype as
+    the kernels see them), with the fp carry observed as the state."""
+    B, T, H, K = q.shape
+    V = v.shape[-1]
+    C = chunk_size
+    nc = T // C
+    act = q.dtype
+    scale = K**-0.5 if scale is None else scale
+    qf, kf = _prepare_qk(q, k, rot_signs, dqk, scale)
+    rnd = lambda x: x.float().to(act).double()  # noqa: E731
+    tile = lambda x: x.reshape(B, nc, C, H, x.shape[-1]).permute(0, 3, 1, 2, 4).double()  # noqa: E731
+    Q, Kt, Vt = tile(qf), tile(kf), tile(v.float())
+    bt = beta.double().reshape(B, nc, C, H).permute(0, 3, 1, 2).unsqueeze(-1)  # [B,H,nc,C,1]
+    if g is not None:
+        gc = g.float().reshape(B, nc, C, H).permute(0, 3, 1, 2).cumsum(-1).double()  # [B,H,nc,C]
+        read = gc.exp().unsqueeze(-1)
+        write = (gc[..., -1:] - gc).exp().unsqueeze(-1)
+        gam = gc[..., -1].exp()
+        tril = torch.ones(C, C, dtype=torch.bool, device=q.device).tril()
+        mask = (gc.unsqueeze(-1) - gc.unsqueeze(-2)).masked_fill(~tril, -torch.inf).exp()
+    else:
+        read = write = torch.ones(1, 1, 1, 1, 1, dtype=torch.float64, device=q.device)
+        gam = None
+        mask = torch.ones(C, C, dtype=torch.float64, device=q.device).tril()
+    Lf = bt**sigma * Kt
+    Rf = bt ** (1 - sigma) * Kt
+    Hw = rnd(bt ** ((1 - sigma) * tau) * Kt)
+    fw = bt ** ((1 - sigma) * (1 - tau))
+    G = ((Lf @ Rf.transpose(-1, -2)) * mask).tril(-1)
+    eye = torch.eye(C, dtype=torch.float64, device=q.device)
+    Tm = torch.linalg.solve_triangular(eye + G, eye.expand(G.shape).clone(), upper=False, unitriangular=True)
+    W = rnd(Tm @ (Lf * read))
+    U = rnd(Tm @ (bt**sigma * Vt))
+    wk, wv = write ** (1 - eta), write**eta
+    Kw = Hw * wk
+    sc.observe("q_read", Q.reshape(B, H, nc * C, K))
+    sc.observe("k_local", Hw.reshape(B, H, nc * C, K))
+    sc.observe("k_write", Kw.reshape(B, H, nc * C, K))
+    sc.observe("w_read", W.reshape(B, H, nc * C, K))
+    S = torch.zeros(B, H, K, V, dtype=torch.float64, device=q.device)
+    for c in range(nc):
+        E = (U[:, :, c] - W[:, :, c] @ S) * fw[:, :, c]
+        sc.observe("e_local", rnd(E))
+        Ew = E * (wv[:, :, c] if g is not None else 1.0)
+        sc.observe("e_write", Ew)
+        local = Kw[:, :, c].transpose(-1, -2) @ Ew
+        S = S * gam[:, :, c, None, None] + local if gam is not None else S + local
+        sc.observe("state", S)
+    return sc
