@@ -71,7 +71,7 @@ typedef struct {
   const float *sw, *sel, *sew;                     /* delta-family extras (null for the linear family) */
   void* o;                /* [B,T,H,V] */
   float* final_state;     /* [B,H,K,V] fp32 carry after the last chunk, or null */
-  const float* initial_state; /* [B,H,K,V] fp32 carry entering the first chunk (linear family), or null = zero */
+  const float* initial_state; /* [B,H,K,V] fp32 carry entering the first chunk, or null = zero */
   const void* unrot_t;        /* canonical storage under a value rotation (the reference's unrot=, zoo/simple_gla.py:31-33,
                                  :150-153): [V,V] fp16, TRANSPOSED, element [v'][v] = unrot[v][v']; v arrives rotated and
                                  every value-side product is multiplied by unrot before it joins the carry / the output

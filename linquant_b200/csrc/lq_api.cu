@@ -42,7 +42,6 @@ int validate_zoo_problem(const lq_zoo_problem* p, bool delta, bool diagonal) {
   if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->o))
     return fail(LQ_ERR_ALIGN, "q, k, v, o must be 16-byte aligned");
   if (p->act_dtype != LQ_F16 && p->act_dtype != LQ_BF16) return fail(LQ_ERR_UNSUPPORTED, "activation dtype must be f16 or bf16");
-  if (delta && p->initial_state != nullptr) return fail(LQ_ERR_UNSUPPORTED, "an initial state is implemented for the linear family only");
   if (p->unrot_t != nullptr && !aligned16(p->unrot_t)) return fail(LQ_ERR_ALIGN, "unrot_t must be 16-byte aligned");
   if (!(p->qmax >= 1.f && p->qmax <= 127.f)) return fail(LQ_ERR_SHAPE, "qmax=%f out of range", (double)p->qmax);
   return LQ_OK;

@@ -174,6 +174,7 @@ struct DeltaStateArgs {
   const float *gcl, *genv;  // diagonal decay: [BH,NT,K] end-of-chunk log-decay, [BH,NT,C] log envelope
   int8_t *hT, *elT;
   float* final_state;
+  const float* initial_state;  // [B,H,K,V] fp32 carry entering the first chunk, or null
   int H, NT, use_g;
   float eta, qmax;
 };
@@ -233,7 +234,14 @@ __global__ void __launch_bounds__(128) zoo_state_delta_kernel(DeltaStateArgs a) 
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-    for (int nt = 0; nt < NTK; ++nt) carry[mt][nt][0] = carry[mt][nt][1] = carry[mt][nt][2] = carry[mt][nt][3] = 0.f;
+    for (int nt = 0; nt < NTK; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const size_t kk_ = (size_t)bh * K + kown + 2 * nt + e;
+        carry[mt][nt][e] = a.initial_state ? a.initial_state[kk_ * V + v0 + 16 * mt + g] : 0.f;
+        carry[mt][nt][2 + e] = a.initial_state ? a.initial_state[kk_ * V + v0 + 16 * mt + g + 8] : 0.f;
+      }
+    }
 
   uint4 wa[KK], wb[KK], ua, ub, kb[NTK];
   float fwa, fwb, gca, gcb, glast;
@@ -456,7 +464,13 @@ __global__ void __launch_bounds__(256) zoo_state_delta_unrot_kernel(DeltaStateAr
 
   float carry[V / 8][4];
 #pragma unroll
-  for (int nt = 0; nt < V / 8; ++nt) carry[nt][0] = carry[nt][1] = carry[nt][2] = carry[nt][3] = 0.f;
+  for (int nt = 0; nt < V / 8; ++nt) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int kr = (i >> 1) ? kb_ : ka;
+      carry[nt][i] = (a.initial_state && owner) ? a.initial_state[((size_t)bh * K + kr) * V + 8 * nt + 2 * j + (i & 1)] : 0.f;
+    }
+  }
 
   auto stage_kw = [&](int c) {
     const int8_t* kwc = a.kwT + (base_tile + c) * (size_t)(K * C);
@@ -719,7 +733,7 @@ int run_state_delta(const lq_zoo_problem* p, const lq_zoo_workspace* ws, cudaStr
   DeltaStateArgs a;
   a.wq = ws->wq; a.kwT = ws->kwT; a.u = ws->u; a.fw = ws->fw; a.gc = ws->gc;
   a.skw = p->skw; a.sw = p->sw; a.sel = p->sel; a.sew = p->sew; a.ss = p->sstate;
-  a.hT = ws->hT; a.elT = ws->vlT; a.final_state = p->final_state; a.gcl = ws->gcl; a.genv = ws->genv;
+  a.hT = ws->hT; a.elT = ws->vlT; a.final_state = p->final_state; a.initial_state = p->initial_state; a.gcl = ws->gcl; a.genv = ws->genv;
   a.H = p->H; a.NT = p->T / p->chunk; a.use_g = p->g != nullptr; a.eta = p->eta; a.qmax = p->qmax;
   if (p->act_dtype == LQ_F16) return dispatch_delta_state<__half>(p, a, st);
   if (p->act_dtype == LQ_BF16) return dispatch_delta_state<__nv_bfloat16>(p, a, st);

@@ -13,7 +13,7 @@ from ... import _cabi
 
 def chunk_delta_int8(q, k, v, g, beta, scales, *, sigma=1.0, tau=1.0, eta=1.0, scale=None, chunk_size=64,
                      output_final_state=False, unrot=None, fla_prep=True, bits=8, out_dtype=None, rot=None, dqk=None,
-                     _debug=None):
+                     initial_state=None, _debug=None):
     """q,k [B,T,H,K], v [B,T,H,V] (fp16/bf16), g [B,T,H] fp32 log-decay or None (DeltaNet), beta [B,T,H].
     scales: 'q' (H,) [on q*scale], 'k' (H,) [Hw, local], 'kw' (H,K) [Hw write], 'w' (H,) [W read],
     'el' (H,V) [E local], 'ew' (H,V) [E write], 'state' (H,V).
@@ -33,6 +33,6 @@ def chunk_delta_int8(q, k, v, g, beta, scales, *, sigma=1.0, tau=1.0, eta=1.0, s
     keep = []
     P = _common.make_problem(q, k, v, g, beta, scales, decay=_cabi.DECAY_NONE if g is None else _cabi.DECAY_SCALAR,
                              eta=eta, sigma=sigma, tau=tau, scale=scale, chunk_size=chunk_size, bits=bits, out=o,
-                             final_state=ht, rot_signs=_common.signs_of(rot, K, q.device), dqk=dqk, keep=keep, unrot=unrot)
+                             final_state=ht, rot_signs=_common.signs_of(rot, K, q.device), dqk=dqk, keep=keep, unrot=unrot, initial_state=initial_state)
     _common.run("lq_delta_fwd", P, True, q, _debug)
     return o, ht

@@ -14,7 +14,7 @@ BC = 16  # secondary chunk
 
 
 def chunk_gla_int8(q, k, v, g, scales, *, eta=0.0, scale=None, chunk_size=64, output_final_state=False, unrot=None,
-                   rot=None, bits=8, out_dtype=None, _debug=None):
+                   rot=None, bits=8, out_dtype=None, initial_state=None, _debug=None):
     """q,k [B,T,H,K], v [B,T,H,V] (fp16/bf16), g [B,T,H,K] fp32 per-channel log-decay.
     scales: 'q' (H,) [on q*scale, tied read/local], 'k' (H,), 'kw' (H,K), 'vw' (H,V), 'vl' (H,V), 'state' (H,V).
     unrot: optional (V,V) R_V^T (canonical storage, v arrives rotated).
@@ -32,6 +32,6 @@ def chunk_gla_int8(q, k, v, g, scales, *, eta=0.0, scale=None, chunk_size=64, ou
     keep = []
     P = _common.make_problem(q, k, v, g, None, scales, decay=_cabi.DECAY_DIAGONAL, eta=eta, sigma=1.0, tau=1.0,
                              scale=scale, chunk_size=chunk_size, bits=bits, out=o, final_state=ht,
-                             rot_signs=_common.signs_of(rot, K, q.device), dqk=None, keep=keep, unrot=unrot)
+                             rot_signs=_common.signs_of(rot, K, q.device), dqk=None, keep=keep, unrot=unrot, initial_state=initial_state)
     _common.run("lq_gla_fwd", P, False, q, _debug)
     return o, ht

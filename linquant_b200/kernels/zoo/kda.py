@@ -13,7 +13,8 @@ from .gla import BC
 
 
 def chunk_kda_int8(q, k, v, g, beta, scales, *, sigma=1.0, tau=1.0, eta=0.0, scale=None, chunk_size=64,
-                   output_final_state=False, unrot=None, rot=None, fla_prep=True, bits=8, out_dtype=None, _debug=None):
+                   output_final_state=False, unrot=None, rot=None, fla_prep=True, bits=8, out_dtype=None, initial_state=None,
+                   _debug=None):
     """q,k [B,T,H,K], v [B,T,H,V] (fp16/bf16), g [B,T,H,K] fp32 per-channel log-decay, beta [B,T,H].
     scales: 'q' (H,), 'k' (H,) [Hw local], 'kw' (H,K) [Hw write], 'w' (H,) [W read], 'el'/'ew' (H,V) [E local /
     write], 'state' (H,V). rot: signed-Hadamard R_QK for the anchored local operands. ``fla_prep`` is accepted for
@@ -31,6 +32,6 @@ def chunk_kda_int8(q, k, v, g, beta, scales, *, sigma=1.0, tau=1.0, eta=0.0, sca
     keep = []
     P = _common.make_problem(q, k, v, g, beta, scales, decay=_cabi.DECAY_DIAGONAL, eta=eta, sigma=sigma, tau=tau,
                              scale=scale, chunk_size=chunk_size, bits=bits, out=o, final_state=ht,
-                             rot_signs=_common.signs_of(rot, K, q.device), dqk=None, keep=keep, unrot=unrot)
+                             rot_signs=_common.signs_of(rot, K, q.device), dqk=None, keep=keep, unrot=unrot, initial_state=initial_state)
     _common.run("lq_kda_fwd", P, True, q, _debug)
     return o, ht

@@ -125,3 +125,22 @@ def test_delta_canonical_storage_rv(decay, sigma, tau, n):
     reference_check(out, ref, exact, label)
     tol = 1e-3 if decay else 3e-2
     assert rel_l2(ht, ref_state) <= tol, f"{label}: final fp32 carry {rel_l2(ht, ref_state):.2e}"
+
+
+@pytest.mark.parametrize("decay", [False, True])
+def test_delta_chained_calls_through_initial_state(decay):
+    """Cached prefill: a sequence processed in two calls, the fp32 carry of the first handed to the second, reproduces
+    the single call exactly (output and final carry)."""
+    from linquant_b200.kernels.zoo.gated_delta_rule import chunk_delta_int8
+
+    q, k, v, g, beta = zoo_inputs(2, 512, 3, 128, 128, decay="scalar" if decay else "none", delta=True, dtype=torch.bfloat16, seed=11)
+    orc = OracleRun(q, k, v, g, beta, family="delta", decay="scalar" if decay else "none", policy="kernel_ptk", sigma=0.5)
+    sc = orc.scales("cuda")
+    d = lambda t, s=slice(None): None if t is None else t[:, s].cuda()  # noqa: E731
+    kw = dict(sigma=0.5, output_final_state=True)
+    whole, fs = chunk_delta_int8(d(q), d(k), d(v), d(g), d(beta), sc, **kw)
+    h1, h2 = slice(0, 192), slice(192, 512)
+    a, sa = chunk_delta_int8(d(q, h1), d(k, h1), d(v, h1), d(g, h1), d(beta, h1), sc, **kw)
+    b, sb = chunk_delta_int8(d(q, h2), d(k, h2), d(v, h2), d(g, h2), d(beta, h2), sc, initial_state=sa, **kw)
+    torch.cuda.synchronize()
+    assert torch.equal(torch.cat([a, b], 1), whole) and torch.equal(sb, fs)

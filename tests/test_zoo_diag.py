@@ -151,3 +151,27 @@ def test_kda_canonical_storage_rv(n):
     assert err <= 2e-3, f"{label}: output rel-L2 {err:.3e}"
     reference_check(out, ref, exact, label)
     assert rel_l2(ht, ref_state) <= 1e-3, f"{label}: final fp32 carry {rel_l2(ht, ref_state):.2e}"
+
+
+@pytest.mark.parametrize("cell", ["gla", "kda"])
+def test_diag_chained_calls_through_initial_state(cell):
+    """Cached prefill for the diagonal-decay cells: two calls chained through the fp32 carry equal the single call."""
+    from linquant_b200.kernels.zoo.gla import chunk_gla_int8
+    from linquant_b200.kernels.zoo.kda import chunk_kda_int8
+
+    delta = cell == "kda"
+    q, k, v, g, beta = zoo_inputs(2, 384, 3, 128, 128, decay="diagonal", delta=delta, dtype=torch.bfloat16, seed=12)
+    orc = OracleRun(q, k, v, g, beta, family="delta" if delta else "linear", decay="diagonal", eta=0.5)
+    sc = orc.scales("cuda")
+    d = lambda t, s=slice(None): None if t is None else t[:, s].cuda()  # noqa: E731
+
+    def call(s, init):
+        if delta:
+            return chunk_kda_int8(d(q, s), d(k, s), d(v, s), d(g, s), d(beta, s), sc, eta=0.5, output_final_state=True, initial_state=init)
+        return chunk_gla_int8(d(q, s), d(k, s), d(v, s), d(g, s), sc, eta=0.5, output_final_state=True, initial_state=init)
+
+    whole, fs = call(slice(None), None)
+    a, sa = call(slice(0, 128), None)
+    b, sb = call(slice(128, 384), sa)
+    torch.cuda.synchronize()
+    assert torch.equal(torch.cat([a, b], 1), whole) and torch.equal(sb, fs)
