@@ -184,3 +184,104 @@ def calibrate_delta(sc: StaticScales, q, k, v, g, beta, *, eta=1.0, sigma=1.0, t
         S = S * gam[:, :, c, None, None] + local if gam is not None else S + local
         sc.observe("state", S)
     return sc
+
+
+SUB = 16  # secondary chunk of the diagonal-decay local product (reference.py:21)
+
+
+def _fp16_grid(x):
+    return x.float().to(torch.float16).to(x.dtype)
+
+
+@torch.no_grad()
+def calibrate_diagonal(sc: StaticScales, q, k, v, g, beta=None, *, eta=0.0, sigma=1.0, tau=1.0, scale=None, chunk_size=64,
+                       rot_signs=None):
+    """Observe every role of the per-channel-decay cells on one batch: GLA (``beta`` None, reference.py:190-199) and
+    KDA (reference.py:202-229), float64 on the inputs' device. The local product is observed as the kernels form
+    it (reference.py:125-152): in 16-token secondary chunks, operands below the diagonal block re-scaled around the
+    block's anchor row and, with ``rot_signs``, rotated on the fp16 grid; the diagonal block on the bare operands."""
+    B, T, H, K = q.shape
+    V = v.shape[-1]
+    C, nc = chunk_size, T // chunk_size
+    act = q.dtype
+    dev = q.device
+    scale = K**-0.5 if scale is None else scale
+    rnd = lambda x: x.float().to(act).double()  # noqa: E731
+    tile = lambda x: x.reshape(B, nc, C, H, x.shape[-1]).permute(0, 3, 1, 2, 4).double()  # noqa: E731
+    Q, Kt, Vt = tile(q.float() * scale), tile(k.float()), tile(v.float())
+    gc = g.float().reshape(B, nc, C, H, K).permute(0, 3, 1, 2, 4).cumsum(-2).double()  # [B,H,nc,C,K]
+    read = gc.exp()
+    write = (gc[..., -1:, :] - gc).exp()
+    gam = gc[..., -1, :].exp().unsqueeze(-1)  # [B,H,nc,K,1]
+    env = write.amax(dim=-1, keepdim=True)
+    kf = write * env ** (-eta)
+    if eta > 0:
+        kf = torch.where(env > 0, kf, torch.zeros_like(kf))
+    vfac = env**eta
+    R = _fp16_grid(signed_hadamard_matrix(rot_signs).to(dev)) if rot_signs is not None else None
+    delta = beta is not None
+
+    def observe_local(X, Y):
+        """roles q_local (tied to q_read) and k_local on the operands of the local product A = X . Y^T"""
+        for s in range(0, C, SUB):
+            rows = slice(s, s + SUB)
+            if s > 0:
+                anchor = gc[..., s : s + 1, :]
+                Xa = X[..., rows, :] * (gc[..., rows, :] - anchor).exp()
+                Ya = Y[..., :s, :] * (anchor - gc[..., :s, :]).exp()
+                if R is not None:
+                    Xa, Ya = (_fp16_grid(Xa) @ R).float().double(), (_fp16_grid(Ya) @ R).float().double()
+                sc.observe("q_local", Xa.reshape(B, H, -1, K))
+                sc.observe("k_local", Ya.reshape(B, H, -1, K))
+            sc.observe("q_local", X[..., rows, :].reshape(B, H, -1, K))
+            sc.observe("k_local", Y[..., rows, :].reshape(B, H, -1, K))
+
+    def gram(X, Y):
+        """strictly lower A_ij = sum_n X_in Y_jn exp(gc_in - gc_jn), secondary-chunk form, unquantised"""
+        A = X.new_zeros(*X.shape[:-1], C)
+        for s in range(0, C, SUB):
+            rows = slice(s, s + SUB)
+            if s > 0:
+                anchor = gc[..., s : s + 1, :]
+                A[..., rows, :s] = (X[..., rows, :] * (gc[..., rows, :] - anchor).exp()) @ \
+                    (Y[..., :s, :] * (anchor - gc[..., :s, :]).exp()).transpose(-1, -2)
+            gd = gc[..., rows, :]
+            keep = torch.ones(SUB, SUB, dtype=torch.bool, device=dev).tril(-1).unsqueeze(-1)
+            w = (gd.unsqueeze(-2) - gd.unsqueeze(-3)).masked_fill(~keep, -torch.inf).exp()
+            A[..., rows, rows] = torch.einsum("...in,...jn,...ijn->...ij", X[..., rows, :], Y[..., rows, :], w).tril(-1)
+        return A
+
+    sc.observe("q_read", (Q * read).reshape(B, H, nc * C, K))
+    if not delta:
+        observe_local(Q, Kt)
+        Kw, Vw = Kt * kf, Vt * vfac
+        sc.observe("v_local", Vt.reshape(B, H, nc * C, V))
+        sc.observe("k_write", Kw.reshape(B, H, nc * C, K))
+        sc.observe("v_write", Vw.reshape(B, H, nc * C, V))
+        S = torch.zeros(B, H, K, V, dtype=torch.float64, device=dev)
+        for c in range(nc):
+            S = S * gam[:, :, c] + Kw[:, :, c].transpose(-1, -2) @ Vw[:, :, c]
+            sc.observe("state", S)
+        return sc
+    bt = beta.double().reshape(B, nc, C, H).permute(0, 3, 1, 2).unsqueeze(-1)
+    Lf, Rf = bt**sigma * Kt, bt ** (1 - sigma) * Kt
+    Hw = rnd(bt ** ((1 - sigma) * tau) * Kt)
+    fw = bt ** ((1 - sigma) * (1 - tau))
+    eye = torch.eye(C, dtype=torch.float64, device=dev)
+    G = gram(Lf, Rf)
+    Tm = torch.linalg.solve_triangular(eye + G, eye.expand(G.shape).clone(), upper=False, unitriangular=True)
+    W = rnd(Tm @ (Lf * read))
+    U = rnd(Tm @ (bt**sigma * Vt))
+    observe_local(Q, Hw)
+    Kw = Hw * kf
+    sc.observe("w_read", W.reshape(B, H, nc * C, K))
+    sc.observe("k_write", Kw.reshape(B, H, nc * C, K))
+    S = torch.zeros(B, H, K, V, dtype=torch.float64, device=dev)
+    for c in range(nc):
+        E = (U[:, :, c] - W[:, :, c] @ S) * fw[:, :, c]
+        sc.observe("e_local", rnd(E))
+        Ew = E * vfac[:, :, c]
+        sc.observe("e_write", Ew)
+        S = S * gam[:, :, c] + Kw[:, :, c].transpose(-1, -2) @ Ew
+        sc.observe("state", S)
+    return sc

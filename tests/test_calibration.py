@@ -49,3 +49,16 @@ def test_delta_observers_match_oracle(decay, sigma, tau, eta, policy):
     got = sc.finalize().kernel_scales(H, K, V, "cpu")
     assert {"w", "el", "ew"} <= set(got)
     _compare(got, ref, 1e-5)
+
+
+@pytest.mark.parametrize("cell", ["gla", "kda"])
+@pytest.mark.parametrize("rot", [False, True])
+@pytest.mark.parametrize("eta", [0.0, 0.5])
+def test_diagonal_observers_match_oracle(cell, rot, eta):
+    delta = cell == "kda"
+    q, k, v, g, beta = zoo_inputs(B, T, H, K, V, decay="diagonal", delta=delta, dtype=torch.float16, seed=5)
+    R, signs = zo.signed_hadamard(K, 3) if rot else (None, None)
+    ref = OracleRun(q, k, v, g, beta, family="delta" if delta else "linear", decay="diagonal", eta=eta, rot_qk=R).scales("cpu")
+    sc = inv.StaticScales("kernel_static", 8, 8)
+    inv.calibrate_diagonal(sc, q, k, v, g, beta, eta=eta, chunk_size=64, rot_signs=None if signs is None else signs.float())
+    _compare(sc.finalize().kernel_scales(H, K, V, "cpu"), ref, 1e-5)
