@@ -62,3 +62,28 @@ def test_diagonal_observers_match_oracle(cell, rot, eta):
     sc = inv.StaticScales("kernel_static", 8, 8)
     inv.calibrate_diagonal(sc, q, k, v, g, beta, eta=eta, chunk_size=64, rot_signs=None if signs is None else signs.float())
     _compare(sc.finalize().kernel_scales(H, K, V, "cpu"), ref, 1e-5)
+
+
+def test_ssd_observers_fill_the_code_range_without_saturating():
+    """Scales from the SSD observers, fed to the oracle's SSD ops on the calibration batch itself: every quantised
+    tensor reaches its top code somewhere and none saturates (the defining property of absmax calibration)."""
+    from linquant_b200.kernels.mamba2.calibration import SsdObservers
+    from oracle import ssd_oracle as so
+
+    g = torch.Generator().manual_seed(21)
+    b, L, Hh, P, G, N, C = 2, 256, 4, 64, 1, 64, 64
+    x = torch.randn(b, L, Hh, P, generator=g).half()
+    Bm, Cm = torch.randn(b, L, G, N, generator=g), torch.randn(b, L, G, N, generator=g)
+    dt_raw, A_log = torch.randn(b, L, Hh, generator=g) * 0.5 - 2, torch.rand(Hh, generator=g) * 2.7
+    obs = SsdObservers().observe(x, dt_raw, A_log, Bm, Cm, C)
+    s = obs.scales()
+    qB = torch.round(Bm / s["B_scale"].view(1, 1, G, 1)).clamp(-127, 127).to(torch.int8)
+    qC = torch.round(Cm / s["C_scale"].view(1, 1, G, 1)).clamp(-127, 127).to(torch.int8)
+    assert int(qB.abs().max()) == 127 and int(qC.abs().max()) == 127
+    dA, dt = so.chunk_cumsum(dt_raw, 1.0, A_log, 1.0, C, None, True)
+    st = so.chunk_state_value(x, qB, dt, dA, s["alpha_hp"], s["B_scale"], s["state_scale"])
+    assert 100 <= int(st.abs().max()) <= 127, int(st.abs().max())            # quantised operands: close to, not above, the top code
+    stk = so.chunk_state_key(x, s["x_scale_hp"], Bm.half(), dt, dA, s["state_scale"], s["b_gate_scale"])
+    assert 100 <= int(stk.abs().max()) <= 127
+    cb = so.bmm_chunk(qC, s["C_scale"], qB, s["B_scale"], C, s["cb_scale"])
+    assert 110 <= int(cb.abs().max()) <= 127
