@@ -84,7 +84,13 @@ __global__ void __launch_bounds__(256) ssd_transpose_b_kernel(const int8_t* qB, 
 // out[:, c] = clamp(s32 entering chunk c), final = clamp(s32 after the last chunk). 16 state bytes per thread.
 __global__ void __launch_bounds__(256) ssd_state_passing_kernel(const int8_t* states, const float* dA, int8_t* out,
                                                                 int8_t* final_state, int H, int NC, int C, int D) {
+  extern __shared__ int s_gq[];  // [NC] Q0.7 gate of every chunk: the serial loop must not wait on its loads
   const int h = blockIdx.y, b = blockIdx.z;
+  {
+    const float* dAl = dA + (((size_t)b * H + h) * NC) * C + (C - 1);
+    for (int c = threadIdx.x; c < NC; c += 256) s_gq[c] = round_half_away(__fmul_rn(expf(dAl[(size_t)c * C]), 128.f), 127.f);
+  }
+  __syncthreads();
   const int d0 = (blockIdx.x * 256 + threadIdx.x) * 16;
   if (d0 >= D) return;
   int s32[16];
@@ -93,27 +99,34 @@ __global__ void __launch_bounds__(256) ssd_state_passing_kernel(const int8_t* st
   const size_t cstride = (size_t)H * D;
   const int8_t* src = states + ((size_t)b * NC * H + h) * D + d0;
   int8_t* dst = out + ((size_t)b * NC * H + h) * D + d0;
-  const float* dAl = dA + (((size_t)b * H + h) * NC) * C + (C - 1);
-  uint4 nxt = __ldg(reinterpret_cast<const uint4*>(src));
-  for (int c = 0; c < NC; ++c) {
-    const uint4 cur = nxt;
-    if (c + 1 < NC) nxt = __ldg(reinterpret_cast<const uint4*>(src + (size_t)(c + 1) * cstride));
-    uint32_t o[4];
+  constexpr int DEPTH = 4;  // chunk tiles in flight per thread
+  uint4 ring[DEPTH];
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      int cd[4];
+  for (int u = 0; u < DEPTH; ++u)
+    if (u < NC) ring[u] = __ldg(reinterpret_cast<const uint4*>(src + (size_t)u * cstride));
+  for (int c0 = 0; c0 < NC; c0 += DEPTH) {
 #pragma unroll
-      for (int k = 0; k < 4; ++k) cd[k] = min(max(s32[4 * w + k], -127), 127);
-      o[w] = pack4(cd[0], cd[1], cd[2], cd[3]);
-    }
-    *reinterpret_cast<uint4*>(dst + (size_t)c * cstride) = make_uint4(o[0], o[1], o[2], o[3]);
-    const float gs = __fmul_rn(expf(dAl[(size_t)c * C]), 128.f);
-    const int gq = round_half_away(gs, 127.f);
-    const uint32_t cw[4] = {cur.x, cur.y, cur.z, cur.w};
+    for (int u = 0; u < DEPTH; ++u) {
+      const int c = c0 + u;
+      if (c >= NC) break;
+      const uint4 cur = ring[u];
+      if (c + DEPTH < NC) ring[u] = __ldg(reinterpret_cast<const uint4*>(src + (size_t)(c + DEPTH) * cstride));
+      uint32_t o[4];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int nw = (int)(int8_t)((cw[i >> 2] >> (8 * (i & 3))) & 0xff);
-      s32[i] = ((s32[i] * gq + 64) >> 7) + nw;
+      for (int w = 0; w < 4; ++w) {
+        int cd[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) cd[k] = min(max(s32[4 * w + k], -127), 127);
+        o[w] = pack4(cd[0], cd[1], cd[2], cd[3]);
+      }
+      *reinterpret_cast<uint4*>(dst + (size_t)c * cstride) = make_uint4(o[0], o[1], o[2], o[3]);
+      const int gq = s_gq[c];
+      const uint32_t cw[4] = {cur.x, cur.y, cur.z, cur.w};
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int nw = (int)(int8_t)((cw[i >> 2] >> (8 * (i & 3))) & 0xff);
+        s32[i] = ((s32[i] * gq + 64) >> 7) + nw;
+      }
     }
   }
   uint32_t o[4];
@@ -359,32 +372,64 @@ __global__ void __launch_bounds__(128) ssd_bmm_kernel(lq_ssd_problem p) {
 }
 
 // ------------------------------------------------------------------------------------------------ chunk scan
-// mamba2/chunk_scan_v2.py:160-256. One CTA per (chunk, head, batch), headdim 64. The x tile is staged once in shared
-// memory as fp16 (XOR-swizzled rows) and serves both the causal fp16 product (ldmatrix.trans B fragments) and the
-// D*x residual; C rows, passed states and the INT8 CB rows are read as fragments straight from global memory.
-//   out = int32(C_i8 . S_i8) * s_C * s_state[p] * exp(dA_m) + fp16(cb * S_cb * exp(dA_m - dA_k) * dt_k, k <= m) . fp16(x) + D x
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
-  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem_row);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+// mamba2/chunk_scan_v2.py:160-256. One CTA per (chunk, head, batch), headdim 64; a warp owns one 16-row tile of the
+// chunk at a time (light and heavy causal rows paired). All INT8 tiles and the x tile (fp16) are staged in shared
+// memory once.
+//   out[m,:] = int32(C_i8[m,:] . S_i8) s_C s_state[p] exp(dA_m)
+//            + sum_{k<=m} fp16(cb[m,k] S_cb exp(dA_m - dA_k) dt_k) fp16(x[k,:]) + D x[m,:]
+// With r = the first row of the warp's tile the decay splits as exp(dA_m - dA_r) exp(dA_r - dA_k) for k < r (both
+// exponents <= 0), so one fp32 accumulator serves everything:
+//   acc  = int32(C.S) s_C s_state[p] exp(dA_r)                      state read, entered at the tile's first row
+//   acc += fp16(cb) * fp16(S_cb exp(dA_r - dA_k) dt_k) . x          tiles strictly below the diagonal: the codes go to
+//                                                                   fp16 exactly, one half2 multiply per two elements
+//   acc *= exp(dA_m - dA_r)                                         row factor, once
+//   acc += fp16(cb S_cb exp(dA_m - dA_k) dt_k, k <= m) . x          the diagonal tile, evaluated per element
+template <int IMM>
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4+%5];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr), "n"(IMM));
+}
+// Two INT8 codes (bytes LO and LO+1 of w, each XOR 0x80) times a half2 factor: the bytes become the low mantissa
+// bits of 1024 in fp16 (exact), 1152 is subtracted (exact) and the product is rounded once.
+template <int LO>
+__device__ __forceinline__ uint32_t codes_times_half2(uint32_t w_xor80, uint32_t factor) {
+  const uint32_t bits = __byte_perm(w_xor80, 0x64646464u, LO == 0 ? 0x5140 : 0x7362);
+  const __half2 c = __hsub2(*reinterpret_cast<const __half2*>(&bits), __half2half2(__ushort_as_half((unsigned short)0x6480)));
+  const __half2 r = __hmul2(c, *reinterpret_cast<const __half2*>(&factor));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+// One k16 step of the causal product: A fragment af against 64 value channels whose x rows ldmatrix reads at
+// base[n2] ^ xorv (+ IMM bytes).
+template <int IMM>
+__device__ __forceinline__ void scan_kstep(float (&conv)[8][4], const uint32_t (&af)[4], const uint32_t (&base)[4], uint32_t xorv) {
+#pragma unroll
+  for (int n2 = 0; n2 < 4; ++n2) {
+    uint32_t r[4];
+    ldsm_x4_trans<IMM>(r, base[n2] ^ xorv);
+    mma_f16(conv[2 * n2], af[0], af[1], af[2], af[3], r[0], r[1]);
+    mma_f16(conv[2 * n2 + 1], af[0], af[1], af[2], af[3], r[2], r[3]);
+  }
 }
 
 template <typename T, int N>
-__global__ void __launch_bounds__(256) ssd_chunk_scan_kernel(lq_ssd_problem p) {
+__global__ void __launch_bounds__(256, 2) ssd_chunk_scan_kernel(lq_ssd_problem p) {
   constexpr int P = 64;
   extern __shared__ __align__(128) uint8_t smem[];
   const int C = p.chunk, NC = p.L / C;
-  uint8_t* s_x = smem;                                   // [C][128 B] fp16, 16-byte chunk index ^ (row & 7)
+  // x tile [C][128 B] fp16; the 16-byte piece ch of row r sits at piece ch ^ f(r), f(r) = (((r>>4)^(r>>2))&3)<<1 | (r&1):
+  // both row orders ldmatrix uses below (16a+b and 4a+b, a = 0..3, b = 0..1) then touch eight different pieces
+  uint8_t* s_x = smem;
   float* s_dA = reinterpret_cast<float*>(smem + (size_t)C * 128);
-  float* s_dt = s_dA + C;
-  float* s_tab = s_dt + C;                               // [8 warps][C] below-diagonal decay table of the warp's m-tile
-  int8_t* s_qc = reinterpret_cast<int8_t*>(s_tab + 8 * C);  // [C][N] q_C codes of the chunk
-  int8_t* s_S = s_qc + (size_t)C * N;                       // [64][N] INT8 state entering the chunk
-  float* s_ss = reinterpret_cast<float*>(s_S + 64 * N);     // [64] state scales, [64] D
-  float* s_D = s_ss + 64;
+  float* s_dts = s_dA + C;                                   // S_cb * dt
+  __half* s_tab = reinterpret_cast<__half*>(s_dts + C);      // [8 warps][C] fp16 below-diagonal factors of the warp's tile
+  int8_t* s_qc = reinterpret_cast<int8_t*>(s_tab + 8 * C);   // [C][N] q_C codes of the chunk
+  int8_t* s_S = s_qc + (size_t)C * N;                        // [64][N] INT8 state entering the chunk
+  float* s_cs = reinterpret_cast<float*>(s_S + 64 * N);      // [64] s_C * state scale, [64] D
+  float* s_D = s_cs + 64;
   // byte offset of 16-byte piece `ch` of row `row` in the two INT8 tiles: an MMA fragment load touches two rows x
   // four pieces per quarter-warp, so odd rows swap their 64-byte halves (rows of 64 bytes interleave by themselves)
   auto frag_off = [](int row, int ch) { return N == 128 ? row * 128 + ((ch ^ ((row & 1) << 2)) << 4) : row * 64 + (ch << 4); };
+  auto x_piece = [](int row, int ch) { return ch ^ (((((row >> 4) ^ (row >> 2)) & 3) << 1) | (row & 1)); };
 
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int grp = h / (p.H / p.G);
@@ -403,12 +448,13 @@ __global__ void __launch_bounds__(256) ssd_chunk_scan_kernel(lq_ssd_problem p) {
     cp_async16(s_S + frag_off(row, ch), sp + (size_t)row * N + 16 * ch);
   }
   cp_async_commit();
+  const float Scb = p.cb_scale[grp];
   for (int t = tid; t < C; t += 256) {
     s_dA[t] = p.dA[cbase + t];
-    s_dt[t] = p.dt[cbase + t];
+    s_dts[t] = __fmul_rn(Scb, p.dt[cbase + t]);
   }
   if (tid < 64) {
-    s_ss[tid] = p.state_scale[h * P + tid];
+    s_cs[tid] = __fmul_rn(p.C_scale[grp], p.state_scale[h * P + tid]);
     s_D[tid] = p.D == nullptr ? 0.f : (p.D_has_hdim ? p.D[h * P + tid] : p.D[h]);
   }
   {
@@ -422,25 +468,66 @@ __global__ void __launch_bounds__(256) ssd_chunk_scan_kernel(lq_ssd_problem p) {
         raw = make_uint4(Act<__half>::pack2(x[0], x[1]), Act<__half>::pack2(x[2], x[3]), Act<__half>::pack2(x[4], x[5]),
                          Act<__half>::pack2(x[6], x[7]));
       }
-      *reinterpret_cast<uint4*>(s_x + row * 128 + ((ch ^ (row & 7)) << 4)) = raw;
+      *reinterpret_cast<uint4*>(s_x + row * 128 + (x_piece(row, ch) << 4)) = raw;
     }
   }
   cp_async_wait<0>();
   __syncthreads();
 
-  const float gscale = p.C_scale[grp], Scb = p.cb_scale[grp];
   const int MT = C / 16;
   const int8_t* cbp = p.cb + (((size_t)b * NC + c) * p.G + grp) * C * C;
-  __half* op = reinterpret_cast<__half*>(p.out);
+  __half* op = reinterpret_cast<__half*>(p.out) + (((size_t)b * p.L + (size_t)c * C) * p.H + h) * P + 2 * j;
+  const size_t orow = (size_t)p.H * P;
+
+  // ldmatrix lanes: matrix mi = lane>>3 (k half mi&1, value tile mi>>1), stored row rr = lane&7 <-> MMA k slot
+  // 8 (mi&1) + rr, which is token offset a-th group of the lane pair (a = rr>>1) + 2 (mi&1) + (rr&1). Two token
+  // orders are used: "grouped" steps cover 64 tokens in four k16 steps, lane j owning tokens 16j + 4u + e of step u
+  // (one 16-byte load of CB codes per row and group); "single" steps cover 16 tokens, lane j owning 4j + e.
+  const int mi = lane >> 3, rr = lane & 7;
+  const uint32_t sx_u32 = (uint32_t)__cvta_generic_to_shared(s_x);
+  uint32_t baseG[4], baseS[4];
+#pragma unroll
+  for (int n2 = 0; n2 < 4; ++n2) {
+    const uint32_t piece = (uint32_t)((2 * n2 + (mi >> 1)) ^ rr) << 4;  // f() of the lane's row without the step bits
+    baseG[n2] = sx_u32 + (16 * (rr >> 1) + 2 * (mi & 1) + (rr & 1)) * 128 + piece;
+    baseS[n2] = sx_u32 + (4 * (rr >> 1) + 2 * (mi & 1) + (rr & 1)) * 128 + piece;
+  }
 
   for (int it = 0; it * 8 < MT; ++it) {
     const int mt = (it & 1) ? it * 8 + 7 - warp : it * 8 + warp;  // pair light and heavy causal rows
     if (mt >= MT) continue;
     const int ma = 16 * mt + g, mb = ma + 8;
+    const int qfull = mt >> 2, rem = mt & 3;
+    const float dref = s_dA[16 * mt];
     const float dAa = s_dA[ma], dAb = s_dA[mb];
+    const int8_t* cba = cbp + (size_t)ma * C;
+    const int8_t* cbb = cbp + (size_t)mb * C;
 
-    // ---- state read (INT8)
-    float accf[8][4];
+    // CB codes of the last, partial group (single steps; the diagonal tile is step `rem` of it) and of the first full group
+    uint32_t ta[4], tb[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      ta[u] = __ldg(reinterpret_cast<const uint32_t*>(cba + 64 * qfull + 16 * u + 4 * j));
+      tb[u] = __ldg(reinterpret_cast<const uint32_t*>(cbb + 64 * qfull + 16 * u + 4 * j));
+    }
+    uint4 ga = make_uint4(0, 0, 0, 0), gb = ga;
+    if (qfull > 0) {
+      ga = __ldg(reinterpret_cast<const uint4*>(cba + 16 * j));
+      gb = __ldg(reinterpret_cast<const uint4*>(cbb + 16 * j));
+    }
+
+    // ---- below-diagonal factors of this tile: tab[k] = fp16(S_cb exp(dA_r - dA_k) dt_k), k < 16 mt
+    __half* tab = s_tab + warp * C;
+    __syncwarp();
+    for (int k = 2 * lane; k < 16 * mt; k += 64) {
+      const float2 d = *reinterpret_cast<const float2*>(s_dA + k), t = *reinterpret_cast<const float2*>(s_dts + k);
+      *reinterpret_cast<__half2*>(tab + k) =
+          __floats2half2_rn(__fmul_rn(__expf(__fsub_rn(dref, d.x)), t.x), __fmul_rn(__expf(__fsub_rn(dref, d.y)), t.y));
+    }
+    __syncwarp();
+
+    // ---- state read (INT8), entered at the tile's first row
+    float conv[8][4];
     {
       uint4 qa[N / 64], qb[N / 64];
 #pragma unroll
@@ -448,7 +535,7 @@ __global__ void __launch_bounds__(256) ssd_chunk_scan_kernel(lq_ssd_problem p) {
         qa[kk] = *reinterpret_cast<const uint4*>(s_qc + frag_off(ma, 4 * kk + j));
         qb[kk] = *reinterpret_cast<const uint4*>(s_qc + frag_off(mb, 4 * kk + j));
       }
-      const float ga = expf(dAa), gb = expf(dAb);
+      const float er = __expf(dref);
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
         int acc[4] = {0, 0, 0, 0};
@@ -458,110 +545,112 @@ __global__ void __launch_bounds__(256) ssd_chunk_scan_kernel(lq_ssd_problem p) {
           mma_s8(acc, qa[kk].x, qb[kk].x, qa[kk].y, qb[kk].y, bs.x, bs.y);
           mma_s8(acc, qa[kk].z, qb[kk].z, qa[kk].w, qb[kk].w, bs.z, bs.w);
         }
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const float ss = s_ss[8 * nt + 2 * j + e];
-          accf[nt][e] = __fmul_rn(__fmul_rn(__fmul_rn((float)acc[e], gscale), ss), ga);
-          accf[nt][2 + e] = __fmul_rn(__fmul_rn(__fmul_rn((float)acc[2 + e], gscale), ss), gb);
-        }
+        const float2 cs = *reinterpret_cast<const float2*>(s_cs + 8 * nt + 2 * j);
+        const float c0 = __fmul_rn(cs.x, er), c1 = __fmul_rn(cs.y, er);
+        conv[nt][0] = __fmul_rn((float)acc[0], c0);
+        conv[nt][1] = __fmul_rn((float)acc[1], c1);
+        conv[nt][2] = __fmul_rn((float)acc[2], c0);
+        conv[nt][3] = __fmul_rn((float)acc[3], c1);
       }
     }
-    // ---- causal fp16 product. Within a k16 step the reduction index is permuted so that lane j owns four
-    // consecutive tokens 4j .. 4j+3 (one 32-bit load of CB codes per row); the x rows handed to ldmatrix follow
-    // the same permutation. Tiles strictly below the diagonal take the decay from a per-warp table
-    //   tab[k] = Scb * exp(dA[16 mt] - dA[k]) * dt[k]   (k < 16 mt, exponent <= 0)
-    // times the row factor exp(dA[m] - dA[16 mt]) (<= 1); the diagonal tile evaluates exp(dA[m] - dA[k]) directly
-    // under the causal mask.
-    float conv[8][4];
+
+    // ---- full groups of 64 tokens below the diagonal
+    for (int q = 0; q < qfull; ++q) {
+      uint4 na = ga, nb = gb;
+      if (q + 1 < qfull) {
+        na = __ldg(reinterpret_cast<const uint4*>(cba + 64 * (q + 1) + 16 * j));
+        nb = __ldg(reinterpret_cast<const uint4*>(cbb + 64 * (q + 1) + 16 * j));
+      }
+      const uint32_t wa[4] = {ga.x ^ 0x80808080u, ga.y ^ 0x80808080u, ga.z ^ 0x80808080u, ga.w ^ 0x80808080u};
+      const uint32_t wb[4] = {gb.x ^ 0x80808080u, gb.y ^ 0x80808080u, gb.z ^ 0x80808080u, gb.w ^ 0x80808080u};
+      const uint4 tv0 = *reinterpret_cast<const uint4*>(tab + 64 * q + 16 * j);       // steps 0, 1
+      const uint4 tv1 = *reinterpret_cast<const uint4*>(tab + 64 * q + 16 * j + 8);   // steps 2, 3
+      const uint32_t tv[8] = {tv0.x, tv0.y, tv0.z, tv0.w, tv1.x, tv1.y, tv1.z, tv1.w};
+      uint32_t bq[4];
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) conv[nt][0] = conv[nt][1] = conv[nt][2] = conv[nt][3] = 0.f;
-    float* tab = s_tab + warp * C;
-    const float dref = s_dA[16 * mt];
-    __syncwarp();
-    for (int k = lane; k < 16 * mt; k += 32) tab[k] = __fmul_rn(__fmul_rn(Scb, __expf(__fsub_rn(dref, s_dA[k]))), s_dt[k]);
-    __syncwarp();
-    const float ea = __expf(__fsub_rn(dAa, dref)), eb = __expf(__fsub_rn(dAb, dref));
-    const int mi = lane >> 3, rr = lane & 7;
-    const int xrow = 4 * (rr >> 1) + 2 * (mi & 1) + (rr & 1);  // ldmatrix row of this lane within a k16 step
-    const int8_t* cba = cbp + (size_t)ma * C + 4 * j;
-    const int8_t* cbb = cbp + (size_t)mb * C + 4 * j;
-    // CB codes travel four k16 steps ahead of their use (a ring of four register pairs)
-    uint32_t wa_r[4], wb_r[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int ks = u <= mt ? u : mt;
-      wa_r[u] = __ldg(reinterpret_cast<const uint32_t*>(cba + 16 * ks));
-      wb_r[u] = __ldg(reinterpret_cast<const uint32_t*>(cbb + 16 * ks));
+      for (int n2 = 0; n2 < 4; ++n2) bq[n2] = baseG[n2] + q * 8192;
+      {
+        const uint32_t af[4] = {codes_times_half2<0>(wa[0], tv[0]), codes_times_half2<0>(wb[0], tv[0]),
+                                codes_times_half2<2>(wa[0], tv[1]), codes_times_half2<2>(wb[0], tv[1])};
+        scan_kstep<0>(conv, af, bq, 0u);
+      }
+      {
+        const uint32_t af[4] = {codes_times_half2<0>(wa[1], tv[2]), codes_times_half2<0>(wb[1], tv[2]),
+                                codes_times_half2<2>(wa[1], tv[3]), codes_times_half2<2>(wb[1], tv[3])};
+        scan_kstep<512>(conv, af, bq, 1u << 5);
+      }
+      {
+        const uint32_t af[4] = {codes_times_half2<0>(wa[2], tv[4]), codes_times_half2<0>(wb[2], tv[4]),
+                                codes_times_half2<2>(wa[2], tv[5]), codes_times_half2<2>(wb[2], tv[5])};
+        scan_kstep<1024>(conv, af, bq, 2u << 5);
+      }
+      {
+        const uint32_t af[4] = {codes_times_half2<0>(wa[3], tv[6]), codes_times_half2<0>(wb[3], tv[6]),
+                                codes_times_half2<2>(wa[3], tv[7]), codes_times_half2<2>(wb[3], tv[7])};
+        scan_kstep<1536>(conv, af, bq, 3u << 5);
+      }
+      ga = na;
+      gb = nb;
     }
-    for (int ks0 = 0; ks0 <= mt; ks0 += 4) {
+    // ---- single steps of the partial group, below the diagonal (at most three)
+    uint32_t bs_[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int ks = ks0 + u;
-        if (ks > mt) break;
-        uint32_t af[4];
-        const int k0 = 16 * ks + 4 * j;
-        const uint32_t wa = wa_r[u], wb = wb_r[u];
-        if (ks + 4 <= mt) {
-          wa_r[u] = __ldg(reinterpret_cast<const uint32_t*>(cba + 16 * (ks + 4)));
-          wb_r[u] = __ldg(reinterpret_cast<const uint32_t*>(cbb + 16 * (ks + 4)));
-        }
-        float va[4], vb[4];
-        if (ks < mt) {
-          const float4 t4 = *reinterpret_cast<const float4*>(tab + k0);
-          const float tv[4] = {t4.x, t4.y, t4.z, t4.w};
-          const uint32_t ua = wa ^ 0x80808080u, ub = wb ^ 0x80808080u;
-          const float fa[4] = {s8_to_float<0>(ua), s8_to_float<1>(ua), s8_to_float<2>(ua), s8_to_float<3>(ua)};
-          const float fb[4] = {s8_to_float<0>(ub), s8_to_float<1>(ub), s8_to_float<2>(ub), s8_to_float<3>(ub)};
+    for (int n2 = 0; n2 < 4; ++n2) bs_[n2] = baseS[n2] + qfull * 8192;
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            va[e] = __fmul_rn(__fmul_rn(fa[e], ea), tv[e]);
-            vb[e] = __fmul_rn(__fmul_rn(fb[e], eb), tv[e]);
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int k = k0 + e;
-            const float dk = s_dA[k], dtk = s_dt[k];
-            const float ca = (float)(int8_t)(wa >> (8 * e)), cb = (float)(int8_t)(wb >> (8 * e));
-            va[e] = (ma >= k) ? __fmul_rn(__fmul_rn(__fmul_rn(ca, Scb), __expf(__fsub_rn(dAa, dk))), dtk) : 0.f;
-            vb[e] = (mb >= k) ? __fmul_rn(__fmul_rn(__fmul_rn(cb, Scb), __expf(__fsub_rn(dAb, dk))), dtk) : 0.f;
-          }
-        }
-        af[0] = Act<__half>::pack2(va[0], va[1]);
-        af[1] = Act<__half>::pack2(vb[0], vb[1]);
-        af[2] = Act<__half>::pack2(va[2], va[3]);
-        af[3] = Act<__half>::pack2(vb[2], vb[3]);
-#pragma unroll
-        for (int n2 = 0; n2 < 4; ++n2) {
-          const int row = 16 * ks + xrow;
-          const int ch = 2 * n2 + (mi >> 1);
-          uint32_t r[4];
-          ldmatrix_x4_trans(r, s_x + row * 128 + ((ch ^ (row & 7)) << 4));
-          mma_f16(conv[2 * n2], af[0], af[1], af[2], af[3], r[0], r[1]);
-          mma_f16(conv[2 * n2 + 1], af[0], af[1], af[2], af[3], r[2], r[3]);
-        }
+    for (int u = 0; u < 3; ++u) {
+      if (u < rem) {
+        const uint2 tvv = *reinterpret_cast<const uint2*>(tab + 64 * qfull + 16 * u + 4 * j);
+        const uint32_t wa = ta[u] ^ 0x80808080u, wb = tb[u] ^ 0x80808080u;
+        const uint32_t af[4] = {codes_times_half2<0>(wa, tvv.x), codes_times_half2<0>(wb, tvv.x),
+                                codes_times_half2<2>(wa, tvv.y), codes_times_half2<2>(wb, tvv.y)};
+        if (u == 0) scan_kstep<0>(conv, af, bs_, 0u);
+        if (u == 1) scan_kstep<2048>(conv, af, bs_, 1u << 5);
+        if (u == 2) scan_kstep<4096>(conv, af, bs_, 2u << 5);
       }
     }
-    // ---- combine, D*x residual, store fp16
+    // ---- row factor, then the diagonal tile per element
+    {
+      const float ea = __expf(__fsub_rn(dAa, dref)), eb = __expf(__fsub_rn(dAb, dref));
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-      const int pc = 8 * nt + 2 * j;
-      float oa[2], ob[2];
-      const float2 xa = __half22float2(*reinterpret_cast<const __half2*>(s_x + ma * 128 + ((nt ^ (ma & 7)) << 4) + 4 * j));
-      const float2 xb = __half22float2(*reinterpret_cast<const __half2*>(s_x + mb * 128 + ((nt ^ (mb & 7)) << 4) + 4 * j));
-      const float xav[2] = {xa.x, xa.y}, xbv[2] = {xb.x, xb.y};
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        oa[e] = __fadd_rn(accf[nt][e], conv[nt][e]);
-        ob[e] = __fadd_rn(accf[nt][2 + e], conv[nt][2 + e]);
-        if (p.D != nullptr) {
-          const float Dv = s_D[pc + e];
-          oa[e] = __fadd_rn(oa[e], __fmul_rn(xav[e], Dv));
-          ob[e] = __fadd_rn(ob[e], __fmul_rn(xbv[e], Dv));
-        }
+      for (int nt = 0; nt < 8; ++nt) {
+        conv[nt][0] *= ea; conv[nt][1] *= ea; conv[nt][2] *= eb; conv[nt][3] *= eb;
       }
-      *reinterpret_cast<uint32_t*>(op + (((size_t)b * p.L + (size_t)c * C + ma) * p.H + h) * P + pc) = Act<__half>::pack2(oa[0], oa[1]);
-      *reinterpret_cast<uint32_t*>(op + (((size_t)b * p.L + (size_t)c * C + mb) * p.H + h) * P + pc) = Act<__half>::pack2(ob[0], ob[1]);
+      const uint32_t wda = (rem == 0 ? ta[0] : rem == 1 ? ta[1] : rem == 2 ? ta[2] : ta[3]) ^ 0x80808080u;
+      const uint32_t wdb = (rem == 0 ? tb[0] : rem == 1 ? tb[1] : rem == 2 ? tb[2] : tb[3]) ^ 0x80808080u;
+      const float4 dk4 = *reinterpret_cast<const float4*>(s_dA + 16 * mt + 4 * j);
+      const float4 sk4 = *reinterpret_cast<const float4*>(s_dts + 16 * mt + 4 * j);
+      const float dk[4] = {dk4.x, dk4.y, dk4.z, dk4.w}, sk[4] = {sk4.x, sk4.y, sk4.z, sk4.w};
+      const float fa[4] = {s8_to_float<0>(wda), s8_to_float<1>(wda), s8_to_float<2>(wda), s8_to_float<3>(wda)};
+      const float fb[4] = {s8_to_float<0>(wdb), s8_to_float<1>(wdb), s8_to_float<2>(wdb), s8_to_float<3>(wdb)};
+      float va[4], vb[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int kl = 4 * j + e;  // token within the tile; rows g and g + 8
+        va[e] = (g >= kl) ? __fmul_rn(__fmul_rn(fa[e], __expf(__fsub_rn(dAa, dk[e]))), sk[e]) : 0.f;
+        vb[e] = (g + 8 >= kl) ? __fmul_rn(__fmul_rn(fb[e], __expf(__fsub_rn(dAb, dk[e]))), sk[e]) : 0.f;
+      }
+      const uint32_t af[4] = {Act<__half>::pack2(va[0], va[1]), Act<__half>::pack2(vb[0], vb[1]),
+                              Act<__half>::pack2(va[2], va[3]), Act<__half>::pack2(vb[2], vb[3])};
+      uint32_t bd[4];
+#pragma unroll
+      for (int n2 = 0; n2 < 4; ++n2) bd[n2] = bs_[n2] + rem * 2048;
+      scan_kstep<0>(conv, af, bd, (uint32_t)rem << 5);
+    }
+    // ---- D*x residual, store fp16
+    {
+      const uint8_t* xa_row = s_x + ma * 128 + 4 * j;
+      const uint8_t* xb_row = s_x + mb * 128 + 4 * j;
+      const int fa_ = x_piece(ma, 0), fb_ = x_piece(mb, 0);
+      __half* oa_p = op + (size_t)ma * orow;
+      __half* ob_p = op + (size_t)mb * orow;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const float2 xa = __half22float2(*reinterpret_cast<const __half2*>(xa_row + ((nt ^ fa_) << 4)));
+        const float2 xb = __half22float2(*reinterpret_cast<const __half2*>(xb_row + ((nt ^ fb_) << 4)));
+        const float2 Dv = *reinterpret_cast<const float2*>(s_D + 8 * nt + 2 * j);
+        *reinterpret_cast<uint32_t*>(oa_p + 8 * nt) = Act<__half>::pack2(fmaf(xa.x, Dv.x, conv[nt][0]), fmaf(xa.y, Dv.y, conv[nt][1]));
+        *reinterpret_cast<uint32_t*>(ob_p + 8 * nt) = Act<__half>::pack2(fmaf(xb.x, Dv.x, conv[nt][2]), fmaf(xb.y, Dv.y, conv[nt][3]));
+      }
     }
   }
 }
@@ -683,7 +772,8 @@ extern "C" int lq_ssd_state_passing(const lq_ssd_problem* p, lq_stream stream) {
   const int D = p->P * p->N;
   if (D % 16 != 0) return fail(LQ_ERR_SHAPE, "state_passing: P*N must be a multiple of 16");
   dim3 grid((D / 16 + 255) / 256, p->H, p->B);
-  ssd_state_passing_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p->states, p->dA, p->passed, p->final_state, p->H,
+  if ((size_t)(p->L / p->chunk) * sizeof(int) > 48 * 1024) return fail(LQ_ERR_UNSUPPORTED, "state_passing: more than 12288 chunks");
+  ssd_state_passing_kernel<<<grid, 256, (size_t)(p->L / p->chunk) * sizeof(int), (cudaStream_t)stream>>>(p->states, p->dA, p->passed, p->final_state, p->H,
                                                                     p->L / p->chunk, p->chunk, D);
   return check_launch("ssd_state_passing_kernel");
 }
@@ -772,7 +862,7 @@ extern "C" int lq_ssd_bmm_chunk(const lq_ssd_problem* p, int b_is_fp, lq_stream 
 
 template <typename T, int N>
 static int launch_scan(const lq_ssd_problem* p, cudaStream_t st) {
-  const size_t smem = (size_t)p->chunk * 128 + 10 * sizeof(float) * p->chunk + (size_t)(p->chunk + 64) * N + 128 * sizeof(float);
+  const size_t smem = (size_t)p->chunk * 128 + 6 * sizeof(float) * p->chunk + (size_t)(p->chunk + 64) * N + 128 * sizeof(float);
   dim3 grid(p->L / p->chunk, p->H, p->B);
   cudaFuncSetAttribute(ssd_chunk_scan_kernel<T, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
   ssd_chunk_scan_kernel<T, N><<<grid, 256, smem, st>>>(*p);
