@@ -422,8 +422,7 @@ __global__ void __launch_bounds__(256, 2) ssd_chunk_scan_kernel(lq_ssd_problem p
   float* s_dA = reinterpret_cast<float*>(smem + (size_t)C * 128);
   float* s_dts = s_dA + C;                                   // S_cb * dt
   __half* s_tab = reinterpret_cast<__half*>(s_dts + C);      // [8 warps][C] fp16 below-diagonal factors of the warp's tile
-  int8_t* s_qc = reinterpret_cast<int8_t*>(s_tab + 8 * C);   // [C][N] q_C codes of the chunk
-  int8_t* s_S = s_qc + (size_t)C * N;                        // [64][N] INT8 state entering the chunk
+  int8_t* s_S = reinterpret_cast<int8_t*>(s_tab + 8 * C);    // [64][N] INT8 state entering the chunk
   float* s_cs = reinterpret_cast<float*>(s_S + 64 * N);      // [64] s_C * state scale, [64] D
   float* s_D = s_cs + 64;
   // byte offset of 16-byte piece `ch` of row `row` in the two INT8 tiles: an MMA fragment load touches two rows x
@@ -439,15 +438,10 @@ __global__ void __launch_bounds__(256, 2) ssd_chunk_scan_kernel(lq_ssd_problem p
 
   const int8_t* qc = p.q_C + (((size_t)b * p.L + (size_t)c * C) * p.G + grp) * N;
   const int8_t* sp = p.passed + ((((size_t)b * NC + c) * p.H + h) * P) * N;
-  for (int i = tid; i < C * (N / 16); i += 256) {
-    const int row = i / (N / 16), ch = i % (N / 16);
-    cp_async16(s_qc + frag_off(row, ch), qc + (size_t)row * p.G * N + 16 * ch);
-  }
   for (int i = tid; i < 64 * (N / 16); i += 256) {
     const int row = i / (N / 16), ch = i % (N / 16);
     cp_async16(s_S + frag_off(row, ch), sp + (size_t)row * N + 16 * ch);
   }
-  cp_async_commit();
   const float Scb = p.cb_scale[grp];
   for (int t = tid; t < C; t += 256) {
     s_dA[t] = p.dA[cbase + t];
@@ -461,6 +455,10 @@ __global__ void __launch_bounds__(256, 2) ssd_chunk_scan_kernel(lq_ssd_problem p
     const T* xp = reinterpret_cast<const T*>(p.x) + (size_t)b * p.x_stride_b + (size_t)h * p.x_stride_h;
     for (int i = tid; i < C * 8; i += 256) {
       const int row = i >> 3, ch = i & 7;
+      if (std::is_same<T, __half>::value) {
+        cp_async16(s_x + row * 128 + (x_piece(row, ch) << 4), xp + (size_t)(c * C + row) * p.x_stride_t + 8 * ch);
+        continue;
+      }
       uint4 raw = __ldg(reinterpret_cast<const uint4*>(xp + (size_t)(c * C + row) * p.x_stride_t + 8 * ch));
       if (!std::is_same<T, __half>::value) {
         float x[8];
@@ -471,6 +469,7 @@ __global__ void __launch_bounds__(256, 2) ssd_chunk_scan_kernel(lq_ssd_problem p
       *reinterpret_cast<uint4*>(s_x + row * 128 + (x_piece(row, ch) << 4)) = raw;
     }
   }
+  cp_async_commit();
   cp_async_wait<0>();
   __syncthreads();
 
@@ -510,6 +509,13 @@ __global__ void __launch_bounds__(256, 2) ssd_chunk_scan_kernel(lq_ssd_problem p
       ta[u] = __ldg(reinterpret_cast<const uint32_t*>(cba + 64 * qfull + 16 * u + 4 * j));
       tb[u] = __ldg(reinterpret_cast<const uint32_t*>(cbb + 64 * qfull + 16 * u + 4 * j));
     }
+    // q_C rows of the tile: every code is used once per CTA, so the fragments come straight from global memory
+    uint4 qa[N / 64], qb[N / 64];
+#pragma unroll
+    for (int kk = 0; kk < N / 64; ++kk) {
+      qa[kk] = __ldg(reinterpret_cast<const uint4*>(qc + (size_t)ma * p.G * N + 64 * kk + 16 * j));
+      qb[kk] = __ldg(reinterpret_cast<const uint4*>(qc + (size_t)mb * p.G * N + 64 * kk + 16 * j));
+    }
     uint4 ga = make_uint4(0, 0, 0, 0), gb = ga;
     if (qfull > 0) {
       ga = __ldg(reinterpret_cast<const uint4*>(cba + 16 * j));
@@ -529,12 +535,6 @@ __global__ void __launch_bounds__(256, 2) ssd_chunk_scan_kernel(lq_ssd_problem p
     // ---- state read (INT8), entered at the tile's first row
     float conv[8][4];
     {
-      uint4 qa[N / 64], qb[N / 64];
-#pragma unroll
-      for (int kk = 0; kk < N / 64; ++kk) {
-        qa[kk] = *reinterpret_cast<const uint4*>(s_qc + frag_off(ma, 4 * kk + j));
-        qb[kk] = *reinterpret_cast<const uint4*>(s_qc + frag_off(mb, 4 * kk + j));
-      }
       const float er = __expf(dref);
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
@@ -862,7 +862,7 @@ extern "C" int lq_ssd_bmm_chunk(const lq_ssd_problem* p, int b_is_fp, lq_stream 
 
 template <typename T, int N>
 static int launch_scan(const lq_ssd_problem* p, cudaStream_t st) {
-  const size_t smem = (size_t)p->chunk * 128 + 6 * sizeof(float) * p->chunk + (size_t)(p->chunk + 64) * N + 128 * sizeof(float);
+  const size_t smem = (size_t)p->chunk * 128 + 6 * sizeof(float) * p->chunk + (size_t)64 * N + 128 * sizeof(float);
   dim3 grid(p->L / p->chunk, p->H, p->B);
   cudaFuncSetAttribute(ssd_chunk_scan_kernel<T, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
   ssd_chunk_scan_kernel<T, N><<<grid, 256, smem, st>>>(*p);
