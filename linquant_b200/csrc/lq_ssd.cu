@@ -402,12 +402,15 @@ __device__ __forceinline__ uint32_t codes_times_half2(uint32_t w_xor80, uint32_t
 // base[n2] ^ xorv (+ IMM bytes).
 template <int IMM>
 __device__ __forceinline__ void scan_kstep(float (&conv)[8][4], const uint32_t (&af)[4], const uint32_t (&base)[4], uint32_t xorv) {
+  // the four fragment loads go out together: the assembly statements issue in program order, and a load placed
+  // between two tiles' products would expose its latency four times per step
+  uint32_t r[4][4];
+#pragma unroll
+  for (int n2 = 0; n2 < 4; ++n2) ldsm_x4_trans<IMM>(r[n2], base[n2] ^ xorv);
 #pragma unroll
   for (int n2 = 0; n2 < 4; ++n2) {
-    uint32_t r[4];
-    ldsm_x4_trans<IMM>(r, base[n2] ^ xorv);
-    mma_f16(conv[2 * n2], af[0], af[1], af[2], af[3], r[0], r[1]);
-    mma_f16(conv[2 * n2 + 1], af[0], af[1], af[2], af[3], r[2], r[3]);
+    mma_f16(conv[2 * n2], af[0], af[1], af[2], af[3], r[n2][0], r[n2][1]);
+    mma_f16(conv[2 * n2 + 1], af[0], af[1], af[2], af[3], r[n2][2], r[n2][3]);
   }
 }
 
@@ -536,21 +539,27 @@ __global__ void __launch_bounds__(256, 2) ssd_chunk_scan_kernel(lq_ssd_problem p
     float conv[8][4];
     {
       const float er = __expf(dref);
+      // eight independent accumulator chains: the products of one value tile would otherwise wait on each other
+      int acc[8][4];
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0;
+#pragma unroll
+      for (int kk = 0; kk < N / 64; ++kk) {
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+          const uint4 bs = *reinterpret_cast<const uint4*>(s_S + frag_off(8 * nt + g, 4 * kk + j));
+          mma_s8(acc[nt], qa[kk].x, qb[kk].x, qa[kk].y, qb[kk].y, bs.x, bs.y);
+          mma_s8(acc[nt], qa[kk].z, qb[kk].z, qa[kk].w, qb[kk].w, bs.z, bs.w);
+        }
+      }
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
-        int acc[4] = {0, 0, 0, 0};
-#pragma unroll
-        for (int kk = 0; kk < N / 64; ++kk) {
-          const uint4 bs = *reinterpret_cast<const uint4*>(s_S + frag_off(8 * nt + g, 4 * kk + j));
-          mma_s8(acc, qa[kk].x, qb[kk].x, qa[kk].y, qb[kk].y, bs.x, bs.y);
-          mma_s8(acc, qa[kk].z, qb[kk].z, qa[kk].w, qb[kk].w, bs.z, bs.w);
-        }
         const float2 cs = *reinterpret_cast<const float2*>(s_cs + 8 * nt + 2 * j);
         const float c0 = __fmul_rn(cs.x, er), c1 = __fmul_rn(cs.y, er);
-        conv[nt][0] = __fmul_rn((float)acc[0], c0);
-        conv[nt][1] = __fmul_rn((float)acc[1], c1);
-        conv[nt][2] = __fmul_rn((float)acc[2], c0);
-        conv[nt][3] = __fmul_rn((float)acc[3], c1);
+        conv[nt][0] = __fmul_rn((float)acc[nt][0], c0);
+        conv[nt][1] = __fmul_rn((float)acc[nt][1], c1);
+        conv[nt][2] = __fmul_rn((float)acc[nt][2], c0);
+        conv[nt][3] = __fmul_rn((float)acc[nt][3], c1);
       }
     }
 
