@@ -19,31 +19,50 @@ __device__ __forceinline__ int round_rint(float y, float lo, float hi) {
 }
 
 // ------------------------------------------------------------------------------------------------ cumsum
-// mamba2/chunk_cumsum.py:52-74. One thread per head walks the chunk; the running sum is kept in double (the CPU
-// oracle's float cumsum accumulates in double).
-__global__ void ssd_cumsum_kernel(lq_ssd_problem p) {
-  const int c = blockIdx.x, b = blockIdx.y, h = threadIdx.x;
-  if (h >= p.H) return;
+// mamba2/chunk_cumsum.py:52-74. One CTA per (chunk, batch, block of 32 heads). The dt tile is read with the head
+// index contiguous (as it lies in memory), transformed and parked in shared memory; each warp then scans four heads
+// with the token index across its lanes, so both outputs are written with the token index contiguous. The running sum
+// is kept in double (the CPU oracle's float cumsum accumulates in double): a warp scan per 32 tokens plus a carry.
+__global__ void __launch_bounds__(256) ssd_cumsum_kernel(lq_ssd_problem p) {
+  extern __shared__ float s_dtv[];  // [C][33]
+  const int c = blockIdx.x, b = blockIdx.y, h0 = blockIdx.z * 32;
   const int C = p.chunk, NC = p.L / C;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float a_scale = p.A_log_scale_dev ? *p.A_log_scale_dev : p.A_log_scale;
   const float d_scale = p.dt_scale_dev ? *p.dt_scale_dev : p.dt_scale;
-  const float A = -expf(__fmul_rn(a_scale, p.A_log[h]));
-  const float bias = p.dt_bias ? p.dt_bias[h] : 0.f;
-  double run = 0.0;
-  const size_t obase = (((size_t)b * p.H + h) * NC + c) * C;
-  for (int t0 = 0; t0 < C; t0 += 16) {
-    float raw[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) raw[i] = __ldg(p.dt_in + ((size_t)b * p.L + (size_t)c * C + t0 + i) * p.H + h);
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float x = __fmul_rn(d_scale, raw[i]);
+  {
+    const int h = h0 + lane;
+    const bool live = h < p.H;
+    const float bias = (p.dt_bias && live) ? p.dt_bias[h] : 0.f;
+    const float* src = p.dt_in + ((size_t)b * p.L + (size_t)c * C) * p.H + h;
+    for (int t = warp; t < C; t += 8) {
+      float x = live ? __ldg(src + (size_t)t * p.H) : 0.f;
+      x = __fmul_rn(d_scale, x);
       if (p.dt_bias) x = __fadd_rn(x, bias);
       if (p.dt_softplus) x = x > 20.f ? x : logf(__fadd_rn(1.0f, expf(x)));
       x = fminf(fmaxf(x, p.dt_min), p.dt_max);
-      p.dt[obase + t0 + i] = x;
-      run += (double)__fmul_rn(x, A);
-      p.dA[obase + t0 + i] = (float)run;
+      s_dtv[t * 33 + lane] = x;
+    }
+  }
+  __syncthreads();
+  for (int hl = warp; hl < 32; hl += 8) {
+    const int h = h0 + hl;
+    if (h >= p.H) break;
+    const float A = -expf(__fmul_rn(a_scale, p.A_log[h]));
+    const size_t obase = (((size_t)b * p.H + h) * NC + c) * C;
+    double carry = 0.0;
+    for (int t0 = 0; t0 < C; t0 += 32) {
+      const float x = s_dtv[(t0 + lane) * 33 + hl];
+      p.dt[obase + t0 + lane] = x;
+      double v = (double)__fmul_rn(x, A);
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const double o = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= d) v += o;
+      }
+      v += carry;
+      p.dA[obase + t0 + lane] = (float)v;
+      carry = __shfl_sync(0xffffffffu, v, 31);
     }
   }
 }
@@ -389,6 +408,18 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4+%5];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr), "n"(IMM));
 }
+// exp(x) as ex2.approx.ftz(x log2 e): decay factors only, where a denormal result may as well be zero
+__device__ __forceinline__ float exp_ftz(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(__fmul_rn(x, 1.4426950408889634f)));
+  return y;
+}
+// first product of an INT8 accumulator chain: C = 0 without zeroing registers
+__device__ __forceinline__ void mma_s8_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+               : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
 // Two INT8 codes (bytes LO and LO+1 of w, each XOR 0x80) times a half2 factor: the bytes become the low mantissa
 // bits of 1024 in fp16 (exact), 1152 is subtracted (exact) and the product is rounded once.
 template <int LO>
@@ -401,12 +432,13 @@ __device__ __forceinline__ uint32_t codes_times_half2(uint32_t w_xor80, uint32_t
 // One k16 step of the causal product: A fragment af against 64 value channels whose x rows ldmatrix reads at
 // base[n2] ^ xorv (+ IMM bytes).
 template <int IMM>
-__device__ __forceinline__ void scan_kstep(float (&conv)[8][4], const uint32_t (&af)[4], const uint32_t (&base)[4], uint32_t xorv) {
+__device__ __forceinline__ void scan_kstep(float (&conv)[8][4], const uint32_t (&af)[4], uint32_t base, uint32_t xorv) {
   // the four fragment loads go out together: the assembly statements issue in program order, and a load placed
-  // between two tiles' products would expose its latency four times per step
+  // between two tiles' products would expose its latency four times per step. Value-tile pair n2 sits 32 n2 bytes
+  // further along the swizzled row, which is an XOR on the same address bits as the step's.
   uint32_t r[4][4];
 #pragma unroll
-  for (int n2 = 0; n2 < 4; ++n2) ldsm_x4_trans<IMM>(r[n2], base[n2] ^ xorv);
+  for (int n2 = 0; n2 < 4; ++n2) ldsm_x4_trans<IMM>(r[n2], base ^ (xorv ^ (uint32_t)(n2 << 5)));
 #pragma unroll
   for (int n2 = 0; n2 < 4; ++n2) {
     mma_f16(conv[2 * n2], af[0], af[1], af[2], af[3], r[n2][0], r[n2][1]);
@@ -435,7 +467,8 @@ __global__ void __launch_bounds__(256, 2) ssd_chunk_scan_kernel(lq_ssd_problem p
 
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int grp = h / (p.H / p.G);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // tells the compiler the tile index is warp-uniform
   const int g = lane >> 2, j = lane & 3;
   const size_t cbase = (((size_t)b * p.H + h) * NC + c) * C;
 
@@ -487,13 +520,9 @@ __global__ void __launch_bounds__(256, 2) ssd_chunk_scan_kernel(lq_ssd_problem p
   // (one 16-byte load of CB codes per row and group); "single" steps cover 16 tokens, lane j owning 4j + e.
   const int mi = lane >> 3, rr = lane & 7;
   const uint32_t sx_u32 = (uint32_t)__cvta_generic_to_shared(s_x);
-  uint32_t baseG[4], baseS[4];
-#pragma unroll
-  for (int n2 = 0; n2 < 4; ++n2) {
-    const uint32_t piece = (uint32_t)((2 * n2 + (mi >> 1)) ^ rr) << 4;  // f() of the lane's row without the step bits
-    baseG[n2] = sx_u32 + (16 * (rr >> 1) + 2 * (mi & 1) + (rr & 1)) * 128 + piece;
-    baseS[n2] = sx_u32 + (4 * (rr >> 1) + 2 * (mi & 1) + (rr & 1)) * 128 + piece;
-  }
+  const uint32_t piece0 = (uint32_t)((mi >> 1) ^ rr) << 4;  // f() of the lane's row without the step bits, value tiles 0/1
+  const uint32_t baseG = sx_u32 + (16 * (rr >> 1) + 2 * (mi & 1) + (rr & 1)) * 128 + piece0;
+  const uint32_t baseS = sx_u32 + (4 * (rr >> 1) + 2 * (mi & 1) + (rr & 1)) * 128 + piece0;
 
   for (int it = 0; it * 8 < MT; ++it) {
     const int mt = (it & 1) ? it * 8 + 7 - warp : it * 8 + warp;  // pair light and heavy causal rows
@@ -531,24 +560,23 @@ __global__ void __launch_bounds__(256, 2) ssd_chunk_scan_kernel(lq_ssd_problem p
     for (int k = 2 * lane; k < 16 * mt; k += 64) {
       const float2 d = *reinterpret_cast<const float2*>(s_dA + k), t = *reinterpret_cast<const float2*>(s_dts + k);
       *reinterpret_cast<__half2*>(tab + k) =
-          __floats2half2_rn(__fmul_rn(__expf(__fsub_rn(dref, d.x)), t.x), __fmul_rn(__expf(__fsub_rn(dref, d.y)), t.y));
+          __floats2half2_rn(__fmul_rn(exp_ftz(__fsub_rn(dref, d.x)), t.x), __fmul_rn(exp_ftz(__fsub_rn(dref, d.y)), t.y));
     }
     __syncwarp();
 
     // ---- state read (INT8), entered at the tile's first row
     float conv[8][4];
     {
-      const float er = __expf(dref);
+      const float er = exp_ftz(dref);
       // eight independent accumulator chains: the products of one value tile would otherwise wait on each other
       int acc[8][4];
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0;
 #pragma unroll
       for (int kk = 0; kk < N / 64; ++kk) {
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
           const uint4 bs = *reinterpret_cast<const uint4*>(s_S + frag_off(8 * nt + g, 4 * kk + j));
-          mma_s8(acc[nt], qa[kk].x, qb[kk].x, qa[kk].y, qb[kk].y, bs.x, bs.y);
+          if (kk == 0) mma_s8_first(acc[nt], qa[kk].x, qb[kk].x, qa[kk].y, qb[kk].y, bs.x, bs.y);
+          else mma_s8(acc[nt], qa[kk].x, qb[kk].x, qa[kk].y, qb[kk].y, bs.x, bs.y);
           mma_s8(acc[nt], qa[kk].z, qb[kk].z, qa[kk].w, qb[kk].w, bs.z, bs.w);
         }
       }
@@ -575,9 +603,7 @@ __global__ void __launch_bounds__(256, 2) ssd_chunk_scan_kernel(lq_ssd_problem p
       const uint4 tv0 = *reinterpret_cast<const uint4*>(tab + 64 * q + 16 * j);       // steps 0, 1
       const uint4 tv1 = *reinterpret_cast<const uint4*>(tab + 64 * q + 16 * j + 8);   // steps 2, 3
       const uint32_t tv[8] = {tv0.x, tv0.y, tv0.z, tv0.w, tv1.x, tv1.y, tv1.z, tv1.w};
-      uint32_t bq[4];
-#pragma unroll
-      for (int n2 = 0; n2 < 4; ++n2) bq[n2] = baseG[n2] + q * 8192;
+      const uint32_t bq = baseG + q * 8192;
       {
         const uint32_t af[4] = {codes_times_half2<0>(wa[0], tv[0]), codes_times_half2<0>(wb[0], tv[0]),
                                 codes_times_half2<2>(wa[0], tv[1]), codes_times_half2<2>(wb[0], tv[1])};
@@ -602,9 +628,7 @@ __global__ void __launch_bounds__(256, 2) ssd_chunk_scan_kernel(lq_ssd_problem p
       gb = nb;
     }
     // ---- single steps of the partial group, below the diagonal (at most three)
-    uint32_t bs_[4];
-#pragma unroll
-    for (int n2 = 0; n2 < 4; ++n2) bs_[n2] = baseS[n2] + qfull * 8192;
+    const uint32_t bs_ = baseS + qfull * 8192;
 #pragma unroll
     for (int u = 0; u < 3; ++u) {
       if (u < rem) {
@@ -619,7 +643,7 @@ __global__ void __launch_bounds__(256, 2) ssd_chunk_scan_kernel(lq_ssd_problem p
     }
     // ---- row factor, then the diagonal tile per element
     {
-      const float ea = __expf(__fsub_rn(dAa, dref)), eb = __expf(__fsub_rn(dAb, dref));
+      const float ea = exp_ftz(__fsub_rn(dAa, dref)), eb = exp_ftz(__fsub_rn(dAb, dref));
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
         conv[nt][0] *= ea; conv[nt][1] *= ea; conv[nt][2] *= eb; conv[nt][3] *= eb;
@@ -635,27 +659,22 @@ __global__ void __launch_bounds__(256, 2) ssd_chunk_scan_kernel(lq_ssd_problem p
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int kl = 4 * j + e;  // token within the tile; rows g and g + 8
-        va[e] = (g >= kl) ? __fmul_rn(__fmul_rn(fa[e], __expf(__fsub_rn(dAa, dk[e]))), sk[e]) : 0.f;
-        vb[e] = (g + 8 >= kl) ? __fmul_rn(__fmul_rn(fb[e], __expf(__fsub_rn(dAb, dk[e]))), sk[e]) : 0.f;
+        va[e] = (g >= kl) ? __fmul_rn(__fmul_rn(fa[e], exp_ftz(__fsub_rn(dAa, dk[e]))), sk[e]) : 0.f;
+        vb[e] = (g + 8 >= kl) ? __fmul_rn(__fmul_rn(fb[e], exp_ftz(__fsub_rn(dAb, dk[e]))), sk[e]) : 0.f;
       }
       const uint32_t af[4] = {Act<__half>::pack2(va[0], va[1]), Act<__half>::pack2(vb[0], vb[1]),
                               Act<__half>::pack2(va[2], va[3]), Act<__half>::pack2(vb[2], vb[3])};
-      uint32_t bd[4];
-#pragma unroll
-      for (int n2 = 0; n2 < 4; ++n2) bd[n2] = bs_[n2] + rem * 2048;
-      scan_kstep<0>(conv, af, bd, (uint32_t)rem << 5);
+      scan_kstep<0>(conv, af, bs_ + rem * 2048, (uint32_t)rem << 5);
     }
     // ---- D*x residual, store fp16
     {
-      const uint8_t* xa_row = s_x + ma * 128 + 4 * j;
-      const uint8_t* xb_row = s_x + mb * 128 + 4 * j;
-      const int fa_ = x_piece(ma, 0), fb_ = x_piece(mb, 0);
+      const uint32_t xa_row = ma * 128 + 4 * j + (x_piece(ma, 0) << 4), xb_row = mb * 128 + 4 * j + (x_piece(mb, 0) << 4);
       __half* oa_p = op + (size_t)ma * orow;
       __half* ob_p = op + (size_t)mb * orow;
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
-        const float2 xa = __half22float2(*reinterpret_cast<const __half2*>(xa_row + ((nt ^ fa_) << 4)));
-        const float2 xb = __half22float2(*reinterpret_cast<const __half2*>(xb_row + ((nt ^ fb_) << 4)));
+        const float2 xa = __half22float2(*reinterpret_cast<const __half2*>(s_x + (xa_row ^ (nt << 4))));
+        const float2 xb = __half22float2(*reinterpret_cast<const __half2*>(s_x + (xb_row ^ (nt << 4))));
         const float2 Dv = *reinterpret_cast<const float2*>(s_D + 8 * nt + 2 * j);
         *reinterpret_cast<uint32_t*>(oa_p + 8 * nt) = Act<__half>::pack2(fmaf(xa.x, Dv.x, conv[nt][0]), fmaf(xa.y, Dv.y, conv[nt][1]));
         *reinterpret_cast<uint32_t*>(ob_p + 8 * nt) = Act<__half>::pack2(fmaf(xb.x, Dv.x, conv[nt][2]), fmaf(xb.y, Dv.y, conv[nt][3]));
@@ -770,8 +789,7 @@ using namespace lq;
 extern "C" int lq_ssd_chunk_cumsum(const lq_ssd_problem* p, lq_stream stream) {
   if (int e = ssd_check(p, "chunk_cumsum")) return e;
   if (!p->dt_in || !p->A_log || !p->dt || !p->dA) return fail(LQ_ERR_NULL, "chunk_cumsum: dt_in, A_log, dt, dA required");
-  if (p->H > 1024) return fail(LQ_ERR_UNSUPPORTED, "chunk_cumsum: more than 1024 heads");
-  ssd_cumsum_kernel<<<dim3(p->L / p->chunk, p->B), ((p->H + 31) / 32) * 32, 0, (cudaStream_t)stream>>>(*p);
+  ssd_cumsum_kernel<<<dim3(p->L / p->chunk, p->B, (p->H + 31) / 32), 256, (size_t)p->chunk * 33 * sizeof(float), (cudaStream_t)stream>>>(*p);
   return check_launch("ssd_cumsum_kernel");
 }
 
