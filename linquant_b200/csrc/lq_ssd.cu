@@ -110,53 +110,45 @@ __global__ void __launch_bounds__(256) ssd_state_passing_kernel(const int8_t* st
     for (int c = threadIdx.x; c < NC; c += 256) s_gq[c] = round_half_away(__fmul_rn(expf(dAl[(size_t)c * C]), 128.f), 127.f);
   }
   __syncthreads();
-  const int d0 = (blockIdx.x * 256 + threadIdx.x) * 16;
+  // eight state bytes per thread: the walk over the chunks is serial, so the threads have to be many
+  const int d0 = (blockIdx.x * 256 + threadIdx.x) * 8;
   if (d0 >= D) return;
-  int s32[16];
+  int s32[8];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) s32[i] = 0;
+  for (int i = 0; i < 8; ++i) s32[i] = 0;
+  // stored copy: clamp to +-127 (the lower bound by hand, the saturating pack gives the upper one)
+  auto codes = [&]() {
+    int m[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m[i] = max(s32[i], -127);
+    return make_uint2(pack_sat_s8x2(m[1], m[0], pack_sat_s8x2(m[3], m[2], 0u)), pack_sat_s8x2(m[5], m[4], pack_sat_s8x2(m[7], m[6], 0u)));
+  };
   const size_t cstride = (size_t)H * D;
   const int8_t* src = states + ((size_t)b * NC * H + h) * D + d0;
   int8_t* dst = out + ((size_t)b * NC * H + h) * D + d0;
   constexpr int DEPTH = 4;  // chunk tiles in flight per thread
-  uint4 ring[DEPTH];
+  uint2 ring[DEPTH];
 #pragma unroll
   for (int u = 0; u < DEPTH; ++u)
-    if (u < NC) ring[u] = __ldg(reinterpret_cast<const uint4*>(src + (size_t)u * cstride));
+    if (u < NC) ring[u] = __ldg(reinterpret_cast<const uint2*>(src + (size_t)u * cstride));
   for (int c0 = 0; c0 < NC; c0 += DEPTH) {
 #pragma unroll
     for (int u = 0; u < DEPTH; ++u) {
       const int c = c0 + u;
       if (c >= NC) break;
-      const uint4 cur = ring[u];
-      if (c + DEPTH < NC) ring[u] = __ldg(reinterpret_cast<const uint4*>(src + (size_t)(c + DEPTH) * cstride));
-      uint32_t o[4];
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        int cd[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) cd[k] = min(max(s32[4 * w + k], -127), 127);
-        o[w] = pack4(cd[0], cd[1], cd[2], cd[3]);
-      }
-      *reinterpret_cast<uint4*>(dst + (size_t)c * cstride) = make_uint4(o[0], o[1], o[2], o[3]);
+      const uint2 cur = ring[u];
+      if (c + DEPTH < NC) ring[u] = __ldg(reinterpret_cast<const uint2*>(src + (size_t)(c + DEPTH) * cstride));
+      *reinterpret_cast<uint2*>(dst + (size_t)c * cstride) = codes();
       const int gq = s_gq[c];
-      const uint32_t cw[4] = {cur.x, cur.y, cur.z, cur.w};
+      const uint32_t cw[2] = {cur.x, cur.y};
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
+      for (int i = 0; i < 8; ++i) {
         const int nw = (int)(int8_t)((cw[i >> 2] >> (8 * (i & 3))) & 0xff);
         s32[i] = ((s32[i] * gq + 64) >> 7) + nw;
       }
     }
   }
-  uint32_t o[4];
-#pragma unroll
-  for (int w = 0; w < 4; ++w) {
-    int cd[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) cd[k] = min(max(s32[4 * w + k], -127), 127);
-    o[w] = pack4(cd[0], cd[1], cd[2], cd[3]);
-  }
-  *reinterpret_cast<uint4*>(final_state + ((size_t)b * H + h) * D + d0) = make_uint4(o[0], o[1], o[2], o[3]);
+  *reinterpret_cast<uint2*>(final_state + ((size_t)b * H + h) * D + d0) = codes();
 }
 
 // ------------------------------------------------------------------------------------------------ chunk state
@@ -797,8 +789,8 @@ extern "C" int lq_ssd_state_passing(const lq_ssd_problem* p, lq_stream stream) {
   if (int e = ssd_check(p, "state_passing")) return e;
   if (!p->states || !p->passed || !p->final_state || !p->dA) return fail(LQ_ERR_NULL, "state_passing: states, passed, final_state, dA required");
   const int D = p->P * p->N;
-  if (D % 16 != 0) return fail(LQ_ERR_SHAPE, "state_passing: P*N must be a multiple of 16");
-  dim3 grid((D / 16 + 255) / 256, p->H, p->B);
+  if (D % 8 != 0) return fail(LQ_ERR_SHAPE, "state_passing: P*N must be a multiple of 8");
+  dim3 grid((D / 8 + 255) / 256, p->H, p->B);
   if ((size_t)(p->L / p->chunk) * sizeof(int) > 48 * 1024) return fail(LQ_ERR_UNSUPPORTED, "state_passing: more than 12288 chunks");
   ssd_state_passing_kernel<<<grid, 256, (size_t)(p->L / p->chunk) * sizeof(int), (cudaStream_t)stream>>>(p->states, p->dA, p->passed, p->final_state, p->H,
                                                                     p->L / p->chunk, p->chunk, D);
