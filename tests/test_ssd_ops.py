@@ -97,6 +97,29 @@ def test_sub_ops_match_oracle(chunk, N, dtype):
     _ssd.check_status(out.device)  # no tcgen05 kernel gave up on a barrier
 
 
+@pytest.mark.parametrize("H,chunk", [(40, 128), (80, 256), (33, 64)])
+def test_cumsum_and_state_passing_many_heads(H, chunk):
+    """More heads than one 32-head block of the cumsum kernel (with a ragged last block), a dt bias and dt limits; state
+    passing both through the chunk-end view of the cumsum (read in place) and through a dense copy of it."""
+    from linquant_b200.kernels.mamba2 import ssd_combined as sc
+
+    g = torch.Generator().manual_seed(5)
+    B, L, dim = 2, 4 * chunk, 1024
+    dt_raw = torch.randn(B, L, H, generator=g) * 0.5 - 2.0
+    A_log = torch.rand(H, generator=g) * 2.7
+    bias = torch.randn(H, generator=g) * 0.3
+    dA_ref, dt_ref = so.chunk_cumsum(dt_raw, 0.7, A_log, 1.1, chunk, bias, True, (0.01, 0.5))
+    dA, dt = sc._quant_chunk_cumsum_fwd(cu(dt_raw), 0.7, cu(A_log), 1.1, chunk, cu(bias), True, (0.01, 0.5))
+    assert rel_l2(dt, dt_ref) < 1e-6 and (dA.cpu() - dA_ref).abs().max() < 1e-5 * dA_ref.abs().max()
+    states = torch.randint(-127, 128, (B, L // chunk, H, dim), generator=g, dtype=torch.int8)
+    sp_ref, fin_ref = so.state_passing(states, dA_ref[..., -1])
+    dAd = cu(dA_ref)
+    for arg in (dAd[..., -1], dAd[..., -1].contiguous()):
+        sp, fin = sc._fixedpoint_state_passing_fwd(cu(states), arg)
+        code_mismatch(sp, sp_ref, "passed states", budget=1e-3, max_step=2)
+        code_mismatch(fin, fin_ref, "final state", budget=1e-3, max_step=2)
+
+
 @pytest.mark.parametrize("keyside", [False, True])
 def test_combined_matches_oracle(keyside):
     from linquant_b200.kernels.mamba2.ssd_combined import _quant_mamba_chunk_scan_combined_fwd as fwd
