@@ -83,20 +83,27 @@ __global__ void __launch_bounds__(128) ssd_chunk_state_tc_kernel(const __grid_co
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const uint32_t tbase = *s_tbase;
 
-  // ---- quantise and transpose x into the A tiles
+  // ---- quantise and transpose x into the A tiles. Shared-memory accesses go through 32-bit shared addresses with the
+  // swizzles reduced to one XOR (loads) or an immediate offset (stores): generic 64-bit addressing cost more integer
+  // instructions here than the quantiser itself.
+  const uint32_t raw_u32 = smem_u32(s_raw), sA_u32 = smem_u32(s_A);
   for (int blk = warp; blk < C / 32; blk += 4) {
     const int t0 = 32 * blk + 4 * tq;           // first of this lane's four tokens
     const int kb = t0 >> 7, tl = t0 & 127;
     const int ch16 = tl >> 4, off = tl & 15;
-    float gk[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) gk[i] = s_gate[t0 + i];
+    const float4 gk4 = *reinterpret_cast<const float4*>(s_gate + t0);
+    const float gk[4] = {gk4.x, gk4.y, gk4.z, gk4.w};
+    // row t0+i, piece (pg ^ tq), bytes 4cp..: the row base carries tq in the piece bits, pg is XORed in
+    const uint32_t ld0 = raw_u32 + t0 * 128 + (tq << 4) + 4 * cp;
+    const int r0 = 2 * cp, r1 = 2 * cp + 1;  // rows within the 8-row group pg
+    const uint32_t st0 = sA_u32 + kb * 8192 + r0 * 128 + ((ch16 ^ r0) << 4) + off;
+    const uint32_t st1 = sA_u32 + kb * 8192 + r1 * 128 + ((ch16 ^ r1) << 4) + off;
 #pragma unroll
     for (int pg = 0; pg < 8; ++pg) {
       int c0v[4], c1v[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const uint32_t raw = *reinterpret_cast<const uint32_t*>(s_raw + (t0 + i) * 128 + ((pg ^ tq) << 4) + 4 * cp);
+        const uint32_t raw = lds_u32((ld0 + i * 128) ^ (pg << 4));
         float x0, x1;
         if (std::is_same<T, __half>::value) {
           const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&raw));
@@ -110,12 +117,8 @@ __global__ void __launch_bounds__(128) ssd_chunk_state_tc_kernel(const __grid_co
         c0v[i] = __float2int_rz(__fadd_rn(y0, copysignf(0.5f, y0)));
         c1v[i] = __float2int_rz(__fadd_rn(y1, copysignf(0.5f, y1)));
       }
-      const uint32_t w0 = pack_sat_s8x2(c0v[1], c0v[0], pack_sat_s8x2(c0v[3], c0v[2], 0u));
-      const uint32_t w1 = pack_sat_s8x2(c1v[1], c1v[0], pack_sat_s8x2(c1v[3], c1v[2], 0u));
-      const int r0 = 2 * cp, r1 = 2 * cp + 1;  // row within the 8-row group pg
-      uint8_t* grp8 = s_A + kb * 8192 + pg * 1024;
-      *reinterpret_cast<uint32_t*>(grp8 + r0 * 128 + ((ch16 ^ r0) << 4) + off) = w0;
-      *reinterpret_cast<uint32_t*>(grp8 + r1 * 128 + ((ch16 ^ r1) << 4) + off) = w1;
+      sts_u32(st0 + pg * 1024, pack_sat_s8x2(c0v[1], c0v[0], pack_sat_s8x2(c0v[3], c0v[2], 0u)));
+      sts_u32(st1 + pg * 1024, pack_sat_s8x2(c1v[1], c1v[0], pack_sat_s8x2(c1v[3], c1v[2], 0u)));
     }
   }
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy writes -> visible to the tensor core
@@ -156,6 +159,7 @@ __global__ void __launch_bounds__(128) ssd_chunk_state_tc_kernel(const __grid_co
     const float ra = __fmul_rn(p.alpha_hp[h * P + pa] / p.state_scale[h * P + pa], bs);
     const float rb = __fmul_rn(p.alpha_hp[h * P + pb] / p.state_scale[h * P + pb], bs);
     const uint32_t tq_addr = tbase + ((uint32_t)(32 * warp) << 16);
+    const uint32_t out_a = smem_u32(s_out) + pa * N + 2 * j, out_b = smem_u32(s_out) + pb * N + 2 * j;
 #pragma unroll
     for (int ng = 0; ng < N / 32; ++ng) {
       uint32_t r[16];
@@ -163,13 +167,13 @@ __global__ void __launch_bounds__(128) ssd_chunk_state_tc_kernel(const __grid_co
       asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
       for (int n4 = 0; n4 < 4; ++n4) {
-        const int col = 32 * ng + 8 * n4 + 2 * j;
+        const int col = 32 * ng + 8 * n4;
         const int a0 = ssd_half_away(__fmul_rn((float)(int)r[4 * n4 + 0], ra), 127.f);
         const int a1 = ssd_half_away(__fmul_rn((float)(int)r[4 * n4 + 1], ra), 127.f);
         const int b0 = ssd_half_away(__fmul_rn((float)(int)r[4 * n4 + 2], rb), 127.f);
         const int b1 = ssd_half_away(__fmul_rn((float)(int)r[4 * n4 + 3], rb), 127.f);
-        *reinterpret_cast<uint16_t*>(s_out + pa * N + col) = (uint16_t)((a0 & 0xff) | ((a1 & 0xff) << 8));
-        *reinterpret_cast<uint16_t*>(s_out + pb * N + col) = (uint16_t)((b0 & 0xff) | ((b1 & 0xff) << 8));
+        sts_u16(out_a + col, (uint16_t)((a0 & 0xff) | ((a1 & 0xff) << 8)));
+        sts_u16(out_b + col, (uint16_t)((b0 & 0xff) | ((b1 & 0xff) << 8)));
       }
     }
   } else if (tid == 0 && status != nullptr) {

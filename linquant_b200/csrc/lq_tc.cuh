@@ -18,6 +18,14 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
   }
   return false;
 }
+// shared-memory accesses by 32-bit shared address (no generic-address arithmetic)
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts_u32(uint32_t addr, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(addr), "r"(v) : "memory"); }
+__device__ __forceinline__ void sts_u16(uint32_t addr, uint16_t v) { asm volatile("st.shared.u16 [%0], %1;\n" ::"r"(addr), "h"(v) : "memory"); }
 
 __device__ __forceinline__ uint64_t desc_kmajor_sw128(uint32_t saddr) {
   // K-major operand, 128-byte rows, 128B swizzle: 8-row groups are 1024 bytes apart; descriptor version 1
