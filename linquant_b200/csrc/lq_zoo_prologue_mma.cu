@@ -29,15 +29,30 @@ __device__ __forceinline__ uint32_t pack4s(const int (&c)[8], int o) {
   return pack_sat2(c[o + 1], c[o], pack_sat2(c[o + 3], c[o + 2], 0u));
 }
 
-template <typename T>
-__device__ __forceinline__ void mma_act(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1);
-template <>
-__device__ __forceinline__ void mma_act<__half>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  mma_f16(c, a0, a1, a2, a3, b0, b1);
-}
-template <>
-__device__ __forceinline__ void mma_act<__nv_bfloat16>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  mma_bf16(c, a0, a1, a2, a3, b0, b1);
+// Hadamard product step: the B fragment arrives as one 64-bit register pair (the MMA wants its two B registers adjacent;
+// separate 32-bit operands chosen per step made the compiler copy them into place before every instruction), and the
+// first step of a chain takes C = 0 instead of zeroed accumulators.
+template <typename T, bool FIRST>
+__device__ __forceinline__ void mma_had(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint64_t bp) {
+  if (std::is_same<T, __half>::value) {
+    if (FIRST)
+      asm volatile("{\n.reg .b32 b0, b1;\nmov.b64 {b0, b1}, %8;\n"
+                   "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {b0,b1}, {%9,%9,%9,%9};\n}\n"
+                   : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "l"(bp), "f"(0.f));
+    else
+      asm volatile("{\n.reg .b32 b0, b1;\nmov.b64 {b0, b1}, %8;\n"
+                   "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {b0,b1}, {%0,%1,%2,%3};\n}\n"
+                   : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "l"(bp));
+  } else {
+    if (FIRST)
+      asm volatile("{\n.reg .b32 b0, b1;\nmov.b64 {b0, b1}, %8;\n"
+                   "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {b0,b1}, {%9,%9,%9,%9};\n}\n"
+                   : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "l"(bp), "f"(0.f));
+    else
+      asm volatile("{\n.reg .b32 b0, b1;\nmov.b64 {b0, b1}, %8;\n"
+                   "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {b0,b1}, {%0,%1,%2,%3};\n}\n"
+                   : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "l"(bp));
+  }
 }
 
 template <typename T, int K, int V, bool Q127>
@@ -77,6 +92,9 @@ __global__ void __launch_bounds__(256, 2) zoo_prologue_linear_mma_kernel(Prologu
     hb0 = (one | (L << 15)) | ((one | ((L ^ (g & 1)) << 15)) << 16);
     hb0n = hb0 ^ 0x80008000u;
   }
+  // the four (b0, b1) sign combinations as register pairs, index 2*neg(b0) + neg(b1)
+  const uint64_t hbp[4] = {(uint64_t)hb0 | ((uint64_t)hb0 << 32), (uint64_t)hb0 | ((uint64_t)hb0n << 32),
+                           (uint64_t)hb0n | ((uint64_t)hb0 << 32), (uint64_t)hb0n | ((uint64_t)hb0n << 32)};
 
   // persistent CTAs: tile t = (batch, chunk, head) with the head fastest, strided by the grid: every CTA gets the same
   // number of tiles to within one, and the CTAs in flight read all heads of the same tokens (adjacent in memory)
@@ -175,7 +193,9 @@ __global__ void __launch_bounds__(256, 2) zoo_prologue_linear_mma_kernel(Prologu
     for (int op = 0; op < 2; ++op) {
       const bool is_q = op == 0;
       const int half = warp >> 2;
-      const uint32_t hb1 = half ? hb0n : hb0, hb1n = half ? hb0 : hb0n;
+      // the channel half of the warp flips the sign of the steps whose input channels carry that bit: applied to the
+      // A fragments of those steps (an XOR on their way into the MMA's register quad)
+      const uint32_t sflip = half ? 0x80008000u : 0u;
       const uint8_t* src = s_qk + buf * 2 * RAW_Q + (is_q ? 0 : RAW_Q);
       uint4 ra[K / 32], rb[K / 32];
 #pragma unroll
@@ -192,19 +212,18 @@ __global__ void __launch_bounds__(256, 2) zoo_prologue_linear_mma_kernel(Prologu
         if (rot) {
           float acc[4][4];
 #pragma unroll
-          for (int n4 = 0; n4 < 4; ++n4) acc[n4][0] = acc[n4][1] = acc[n4][2] = acc[n4][3] = 0.f;
-#pragma unroll
           for (int s = 0; s < KS; ++s) {
             const uint32_t* wa = reinterpret_cast<const uint32_t*>(&ra[s >> 1]);
             const uint32_t* wb = reinterpret_cast<const uint32_t*>(&rb[s >> 1]);
-            const uint32_t a0 = wa[2 * (s & 1)], a2 = wa[2 * (s & 1) + 1], a1 = wb[2 * (s & 1)], a3 = wb[2 * (s & 1) + 1];
+            const bool dep = K == 128 ? ((s >> 2) & 1) : ((s >> 1) & 1);
+            const uint32_t fl = dep ? sflip : 0u;
+            const uint32_t a0 = wa[2 * (s & 1)] ^ fl, a2 = wa[2 * (s & 1) + 1] ^ fl, a1 = wb[2 * (s & 1)] ^ fl, a3 = wb[2 * (s & 1) + 1] ^ fl;
 #pragma unroll
             for (int n4 = 0; n4 < 4; ++n4) {
               // output n-tile nt = 4*ng + n4; its bits above n4 are ngl (compile time) and the warp's channel half
               const int Uc = ((s & 1) & ((n4 >> 1) & 1)) ^ (K == 128 ? (((s >> 1) & 1) & (ngl & 1)) : 0);
-              const bool dep = K == 128 ? ((s >> 2) & 1) : ((s >> 1) & 1);
-              const uint32_t base = dep ? hb1 : hb0, neg = dep ? hb1n : hb0n;
-              mma_act<T>(acc[n4], a0, a1, a2, a3, Uc ? neg : base, (Uc ^ (n4 & 1)) ? neg : base);
+              if (s == 0) mma_had<T, true>(acc[n4], a0, a1, a2, a3, hbp[2 * Uc + (Uc ^ (n4 & 1))]);
+              else mma_had<T, false>(acc[n4], a0, a1, a2, a3, hbp[2 * Uc + (Uc ^ (n4 & 1))]);
             }
           }
           const float4 s0 = *reinterpret_cast<const float4*>(s_sgn + 32 * ng + 8 * j);
