@@ -98,40 +98,58 @@ __global__ void __launch_bounds__(256, 2) zoo_prologue_linear_mma_kernel(Prologu
 
   // persistent CTAs: tile t = (batch, chunk, head) with the head fastest, strided by the grid: every CTA gets the same
   // number of tiles to within one, and the CTAs in flight read all heads of the same tokens (adjacent in memory)
-  auto stage_qk = [&](int t, int buf) {
-    const int h = t % a.H, c = (t / a.H) % a.NT, b = t / (a.H * a.NT);
-    uint8_t* dst = s_qk + buf * 2 * RAW_Q;
-    const size_t row0 = ((size_t)b * a.T + (size_t)c * C) * a.H + h;
-    for (int i = tid; i < C * (K / 8); i += 256) {
-      const int tk = i / (K / 8), ch = i % (K / 8);
-      const int sw = (ch ^ (((tk >> 1) & 1) << 2)) << 4;
-      cp_async16(dst + tk * (K * 2) + sw, qp + (row0 + (size_t)tk * a.H) * K + 8 * ch);
-      cp_async16(dst + RAW_Q + tk * (K * 2) + sw, kp + (row0 + (size_t)tk * a.H) * K + 8 * ch);
+  // staging copies: thread -> (token row r0 + RPI it, 16-byte piece ch0); the swizzle bit of the row does not change
+  // with it, so source and destination advance by constants. Tile indices are decoded once per tile (integer
+  // divisions by run-time extents are the expensive part of this bookkeeping).
+  constexpr int PPRK = K / 8, RPIK = 256 / PPRK, PPRV = V / 8, RPIV = 256 / PPRV;
+  const int rk0 = tid / PPRK, chk0 = tid % PPRK, rv0 = tid / PPRV, chv0 = tid % PPRV;
+  const uint32_t dstk0 = rk0 * (K * 2) + ((chk0 ^ (((rk0 >> 1) & 1) << 2)) << 4);
+  const uint32_t dstv0 = rv0 * (V * 2) + ((chv0 ^ (((rv0 >> 1) & 1) << 2)) << 4);
+  auto stage_qk = [&](int h, int c, int b, int buf) {
+    uint8_t* dst = s_qk + buf * 2 * RAW_Q + dstk0;
+    const size_t off = (((size_t)b * a.T + (size_t)c * C + rk0) * a.H + h) * K + 8 * chk0;
+    const T* sq = qp + off;
+    const T* sk = kp + off;
+    const size_t step = (size_t)RPIK * a.H * K;
+#pragma unroll
+    for (int it = 0; it < C / RPIK; ++it) {
+      cp_async16(dst + it * RPIK * (K * 2), sq);
+      cp_async16(dst + RAW_Q + it * RPIK * (K * 2), sk);
+      sq += step;
+      sk += step;
     }
   };
-  auto stage_v = [&](int t) {
+  auto stage_v = [&](int h, int c, int b) {
     if (a.skip_v) return;
-    const int h = t % a.H, c = (t / a.H) % a.NT, b = t / (a.H * a.NT);
-    const size_t row0 = ((size_t)b * a.T + (size_t)c * C) * a.H + h;
-    for (int i = tid; i < C * (V / 8); i += 256) {
-      const int tk = i / (V / 8), ch = i % (V / 8);
-      cp_async16(s_v + tk * (V * 2) + ((ch ^ (((tk >> 1) & 1) << 2)) << 4), vp + (row0 + (size_t)tk * a.H) * V + 8 * ch);
+    const T* sv = vp + (((size_t)b * a.T + (size_t)c * C + rv0) * a.H + h) * V + 8 * chv0;
+    const size_t step = (size_t)RPIV * a.H * V;
+#pragma unroll
+    for (int it = 0; it < C / RPIV; ++it) {
+      cp_async16(s_v + dstv0 + it * RPIV * (V * 2), sv);
+      sv += step;
     }
   };
-  auto load_g = [&](int t, float& g0, float& g1) {
+  auto load_g = [&](int h, int c, int b, float& g0, float& g1) {
     if (a.g == nullptr) { g0 = g1 = 0.f; return; }
-    const int h = t % a.H, c = (t / a.H) % a.NT, b = t / (a.H * a.NT);
     const size_t base = ((size_t)b * a.T + (size_t)c * C) * a.H + h;
     g0 = __ldg(a.g + base + (size_t)lane * a.H);
     g1 = __ldg(a.g + base + (size_t)(lane + 32) * a.H);
   };
+  auto decode = [&](int t, int& h, int& c, int& b) {
+    h = t % a.H;
+    const int r = t / a.H;
+    c = r % a.NT;
+    b = r / a.NT;
+  };
   const int t_begin = blockIdx.x, t_step = gridDim.x;
   if (t_begin >= n_tiles) return;
-  stage_qk(t_begin, 0);
-  stage_v(t_begin);
+  int h, c, b, hn = 0, cn = 0, bn = 0;
+  decode(t_begin, h, c, b);
+  stage_qk(h, c, b, 0);
+  stage_v(h, c, b);
   cp_async_commit();
   float gn0, gn1;
-  load_g(t_begin, gn0, gn1);
+  load_g(h, c, b, gn0, gn1);
 
   const int mt = warp & 3;
   const int ta = 16 * mt + 2 * g, tb = ta + 1;  // this thread's two tokens of the m-tile
@@ -139,15 +157,15 @@ __global__ void __launch_bounds__(256, 2) zoo_prologue_linear_mma_kernel(Prologu
 
   int h_staged = -1;
   float inv_sq = 1.f, inv_sk = 1.f;
-  for (int t = t_begin, it = 0; t < n_tiles; t += t_step, ++it) {
-    const int h = t % a.H, c = (t / a.H) % a.NT, b = t / (a.H * a.NT);
+  for (int t = t_begin, it = 0; t < n_tiles; t += t_step, ++it, h = hn, c = cn, b = bn) {
     const size_t tile = ((size_t)b * a.H + h) * a.NT + c;
     const int buf = it & 1;
     const bool more = t + t_step < n_tiles;
     cp_async_wait<0>();
     __syncthreads();  // raw tiles of this chunk have landed; the previous chunk's compute and copy-out are done
     if (more) {
-      stage_qk(t + t_step, buf ^ 1);
+      decode(t + t_step, hn, cn, bn);
+      stage_qk(hn, cn, bn, buf ^ 1);
       cp_async_commit();
     }
     if (h != h_staged) {  // per-head channel scales (uniform branch)
@@ -183,7 +201,7 @@ __global__ void __launch_bounds__(256, 2) zoo_prologue_linear_mma_kernel(Prologu
       const float sel = (mt >> 1) ? f1 : f0;
       gca = __shfl_sync(0xffffffffu, sel, ta & 31);
       gcb = __shfl_sync(0xffffffffu, sel, tb & 31);
-      if (more) load_g(t + t_step, gn0, gn1);
+      if (more) load_g(hn, cn, bn, gn0, gn1);
     }
     const bool use_g = a.g != nullptr;
     const float da = glast - gca, db = glast - gcb;
@@ -297,7 +315,7 @@ __global__ void __launch_bounds__(256, 2) zoo_prologue_linear_mma_kernel(Prologu
     }
     __syncthreads();
     if (more) {  // the single v buffer is free again
-      stage_v(t + t_step);
+      stage_v(hn, cn, bn);
       cp_async_commit();
     }
     uint32_t* kw_out = reinterpret_cast<uint32_t*>(a.kwT + tile * (size_t)(K * C));
