@@ -23,6 +23,10 @@ __device__ __forceinline__ int q8(float x, float inv, float qmax) {
   return __float2int_rz(__fadd_rn(y, copysignf(0.5f, y)));
 }
 
+// Four codes on the +-127 grid, packed: the lower clamp by hand, the upper one by the saturating pack (a value above
+// 127.5 truncates to >= 127 and saturates to 127). Same codes as q8(x, inv, 127) four times and pack4.
+__device__ __forceinline__ uint32_t q8x4_127(float x0, float x1, float x2, float x3, float inv);
+
 __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
   uint32_t lo = __byte_perm((uint32_t)a, (uint32_t)b, 0x0040);
   uint32_t hi = __byte_perm((uint32_t)c, (uint32_t)d, 0x0040);
@@ -35,6 +39,13 @@ __device__ __forceinline__ uint32_t pack_sat_s8x2(int hi, int lo, uint32_t upper
   uint32_t d;
   asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;\n" : "=r"(d) : "r"(hi), "r"(lo), "r"(upper));
   return d;
+}
+__device__ __forceinline__ int q8_lower127(float x, float inv) {
+  const float y = fmaxf(__fmul_rn(x, inv), -127.f);
+  return __float2int_rz(__fadd_rn(y, copysignf(0.5f, y)));
+}
+__device__ __forceinline__ uint32_t q8x4_127(float x0, float x1, float x2, float x3, float inv) {
+  return pack_sat_s8x2(q8_lower127(x1, inv), q8_lower127(x0, inv), pack_sat_s8x2(q8_lower127(x3, inv), q8_lower127(x2, inv), 0u));
 }
 // Byte I of w, where w holds four INT8 codes XOR 0x80 (code + 128 as an unsigned byte), as an exact float: the byte
 // becomes the low mantissa bits of 2^23 and the offset is subtracted -- no trip through the conversion unit.
@@ -129,6 +140,12 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
       "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
       : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// first product of an INT8 accumulator chain: C = 0 without zeroing registers
+__device__ __forceinline__ void mma_s8_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+               : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                         uint32_t b1) {

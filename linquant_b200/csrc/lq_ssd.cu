@@ -406,12 +406,6 @@ __device__ __forceinline__ float exp_ftz(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(__fmul_rn(x, 1.4426950408889634f)));
   return y;
 }
-// first product of an INT8 accumulator chain: C = 0 without zeroing registers
-__device__ __forceinline__ void mma_s8_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
-               : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
-}
 // Two INT8 codes (bytes LO and LO+1 of w, each XOR 0x80) times a half2 factor: the bytes become the low mantissa
 // bits of 1024 in fp16 (exact), 1152 is subtracted (exact) and the product is rounded once.
 template <int LO>

@@ -93,24 +93,17 @@ __global__ void __launch_bounds__(128) zoo_state_linear_kernel(StateArgs a) {
 
     // INT8 copy of the carry entering chunk c
     {
-      int ca[8], cb[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        ca[i] = q8(carry_a[i], iss_a, 127.f);
-        cb[i] = q8(carry_b[i], iss_b, 127.f);
-      }
       int8_t* hc = hT + (size_t)c * V * K;
       *reinterpret_cast<uint2*>(hc + state_row_of_channel(va) * K + k0 + 8 * j) =
-          make_uint2(pack4(ca[0], ca[1], ca[2], ca[3]), pack4(ca[4], ca[5], ca[6], ca[7]));
+          make_uint2(q8x4_127(carry_a[0], carry_a[1], carry_a[2], carry_a[3], iss_a), q8x4_127(carry_a[4], carry_a[5], carry_a[6], carry_a[7], iss_a));
       *reinterpret_cast<uint2*>(hc + state_row_of_channel(vb) * K + k0 + 8 * j) =
-          make_uint2(pack4(cb[0], cb[1], cb[2], cb[3]), pack4(cb[4], cb[5], cb[6], cb[7]));
+          make_uint2(q8x4_127(carry_b[0], carry_b[1], carry_b[2], carry_b[3], iss_b), q8x4_127(carry_b[4], carry_b[5], carry_b[6], carry_b[7], iss_b));
     }
 
     int acc[4][4];
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
-      acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0;
-      mma_s8(acc[nt], A_lo.x, A_hi.x, A_lo.y, A_hi.y, Bq[nt].x, Bq[nt].y);
+      mma_s8_first(acc[nt], A_lo.x, A_hi.x, A_lo.y, A_hi.y, Bq[nt].x, Bq[nt].y);
       mma_s8(acc[nt], A_lo.z, A_hi.z, A_lo.w, A_hi.w, Bq[nt].z, Bq[nt].w);
     }
     float gamv[8];
