@@ -293,18 +293,19 @@ __global__ void __launch_bounds__(128) zoo_state_delta_kernel(DeltaStateArgs a) 
         int cd[2 * NTK];
 #pragma unroll
         for (int nt = 0; nt < NTK; ++nt) {
-          cd[2 * nt] = q8(carry[mt][nt][2 * hi], iss_r[i], 127.f);
-          cd[2 * nt + 1] = q8(carry[mt][nt][2 * hi + 1], iss_r[i], 127.f);
+          cd[2 * nt] = q8_lower127(carry[mt][nt][2 * hi], iss_r[i]);  // upper clamp: the saturating pack below
+          cd[2 * nt + 1] = q8_lower127(carry[mt][nt][2 * hi + 1], iss_r[i]);
         }
         uint8_t* sdst = s_h + swz_row<K>(vl, kown >> 4) + (kown & 15);
         int8_t* gdst = hc + (size_t)state_row_of_channel(v0 + vl) * K + kown;
         if (NTK == 4) {
-          const uint2 w = make_uint2(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4 % (2 * NTK)], cd[5 % (2 * NTK)],
-                                                                            cd[6 % (2 * NTK)], cd[7 % (2 * NTK)]));
+          const uint2 w = make_uint2(pack_sat_s8x2(cd[1], cd[0], pack_sat_s8x2(cd[3], cd[2], 0u)),
+                                     pack_sat_s8x2(cd[5 % (2 * NTK)], cd[4 % (2 * NTK)],
+                                                   pack_sat_s8x2(cd[7 % (2 * NTK)], cd[6 % (2 * NTK)], 0u)));
           *reinterpret_cast<uint2*>(sdst) = w;
           *reinterpret_cast<uint2*>(gdst) = w;
         } else {
-          const uint32_t w = pack4(cd[0], cd[1], cd[2], cd[3]);
+          const uint32_t w = pack_sat_s8x2(cd[1], cd[0], pack_sat_s8x2(cd[3], cd[2], 0u));
           *reinterpret_cast<uint32_t*>(sdst) = w;
           *reinterpret_cast<uint32_t*>(gdst) = w;
         }
