@@ -2,7 +2,8 @@
  * linquant_b200 — C ABI of the sm_100a INT8 chunk-prefill kernels.
  *
  * Plain pointers and sizes only; every pointer is a DEVICE pointer unless it says "host". Nothing here allocates
- * device memory: callers own inputs, outputs and the workspace. All launches go to the given stream and return
+ * device memory (the lq_peer_buffer_* set-up calls of the multi-GPU hand-off excepted): callers own inputs, outputs
+ * and the workspace. All launches go to the given stream and return
  * without synchronising. Every entry returns an lq_status (0 = ok); lq_last_error_string() gives the detail of
  * the most recent failure on the calling thread.
  *
@@ -43,6 +44,19 @@ int lq_version(void);
 unsigned long long lq_struct_bytes(int which);
 const char* lq_last_error_string(void);
 
+/* Drains `stream`, reads the device status word and clears it. Returns LQ_ERR_TIMEOUT when a kernel raised it since the
+ * last poll (the outputs of the calls in between are then not valid), LQ_OK otherwise. The launches themselves are
+ * asynchronous, so this is how a bounded device-side wait that ran out (TMA / MMA barrier, peer hand-off flag) reaches the
+ * host. No counterpart in the reference (its Triton kernels have no device-side waits). */
+int lq_status_poll(int* status, lq_stream stream);
+
+/* Self-test of the bounded-wait machinery, for test suites: one CTA initialises an mbarrier that nothing ever arrives
+ * on (no copy or MMA is issued, so nothing is in flight), optionally holds 32 tensor-memory columns meanwhile, lets the
+ * bounded wait of the tcgen05 kernels run out, raises *status, writes its own progress marks to trace[0..3]
+ * (1 = reached the wait, 2 = the wait gave up, 3 = tensor memory freed, 4 = returned normally) and returns. The GPU
+ * is not faulted or hung: the kernel ends by itself after the poll limit (about a millisecond). */
+int lq_selftest_wait_timeout(int* status, int* trace, int hold_tmem, lq_stream stream);
+
 /* ------------------------------------------------------------------------------------------------------------
  * Problem descriptor shared by the zoo-lineage entries (linear attention / Simple GLA / GLA / DeltaNet /
  * Gated DeltaNet / KDA). Layouts follow the reference: q,k [B,T,H,K], v,o [B,T,H,V] dense, act dtype f16/bf16;
@@ -76,6 +90,10 @@ typedef struct {
                                  :150-153): [V,V] fp16, TRANSPOSED, element [v'][v] = unrot[v][v']; v arrives rotated and
                                  every value-side product is multiplied by unrot before it joins the carry / the output
                                  (the delta family also takes the state read into the rotated basis); null = off */
+  int* status;                /* optional device int32 owned by the caller: when given, a kernel whose bounded wait ran out
+                                 raises THIS word instead of the workspace's, and the entries do not clear it (a host keeps
+                                 one word per device and polls it with lq_status_poll when convenient); null = the
+                                 workspace's own word, cleared by the whole-call entries */
 } lq_zoo_problem;
 
 /* Bytes of workspace the zoo entries need for this problem (a host-side computation). */
@@ -185,6 +203,18 @@ typedef struct {
                            kernel, 2 = tcgen05 + TMA kernel (d_state 128 and chunk 128 or 256 only) */
   int* status;          /* optional device int32: set to 1 by a kernel whose bounded wait on a TMA / MMA barrier ran out
                            (its output is then not valid); the caller zeroes it and reads it after synchronising */
+  /* ---- lq_ssd_state_passing only: the integer carry across calls / GPUs (all optional, null = a zero carry, nothing
+     handed on). The recurrence's carry is the unclamped INT32 state (state_passing.py:62-93), so a sequence cut into
+     segments reproduces the one-shot result bit for bit when this carry, not its INT8 copy, crosses the cut. */
+  const int* carry_in;  /* [B,H,P*N] int32 carry entering the first chunk of this call */
+  int* carry_out;       /* [B,H,P*N] int32 carry after the last chunk; may point into ANOTHER GPU's memory (a peer
+                           mapping): the kernel writes it with plain stores */
+  const unsigned* wait_flags; /* [B,H,ceil(P*N/2048)] in THIS GPU's memory: CTA i reads carry_in only after flag i >= epoch,
+                                 polling at most wait_ns nanoseconds; on expiry it raises *status and stores nothing */
+  unsigned* post_flags;       /* same shape, next to carry_out (peer memory allowed): CTA i sets flag i = epoch after its
+                                 carry_out stores are visible system-wide */
+  unsigned epoch;             /* value posted / awaited; the caller increases it on every call so flags need no reset */
+  unsigned long long wait_ns; /* bound of the flag wait (0 = 2 s) */
 } lq_ssd_problem;
 
 /* dt = clamp(softplus(dt_scale*dt + bias)), dA = dt * -exp(A_log_scale*A_log), chunk-local cumsum.
@@ -207,8 +237,20 @@ int lq_ssd_chunk_state_value_static(const lq_ssd_problem* p, lq_stream stream);
  * Replaces _chunk_state_keyside_fwd (mamba2/chunk_state_keyside.py:17-424). */
 int lq_ssd_chunk_state_key(const lq_ssd_problem* p, lq_stream stream);
 /* INT32 fixed-point inter-chunk recurrence with a Q0.7 gate.
- * Replaces _fixedpoint_state_passing_fwd (mamba2/state_passing.py:14-121). */
+ * Replaces _fixedpoint_state_passing_fwd (mamba2/state_passing.py:14-121). With carry_in / carry_out / the flag
+ * fields it is also the hand-off step of the sequence-parallel mode: the producer GPU's kernel stores its final carry
+ * and a flag into the consumer GPU's memory, the consumer's kernel waits (bounded) on its local flag. */
 int lq_ssd_state_passing(const lq_ssd_problem* p, lq_stream stream);
+/* Receive buffers of the sequence-parallel hand-off (set-up calls; the only entries of this library that allocate).
+ * create: cudaMalloc + zero-fill on the current device and the 64-byte CUDA IPC handle of the allocation. open: maps
+ * another process's buffer (owner_device = the CUDA ordinal it lives on) into this process, with peer access enabled
+ * from the current device; the mapping is only ever written with plain stores by lq_ssd_state_passing
+ * (carry_out / post_flags). close / destroy undo open / create. No counterpart in the reference (single GPU). */
+int lq_peer_buffer_create(size_t bytes, void** dev_ptr, unsigned char* handle64);
+int lq_peer_buffer_open(const unsigned char* handle64, int owner_device, void** dev_ptr);
+int lq_peer_buffer_close(void* dev_ptr);
+int lq_peer_buffer_destroy(void* dev_ptr);
+
 /* Per-chunk INT8 C.B^T requantised to INT8 (b_is_fp: B quantised in-kernel from b_fp).
  * Replaces _quant_bmm_chunk_fwd (mamba2/bmm_chunk.py:11-217). */
 int lq_ssd_bmm_chunk(const lq_ssd_problem* p, int b_is_fp, lq_stream stream);

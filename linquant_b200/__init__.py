@@ -4,3 +4,12 @@
 code lives in ``csrc/`` behind the C ABI of ``include/linquant_b200.h``."""
 
 __version__ = "0.1.0"
+
+
+def check_status(device=None):
+    """Raises if a kernel of this package gave up on a bounded device-side wait on ``device`` (default: the current
+    CUDA device) since the last check; see ``linquant_b200._cabi.check_status``. The ops return without synchronising
+    and never read the word themselves, so a caller that wants the guarantee calls this after its forward pass."""
+    from . import _cabi
+
+    _cabi.check_status(device)

@@ -29,7 +29,8 @@ class ZooProblem(C.Structure):
                 ("rot_signs", C.c_void_p), ("dqk", C.c_void_p),
                 ("sq", C.c_void_p), ("sk", C.c_void_p), ("skw", C.c_void_p), ("svl", C.c_void_p), ("svw", C.c_void_p),
                 ("sstate", C.c_void_p), ("sw", C.c_void_p), ("sel", C.c_void_p), ("sew", C.c_void_p),
-                ("o", C.c_void_p), ("final_state", C.c_void_p), ("initial_state", C.c_void_p), ("unrot_t", C.c_void_p)]
+                ("o", C.c_void_p), ("final_state", C.c_void_p), ("initial_state", C.c_void_p), ("unrot_t", C.c_void_p),
+                ("status", C.c_void_p)]
 
 
 class ZooWorkspace(C.Structure):
@@ -58,6 +59,33 @@ def lib():
         L.lq_zoo_carve_workspace.argtypes = [C.POINTER(ZooProblem), C.c_int, C.c_void_p, C.c_size_t, C.POINTER(ZooWorkspace)]
         _lib = L
     return _lib
+
+
+_STATUS_WORDS = {}
+
+
+def status_word(device):
+    """The per-device int32 that every kernel with a bounded device-side wait (TMA / MMA barriers of the tcgen05
+    kernels, the hand-off flag of the sequence-parallel state passing) raises when its wait runs out. It lives as long
+    as the process, so it can be read long after the call that might have raised it."""
+    dev = torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _STATUS_WORDS:
+        _STATUS_WORDS[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+    return _STATUS_WORDS[key]
+
+
+def check_status(device=None):
+    """Deferred error check: drains the current stream of ``device``, and raises ``LinQuantError`` if any kernel
+    launched through this package on that device gave up on a bounded wait since the previous check (its outputs, and
+    those of the calls after it, are then not valid). The ops themselves return without synchronising, so call this
+    where a synchronisation is acceptable -- once per forward pass, or before results leave the GPU."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    w = status_word(dev)
+    fn = lib().lq_status_poll
+    fn.argtypes = [C.c_void_p, C.c_void_p]
+    with torch.cuda.device(dev):
+        check(fn(C.c_void_p(w.data_ptr()), C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)), "check_status")
 
 
 def check(status, what=""):
@@ -129,6 +157,8 @@ class Workspace:
         """After the stream has drained: raises if a kernel's bounded device-side wait expired."""
         if int(self.view("status").item()) != 0:
             raise LinQuantError("a device-side wait timed out (status word set by the kernel)")
+        if self.prob.status:  # the descriptor redirected the kernels to the per-device word
+            check_status(self.buf.device)
 
     def view(self, name):
         p = getattr(self.desc, name)

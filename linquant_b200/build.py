@@ -14,9 +14,8 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "csrc", "build")
 LIB = os.path.join(HERE, "liblinquant_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math=false",
-         "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
-FLAGS.remove("--use_fast_math=false")  # precise division / sqrt / expf are required by the code rule
+# no fast-math: precise division / sqrt / expf are required by the code rule
+FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 
 
 def sources():

@@ -96,6 +96,18 @@ extern "C" unsigned long long lq_struct_bytes(int which) {
 }
 extern "C" const char* lq_last_error_string(void) { return lq::g_err; }
 
+extern "C" int lq_status_poll(int* status, lq_stream stream) {
+  if (!status) return lq::fail(LQ_ERR_NULL, "status_poll: status word is null");
+  cudaStream_t st = (cudaStream_t)stream;
+  int host = 0;
+  cudaError_t e = cudaMemcpyAsync(&host, status, sizeof(int), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return lq::fail(LQ_ERR_LAUNCH, "status_poll: %s", cudaGetErrorString(e));
+  if (host == 0) return LQ_OK;
+  cudaMemsetAsync(status, 0, sizeof(int), st);
+  return lq::fail(LQ_ERR_TIMEOUT, "a bounded device-side wait ran out (status word %d): the outputs written since the last poll are not valid", host);
+}
+
 extern "C" size_t lq_zoo_workspace_bytes(const lq_zoo_problem* p, int delta_family) {
   if (!p || p->chunk <= 0) return 0;
   return lq::carve(p, delta_family, nullptr, nullptr);
@@ -116,7 +128,7 @@ extern "C" int lq_simple_gla_fwd(const lq_zoo_problem* p, void* workspace, size_
   lq_zoo_workspace ws;
   if (int e = lq_zoo_carve_workspace(p, 0, workspace, workspace_bytes, &ws)) return e;
   cudaStream_t st = (cudaStream_t)stream;
-  cudaMemsetAsync(ws.status, 0, sizeof(int), st);
+  if (p->status == nullptr) cudaMemsetAsync(ws.status, 0, sizeof(int), st);
   if (int e = lq::run_prologue_linear(p, &ws, 0, st)) return e;
   if (int e = lq::run_state_linear(p, &ws, st)) return e;
   return lq::run_output_scalar(p, &ws, p->svl, st);
@@ -127,7 +139,7 @@ extern "C" int lq_delta_fwd(const lq_zoo_problem* p, void* workspace, size_t wor
   lq_zoo_workspace ws;
   if (int e = lq_zoo_carve_workspace(p, 1, workspace, workspace_bytes, &ws)) return e;
   cudaStream_t st = (cudaStream_t)stream;
-  cudaMemsetAsync(ws.status, 0, sizeof(int), st);
+  if (p->status == nullptr) cudaMemsetAsync(ws.status, 0, sizeof(int), st);
   if (int e = lq::run_prologue_delta(p, &ws, st)) return e;
   if (int e = lq::run_state_delta(p, &ws, st)) return e;
   return lq::run_output_scalar(p, &ws, p->sel, st);
@@ -138,6 +150,7 @@ extern "C" int lq_gla_fwd(const lq_zoo_problem* p, void* workspace, size_t works
   lq_zoo_workspace ws;
   if (int e = lq_zoo_carve_workspace(p, 0, workspace, workspace_bytes, &ws)) return e;
   cudaStream_t st = (cudaStream_t)stream;
+  if (p->status == nullptr) cudaMemsetAsync(ws.status, 0, sizeof(int), st);
   if (int e = lq::run_diag_stage(p, &ws, false, 0, st)) return e;
   if (int e = lq::run_diag_stage(p, &ws, false, 1, st)) return e;
   if (int e = lq::run_state_linear(p, &ws, st)) return e;
@@ -149,6 +162,7 @@ extern "C" int lq_kda_fwd(const lq_zoo_problem* p, void* workspace, size_t works
   lq_zoo_workspace ws;
   if (int e = lq_zoo_carve_workspace(p, 1, workspace, workspace_bytes, &ws)) return e;
   cudaStream_t st = (cudaStream_t)stream;
+  if (p->status == nullptr) cudaMemsetAsync(ws.status, 0, sizeof(int), st);
   if (int e = lq::run_diag_stage(p, &ws, true, 0, st)) return e;
   if (int e = lq::run_diag_stage(p, &ws, true, 1, st)) return e;
   if (int e = lq::run_diag_stage(p, &ws, true, 2, st)) return e;

@@ -22,7 +22,7 @@ __device__ __forceinline__ int round_rint(float y, float lo, float hi) {
 // mamba2/chunk_cumsum.py:52-74. One CTA per (chunk, batch, block of 32 heads). The dt tile is read with the head
 // index contiguous (as it lies in memory), transformed and parked in shared memory; each warp then scans four heads
 // with the token index across its lanes, so both outputs are written with the token index contiguous. The running sum
-// is kept in double (the CPU oracle's float cumsum accumulates in double): a warp scan per 32 tokens plus a carry.
+// is kept in double: a warp scan per 32 tokens plus a carry.
 __global__ void __launch_bounds__(256) ssd_cumsum_kernel(lq_ssd_problem p) {
   extern __shared__ float s_dtv[];  // [C][33]
   const int c = blockIdx.x, b = blockIdx.y, h0 = blockIdx.z * 32;
@@ -100,55 +100,120 @@ __global__ void __launch_bounds__(256) ssd_transpose_b_kernel(const int8_t* qB, 
 
 // ------------------------------------------------------------------------------------------------ state passing
 // mamba2/state_passing.py:55-93: s32 <- ((s32 * gate_q + 64) >> 7) + new, gate_q = clamp(half_away(exp(dA_last)*128)),
-// out[:, c] = clamp(s32 entering chunk c), final = clamp(s32 after the last chunk). 16 state bytes per thread.
+// out[:, c] = clamp(s32 entering chunk c), final = clamp(s32 after the last chunk). Eight state bytes per thread.
+//
+// The unclamped INT32 carry can enter and leave the call (carry_in / carry_out), which is what makes a sequence cut
+// into segments -- several calls, or one segment per GPU -- reproduce the one-shot result bit for bit. In the
+// sequence-parallel mode carry_out and post_flags point into the NEXT GPU's memory: each CTA stores its slice of the
+// carry with plain stores, makes them visible system-wide and then posts its own flag; the next GPU's CTA of the same
+// index polls its local flag for a bounded time before it reads carry_in.
+struct PassingLink {
+  const int* carry_in;
+  int* carry_out;
+  const unsigned* wait_flags;
+  unsigned* post_flags;
+  unsigned epoch;
+  unsigned long long wait_ns;
+  int* status;
+};
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+
 __global__ void __launch_bounds__(256) ssd_state_passing_kernel(const int8_t* states, const float* dA, int8_t* out,
-                                                                int8_t* final_state, int H, int NC, int C, int D) {
+                                                                int8_t* final_state, int H, int NC, int C, int D,
+                                                                PassingLink link) {
   extern __shared__ int s_gq[];  // [NC] Q0.7 gate of every chunk: the serial loop must not wait on its loads
+  __shared__ int s_ok;
   const int h = blockIdx.y, b = blockIdx.z;
+  const size_t cta = ((size_t)b * H + h) * gridDim.x + blockIdx.x;
   {
     const float* dAl = dA + (((size_t)b * H + h) * NC) * C + (C - 1);
     for (int c = threadIdx.x; c < NC; c += 256) s_gq[c] = round_half_away(__fmul_rn(expf(dAl[(size_t)c * C]), 128.f), 127.f);
   }
+  if (link.wait_flags != nullptr && threadIdx.x == 0) {
+    // bounded poll of this CTA's flag: a time limit on the global timer, and an iteration limit as a second guard
+    const unsigned long long limit = link.wait_ns ? link.wait_ns : 2000000000ull;
+    const unsigned long long t0 = globaltimer_ns();
+    int ok = 0;
+    const long long max_it = (long long)(limit >> 6) + 1024;  // each round costs at least the 200 ns sleep
+    for (long long it = 0; it < max_it; ++it) {
+      if (ld_acquire_sys(link.wait_flags + cta) >= link.epoch) { ok = 1; break; }
+      if (globaltimer_ns() - t0 > limit) break;
+      __nanosleep(200);
+    }
+    s_ok = ok;
+    if (!ok && link.status != nullptr) atomicExch(link.status, 2);
+  }
   __syncthreads();
+  if (link.wait_flags != nullptr && !s_ok) return;  // nothing stored, nothing posted: the host reads the status word
   // eight state bytes per thread: the walk over the chunks is serial, so the threads have to be many
   const int d0 = (blockIdx.x * 256 + threadIdx.x) * 8;
-  if (d0 >= D) return;
+  const bool live = d0 < D;
   int s32[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) s32[i] = 0;
-  // stored copy: clamp to +-127 (the lower bound by hand, the saturating pack gives the upper one)
-  auto codes = [&]() {
-    int m[8];
+  if (live && link.carry_in != nullptr) {
+    const int4* ci = reinterpret_cast<const int4*>(link.carry_in + ((size_t)b * H + h) * D + d0);
+    const int4 lo = ci[0], hi = ci[1];
+    s32[0] = lo.x; s32[1] = lo.y; s32[2] = lo.z; s32[3] = lo.w;
+    s32[4] = hi.x; s32[5] = hi.y; s32[6] = hi.z; s32[7] = hi.w;
+  }
+  if (live) {
+    // stored copy: clamp to +-127 (the lower bound by hand, the saturating pack gives the upper one)
+    auto codes = [&]() {
+      int m[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) m[i] = max(s32[i], -127);
-    return make_uint2(pack_sat_s8x2(m[1], m[0], pack_sat_s8x2(m[3], m[2], 0u)), pack_sat_s8x2(m[5], m[4], pack_sat_s8x2(m[7], m[6], 0u)));
-  };
-  const size_t cstride = (size_t)H * D;
-  const int8_t* src = states + ((size_t)b * NC * H + h) * D + d0;
-  int8_t* dst = out + ((size_t)b * NC * H + h) * D + d0;
-  constexpr int DEPTH = 4;  // chunk tiles in flight per thread
-  uint2 ring[DEPTH];
+      for (int i = 0; i < 8; ++i) m[i] = max(s32[i], -127);
+      return make_uint2(pack_sat_s8x2(m[1], m[0], pack_sat_s8x2(m[3], m[2], 0u)), pack_sat_s8x2(m[5], m[4], pack_sat_s8x2(m[7], m[6], 0u)));
+    };
+    const size_t cstride = (size_t)H * D;
+    const int8_t* src = states + ((size_t)b * NC * H + h) * D + d0;
+    int8_t* dst = out + ((size_t)b * NC * H + h) * D + d0;
+    constexpr int DEPTH = 4;  // chunk tiles in flight per thread
+    uint2 ring[DEPTH];
 #pragma unroll
-  for (int u = 0; u < DEPTH; ++u)
-    if (u < NC) ring[u] = __ldg(reinterpret_cast<const uint2*>(src + (size_t)u * cstride));
-  for (int c0 = 0; c0 < NC; c0 += DEPTH) {
+    for (int u = 0; u < DEPTH; ++u)
+      if (u < NC) ring[u] = __ldg(reinterpret_cast<const uint2*>(src + (size_t)u * cstride));
+    for (int c0 = 0; c0 < NC; c0 += DEPTH) {
 #pragma unroll
-    for (int u = 0; u < DEPTH; ++u) {
-      const int c = c0 + u;
-      if (c >= NC) break;
-      const uint2 cur = ring[u];
-      if (c + DEPTH < NC) ring[u] = __ldg(reinterpret_cast<const uint2*>(src + (size_t)(c + DEPTH) * cstride));
-      *reinterpret_cast<uint2*>(dst + (size_t)c * cstride) = codes();
-      const int gq = s_gq[c];
-      const uint32_t cw[2] = {cur.x, cur.y};
+      for (int u = 0; u < DEPTH; ++u) {
+        const int c = c0 + u;
+        if (c >= NC) break;
+        const uint2 cur = ring[u];
+        if (c + DEPTH < NC) ring[u] = __ldg(reinterpret_cast<const uint2*>(src + (size_t)(c + DEPTH) * cstride));
+        *reinterpret_cast<uint2*>(dst + (size_t)c * cstride) = codes();
+        const int gq = s_gq[c];
+        const uint32_t cw[2] = {cur.x, cur.y};
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int nw = (int)(int8_t)((cw[i >> 2] >> (8 * (i & 3))) & 0xff);
-        s32[i] = ((s32[i] * gq + 64) >> 7) + nw;
+        for (int i = 0; i < 8; ++i) {
+          const int nw = (int)(int8_t)((cw[i >> 2] >> (8 * (i & 3))) & 0xff);
+          s32[i] = ((s32[i] * gq + 64) >> 7) + nw;
+        }
       }
     }
+    *reinterpret_cast<uint2*>(final_state + ((size_t)b * H + h) * D + d0) = codes();
+    if (link.carry_out != nullptr) {
+      int4* co = reinterpret_cast<int4*>(link.carry_out + ((size_t)b * H + h) * D + d0);
+      co[0] = make_int4(s32[0], s32[1], s32[2], s32[3]);
+      co[1] = make_int4(s32[4], s32[5], s32[6], s32[7]);
+    }
   }
-  *reinterpret_cast<uint2*>(final_state + ((size_t)b * H + h) * D + d0) = codes();
+  if (link.post_flags != nullptr) {
+    __threadfence_system();  // every thread's carry stores before the flag
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_sys(link.post_flags + cta, link.epoch);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------ chunk state
@@ -784,10 +849,15 @@ extern "C" int lq_ssd_state_passing(const lq_ssd_problem* p, lq_stream stream) {
   if (!p->states || !p->passed || !p->final_state || !p->dA) return fail(LQ_ERR_NULL, "state_passing: states, passed, final_state, dA required");
   const int D = p->P * p->N;
   if (D % 8 != 0) return fail(LQ_ERR_SHAPE, "state_passing: P*N must be a multiple of 8");
+  if ((p->carry_in && (reinterpret_cast<uintptr_t>(p->carry_in) & 15u)) || (p->carry_out && (reinterpret_cast<uintptr_t>(p->carry_out) & 15u)))
+    return fail(LQ_ERR_ALIGN, "state_passing: carry_in / carry_out must be 16-byte aligned");
+  if ((p->wait_flags || p->post_flags) && p->epoch == 0) return fail(LQ_ERR_SHAPE, "state_passing: the flag hand-off needs epoch >= 1");
+  if (p->wait_flags && !p->carry_in) return fail(LQ_ERR_NULL, "state_passing: wait_flags without carry_in");
   dim3 grid((D / 8 + 255) / 256, p->H, p->B);
   if ((size_t)(p->L / p->chunk) * sizeof(int) > 48 * 1024) return fail(LQ_ERR_UNSUPPORTED, "state_passing: more than 12288 chunks");
+  PassingLink link{p->carry_in, p->carry_out, p->wait_flags, p->post_flags, p->epoch, p->wait_ns, p->status};
   ssd_state_passing_kernel<<<grid, 256, (size_t)(p->L / p->chunk) * sizeof(int), (cudaStream_t)stream>>>(p->states, p->dA, p->passed, p->final_state, p->H,
-                                                                    p->L / p->chunk, p->chunk, D);
+                                                                    p->L / p->chunk, p->chunk, D, link);
   return check_launch("ssd_state_passing_kernel");
 }
 
@@ -849,10 +919,13 @@ static int static_scratch(int8_t** out) {
 extern "C" size_t lq_ssd_static_scratch_bytes(void) { return lq::kStaticScratchBytes; }
 
 extern "C" int lq_ssd_chunk_state_value_static(const lq_ssd_problem* p, lq_stream stream) {
-  if (!p) return fail(LQ_ERR_NULL, "chunk_state_value_static: problem descriptor is null");
-  const size_t need = (size_t)p->B * (size_t)p->L * (size_t)p->G * (size_t)p->N;
-  if (p->B <= 0 || p->L <= 0 || p->G <= 0 || p->N <= 0 || need > lq::kStaticScratchBytes)
-    return fail(LQ_ERR_WORKSPACE, "chunk_state_value_static: B*L*G*N = %zu bytes of scratch needed, the built-in array holds %zu; "
+  // the ordinary shape checks first (non-positive or unsupported extents are shape errors, not capacity errors)
+  if (int e = ssd_check(p, "chunk_state_value_static")) return e;
+  if (int e = ssd_check_pn(p, "chunk_state_value_static")) return e;
+  // B, L, G are positive ints and N is 64 or 128 here, so the 64-bit product cannot wrap
+  const unsigned long long need = (unsigned long long)p->B * (unsigned long long)p->L * (unsigned long long)p->G * (unsigned long long)p->N;
+  if (need > lq::kStaticScratchBytes)
+    return fail(LQ_ERR_WORKSPACE, "chunk_state_value_static: B*L*G*N = %llu bytes of scratch needed, the built-in array holds %zu; "
                 "use lq_ssd_chunk_state_value with a caller-owned q_BT for larger problems", need, lq::kStaticScratchBytes);
   lq_ssd_problem q = *p;
   if (int e = lq::static_scratch(&q.q_BT)) return e;

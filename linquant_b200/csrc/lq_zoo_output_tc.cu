@@ -277,7 +277,7 @@ static int launch_output_tc(const lq_zoo_problem* p, const lq_zoo_workspace* ws,
 int run_output_tc(const lq_zoo_problem* p, const lq_zoo_workspace* ws, const float* s_local_value, cudaStream_t st) {
   OutputTcArgs a;
   a.vlT = ws->vlT; a.gc = ws->gc; a.sq = p->sq; a.sk = p->sk; a.svl = s_local_value; a.ss = p->sstate; a.o = p->o;
-  a.status = ws->status; a.T = p->T; a.H = p->H; a.NT = p->T / p->chunk;
+  a.status = p->status != nullptr ? p->status : ws->status; a.T = p->T; a.H = p->H; a.NT = p->T / p->chunk;
   if (p->V == 128) return launch_output_tc<128>(p, ws, a, st);
   if (p->V == 64) return launch_output_tc<64>(p, ws, a, st);
   return fail(LQ_ERR_UNSUPPORTED, "output: V must be 64 or 128");

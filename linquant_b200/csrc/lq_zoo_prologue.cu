@@ -10,8 +10,8 @@
 // state pass and the B operand of the A.v product want.
 //
 // Reference arithmetic: zoo/simple_gla.py:16-20 (_q8), :57-67 (write gating and codes), :129-130,:149 (read /
-// local codes), :191 (chunk-local cumsum; torch accumulates a float cumsum in double on the CPU oracle, so the
-// scan here runs in double too), reference.py:41-47 (rotate -> round to activation dtype -> scale).
+// local codes), :191 (chunk-local cumsum of the fp32 log-decay; the scan here accumulates in double and rounds each
+// prefix to fp32), reference.py:41-47 (rotate -> round to activation dtype -> scale).
 #include "lq_zoo_rows.cuh"
 
 namespace lq {

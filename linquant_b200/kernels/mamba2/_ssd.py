@@ -22,36 +22,32 @@ class SsdProblem(C.Structure):
                 ("cb_scale", C.c_void_p), ("alpha_hp", C.c_void_p), ("x_scale_hp", C.c_void_p), ("state_scale", C.c_void_p),
                 ("b_gate_scale", C.c_void_p), ("bgs_stride", C.c_longlong * 4),
                 ("states", C.c_void_p), ("passed", C.c_void_p), ("final_state", C.c_void_p), ("cb", C.c_void_p),
-                ("D", C.c_void_p), ("D_has_hdim", C.c_int), ("out", C.c_void_p), ("scan_kernel", C.c_int), ("status", C.c_void_p)]
-
-
-_STATUS = {}
+                ("D", C.c_void_p), ("D_has_hdim", C.c_int), ("out", C.c_void_p), ("scan_kernel", C.c_int), ("status", C.c_void_p),
+                ("carry_in", C.c_void_p), ("carry_out", C.c_void_p), ("wait_flags", C.c_void_p), ("post_flags", C.c_void_p),
+                ("epoch", C.c_uint), ("wait_ns", C.c_ulonglong)]
 
 
 def status_word(device):
-    """One int32 per device that the tcgen05 kernels raise when a bounded barrier wait runs out."""
-    key = torch.device(device).index
-    if key not in _STATUS:
-        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _STATUS[key]
+    """The per-device status word (shared with the zoo ops) that a kernel raises when a bounded wait runs out."""
+    return _cabi.status_word(device)
 
 
 def check_status(device):
-    """Synchronises and raises if any SSD kernel on ``device`` reported an expired wait since the last check."""
-    w = status_word(device)
-    if int(w.item()) != 0:
-        w.zero_()
-        raise _cabi.LinQuantError("an SSD kernel gave up waiting on a TMA / MMA barrier; its output is not valid")
+    """Synchronises and raises if any kernel on ``device`` reported an expired wait since the last check."""
+    _cabi.check_status(device)
 
 
 class Call:
     """Collects tensors into an ``SsdProblem`` (keeping them alive) and launches one entry of the C ABI."""
 
-    def __init__(self, device):
+    def __init__(self, device, status=True):
         self.p = SsdProblem()
         self.keep = []
         self.device = device
-        self.p.status = status_word(device).data_ptr()
+        # status=None / False: no word (the kernels then skip the report); True: the per-device word, created on first use
+        if status is True:
+            status = status_word(device)
+        self.p.status = status.data_ptr() if torch.is_tensor(status) else None
 
     def dims(self, **kw):
         for k, v in kw.items():
@@ -63,8 +59,9 @@ class Call:
         setattr(self.p, name, None if t is None else t.data_ptr())
         return t
 
-    def x(self, x):
+    def x(self, x, copy_ok=True):
         if x.stride(-1) != 1:
+            assert copy_ok, "x must have a unit stride along headdim (this entry copies nothing)"
             x = x.contiguous()
         self.keep.append(x)
         self.p.x = x.data_ptr()

@@ -5,9 +5,17 @@ import torch
 from . import _ssd
 
 
-def _fixedpoint_state_passing_fwd(states_i8, dA_chunk_cumsum, gate_shift=7):
+def _fixedpoint_state_passing_fwd(states_i8, dA_chunk_cumsum, gate_shift=7, initial_carry=None, return_carry=False,
+                                  link=None):
     """states_i8 (B, nchunks, H, dim) int8, dA_chunk_cumsum (B, H, nchunks) -> (out_i8, final_states_i8);
-    out_i8[:, c] is the state entering chunk c."""
+    out_i8[:, c] is the state entering chunk c.
+
+    Extensions over the reference signature (which always starts from a zero state, state_passing.py:54-60):
+    ``initial_carry`` (B, H, dim) int32 is the unclamped carry entering the first chunk; ``return_carry=True`` appends
+    the unclamped int32 carry after the last chunk to the result. Feeding one call's carry to the next reproduces the
+    single call over the concatenated chunks bit for bit (cached prefill, sequence split over GPUs). ``link`` is the
+    sequence-parallel hand-off (``linquant_b200.seqpar.SsdLink``): where the carry comes from and goes to, and the
+    flags that order the two GPUs' kernels."""
     _ssd.require_cuda(states_i8, "_fixedpoint_state_passing_fwd")
     if gate_shift != 7:
         raise NotImplementedError("the fixed-point gate is Q0.7 (gate_shift=7)")
@@ -31,5 +39,13 @@ def _fixedpoint_state_passing_fwd(states_i8, dA_chunk_cumsum, gate_shift=7):
     call.put("states", states_i8)
     out = call.put("passed", torch.empty_like(states_i8, memory_format=torch.contiguous_format))
     final = call.put("final_state", torch.empty(B, H, dim, device=dev, dtype=torch.int8))
+    carry = None
+    if initial_carry is not None:
+        assert initial_carry.shape == (B, H, dim) and initial_carry.dtype == torch.int32
+        call.put("carry_in", initial_carry.contiguous())
+    if return_carry:
+        carry = call.put("carry_out", torch.empty(B, H, dim, device=dev, dtype=torch.int32))
+    if link is not None:
+        link.apply(call, B, H, dim)
     call.launch("lq_ssd_state_passing")
-    return out, final
+    return (out, final, carry) if return_carry else (out, final)

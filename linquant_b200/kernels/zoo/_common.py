@@ -65,6 +65,7 @@ def make_problem(q, k, v, g, beta, scales, *, decay, eta, sigma, tau, scale, chu
         assert tuple(unrot.shape) == (V, V), f"unrot must be ({V},{V})"
         unrot = unrot.to(device=dev, dtype=torch.float16).t().contiguous()
     put("unrot_t", unrot)
+    P.status = _cabi.status_word(dev).data_ptr()  # sticky per-device word: read by linquant_b200.check_status()
     return P
 
 

@@ -101,3 +101,143 @@ def segmented_on_one_device(q, k, v, g, scales, nseg, *, eta=1.0, scale=None, ch
     firsts = [s.pass1() for s in segs]
     s_in = incoming_carries(torch.stack([f[0] for f in firsts]), torch.stack([f[1] for f in firsts]))
     return torch.cat([s.pass2(s_in[i] if i > 0 else None) for i, s in enumerate(segs)], dim=1)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# Mamba-2 SSD (SSDi8 lineage): the carry of the inter-chunk recurrence is an unclamped INT32 tensor, so handing THAT
+# from the GPU that holds segment r to the GPU that holds segment r+1 reproduces the one-GPU result bit for bit.
+# Every rank runs cumsum / chunk state / C.B^T of its own segment at once; the fixed-point state passing then forms a
+# chain: rank r's kernel waits (bounded) for its local flags, runs its chunks, and stores its final carry and the
+# flags straight into rank r+1's receive buffer over NVLink (plain stores into a CUDA-IPC mapping of memory that
+# lives on the consumer GPU); the chunk scans run at once again.
+import ctypes as _C
+
+
+def _flag_count(B, H, D):
+    return B * H * ((D // 8 + 255) // 256)
+
+
+class _DevArray:
+    """A raw device allocation seen as a tensor (``torch.as_tensor`` reads ``__cuda_array_interface__``)."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+class SsdLink:
+    """One rank's end of the hand-off chain for a fixed (B, H, P*N): a receive buffer in this GPU's memory (int32 carry
+    followed by one flag per state-passing CTA) and, unless this is the last rank, the mapping of the next rank's
+    buffer. Construction is collective over ``group`` (the IPC handles travel by ``all_gather_object``); ``local=True``
+    builds the chain inside one process on one GPU instead (every segment's buffer is a local tensor), which is how a
+    single device runs all segments one after the other."""
+
+    def __init__(self, B, H, D, device, group=None, wait_ns=0, _local_next=None, _local_first=False, local=False):
+        import torch.distributed as dist
+
+        self.B, self.H, self.D = B, H, D
+        self.device = torch.device(device)
+        self.wait_ns = int(wait_ns)
+        self.epoch = 0
+        self.carry_bytes = B * H * D * 4
+        self.nbytes = self.carry_bytes + _flag_count(B, H, D) * 4
+        self._own_ptr = self._next_ptr = None
+        self._lib = _cabi.lib()
+        if local:
+            self.rank, self.world = (0 if _local_first else 1), 2
+            self.buf = torch.zeros(self.nbytes, dtype=torch.uint8, device=self.device)
+            self.recv_ptr = self.buf.data_ptr()
+            self.next_ptr = None if _local_next is None else _local_next.recv_ptr
+            self.is_first, self.is_last = _local_first, _local_next is None
+            return
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.is_first, self.is_last = self.rank == 0, self.rank == self.world - 1
+        handle = (_C.c_ubyte * 64)()
+        ptr = _C.c_void_p()
+        fn = self._lib.lq_peer_buffer_create
+        fn.argtypes = [_C.c_size_t, _C.POINTER(_C.c_void_p), _C.POINTER(_C.c_ubyte)]
+        with torch.cuda.device(self.device):
+            _cabi.check(fn(self.nbytes, _C.byref(ptr), handle), "lq_peer_buffer_create")
+        self._own_ptr = self.recv_ptr = ptr.value
+        self.buf = torch.as_tensor(_DevArray(self.recv_ptr, self.nbytes), device=self.device)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, (bytes(handle), self.device.index), group=group)
+        self.next_ptr = None
+        if not self.is_last:
+            h, owner = handles[self.rank + 1]
+            nxt = _C.c_void_p()
+            op = self._lib.lq_peer_buffer_open
+            op.argtypes = [_C.POINTER(_C.c_ubyte), _C.c_int, _C.POINTER(_C.c_void_p)]
+            with torch.cuda.device(self.device):
+                _cabi.check(op((_C.c_ubyte * 64).from_buffer_copy(h), owner, _C.byref(nxt)), "lq_peer_buffer_open")
+            self._next_ptr = self.next_ptr = nxt.value
+        dist.barrier(group)
+
+    def next_call(self):
+        """A new forward pass: the flags of the previous one stay where they are and simply become stale."""
+        self.epoch += 1
+
+    def apply(self, call, B, H, dim):
+        assert (B, H, dim) == (self.B, self.H, self.D), "the link was built for another problem shape"
+        assert self.epoch >= 1, "call next_call() once per forward pass before the state passing"
+        p = call.p
+        call.keep.append(self.buf)
+        if not self.is_first:
+            p.carry_in = self.recv_ptr
+            p.wait_flags = self.recv_ptr + self.carry_bytes
+        if self.next_ptr is not None:
+            p.carry_out = self.next_ptr
+            p.post_flags = self.next_ptr + self.carry_bytes
+        p.epoch = self.epoch
+        p.wait_ns = self.wait_ns
+
+    def close(self):
+        if self._next_ptr:
+            fn = self._lib.lq_peer_buffer_close
+            fn.argtypes = [_C.c_void_p]
+            fn(self._next_ptr)
+            self._next_ptr = None
+        if self._own_ptr:
+            torch.cuda.synchronize(self.device)
+            self.buf = None
+            fn = self._lib.lq_peer_buffer_destroy
+            fn.argtypes = [_C.c_void_p]
+            fn(self._own_ptr)
+            self._own_ptr = None
+
+
+def ssd_combined_seqpar(link, x_fp, q_dt, dt_scale, q_A_log, A_log_scale, q_B, B_scale, q_C, C_scale, chunk_size, q_D, D_scale,
+                        **kw):
+    """``_quant_mamba_chunk_scan_combined_fwd`` on this rank's segment of the sequence (tokens
+    [rank*L/W, (rank+1)*L/W) of every tensor with a token axis; L/W a multiple of the chunk size). The only exchange is
+    the INT32 carry of the state passing, written by the previous rank's kernel into this rank's receive buffer. Returns
+    (out segment, None); equal, bit for bit, to the same rows of the single-GPU result."""
+    from .kernels.mamba2 import ssd_combined as sc
+
+    link.next_call()
+    return sc._quant_mamba_chunk_scan_combined_fwd(x_fp, q_dt, dt_scale, q_A_log, A_log_scale, q_B, B_scale, q_C, C_scale,
+                                                   chunk_size, q_D, D_scale, _link=link, **kw)
+
+
+def ssd_segmented_on_one_device(nseg, x_fp, q_dt, dt_scale, q_A_log, A_log_scale, q_B, B_scale, q_C, C_scale, chunk_size, q_D,
+                                D_scale, **kw):
+    """All ``nseg`` segments on one GPU, one after the other on the current stream: the same kernels and the same
+    carry / flag traffic as ``nseg`` ranks, with local buffers in place of the peer mappings."""
+    B, L, H, P = x_fp.shape
+    N = q_B.shape[-1]
+    assert L % (nseg * chunk_size) == 0
+    S = L // nseg
+    links, nxt = [], None
+    for i in reversed(range(nseg)):
+        nxt = SsdLink(B, H, P * N, x_fp.device, local=True, _local_next=nxt, _local_first=(i == 0))
+        links.append(nxt)
+    links.reverse()
+    cut = lambda t, i: t[:, i * S:(i + 1) * S]  # noqa: E731
+    outs = []
+    for i, link in enumerate(links):
+        kws = dict(kw)
+        if kws.get("b_fp") is not None:
+            kws["b_fp"] = cut(kws["b_fp"], i)
+        o, _ = ssd_combined_seqpar(link, cut(x_fp, i), cut(q_dt, i), dt_scale, q_A_log, A_log_scale, cut(q_B, i), B_scale,
+                                   cut(q_C, i), C_scale, chunk_size, q_D, D_scale, **kws)
+        outs.append(o)
+    return torch.cat(outs, dim=1)

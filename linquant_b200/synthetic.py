@@ -48,11 +48,14 @@ def make_inputs(cfg, seed=0, B=None, T=None):
     k = torch.randn(B, T, H, K, generator=g)
     if c["op"] == "delta":
         q = F.normalize(q, dim=-1)
-    k = F.normalize(k, dim=-1)
     if c.get("outliers"):
+        # heavy key channels: scaled in the raw draw, so that k keeps unit norm after the normalisation below. A delta
+        # rule needs beta * |k|^2 < 2 to stay bounded; scaling after the normalisation (|k|^2 about 4) makes the
+        # recurrence grow without bound over a long sequence, which no model activation does.
         nout = max(1, int(round(c["outliers"] * K)))
         idx = torch.randperm(K, generator=g)[:nout]
         k[..., idx] *= 20.0
+    k = F.normalize(k, dim=-1)
     v = torch.randn(B, T, H, V, generator=g)
     gshape = (B, T, H, K) if c["op"] in ("kda", "gla") else (B, T, H)
     gd = F.logsigmoid(torch.randn(*gshape, generator=g) + c["gmean"]).float()

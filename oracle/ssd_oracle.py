@@ -102,11 +102,13 @@ def chunk_state_key(x, x_scale_hp, b_fp, dt, dA, out_qscale, b_gate_scale):
     return _rint(accf).clamp(-127, 127).to(torch.int8).permute(0, 2, 1, 3, 4).contiguous()
 
 
-def state_passing(states_i8, dA_last, gate_shift=7):
-    """states [B,NC,H,D] int8, dA_last [B,H,NC] -> (out [B,NC,H,D] int8 entering states, final [B,H,D])."""
+def state_passing(states_i8, dA_last, gate_shift=7, initial_carry=None, return_carry=False):
+    """states [B,NC,H,D] int8, dA_last [B,H,NC] -> (out [B,NC,H,D] int8 entering states, final [B,H,D]).
+    ``initial_carry`` [B,H,D] is the unclamped int32 carry entering the first chunk (the reference starts from zero,
+    state_passing.py:54-60); ``return_carry`` appends the carry after the last chunk."""
     B, nc, H, D = states_i8.shape
     S = 1 << gate_shift
-    s32 = torch.zeros(B, H, D, dtype=torch.int64)
+    s32 = torch.zeros(B, H, D, dtype=torch.int64) if initial_carry is None else initial_carry.to(torch.int64).clone()
     out = torch.empty_like(states_i8)
     final = None
     for c in range(nc):
@@ -116,6 +118,8 @@ def state_passing(states_i8, dA_last, gate_shift=7):
         s32 = ((s32 * gq.unsqueeze(-1) + (S >> 1)) >> gate_shift) + states_i8[:, c].to(torch.int64)
         s32 = ((s32 + 2**31) % 2**32) - 2**31  # int32 wrap-around
     final = s32.clamp(-127, 127).to(torch.int8)
+    if return_carry:
+        return out, final, s32.to(torch.int32)
     return out, final
 
 
@@ -164,7 +168,8 @@ def chunk_scan(cb_i8, x, dt, dA, q_C, C_scale, states, q_D, D_scale, state_scale
 
 def ssd_combined(x, dt, dt_scale, A_log, A_log_scale, q_B, B_scale, q_C, C_scale, chunk, q_D, D_scale, dt_bias=None,
                  dt_softplus=True, dt_limit=(0.0, float("inf")), static_state_scale=None, static_cb_scale=None,
-                 alpha_hp=None, bscale_g=None, keyside=False, x_scale_hp=None, b_fp=None, b_gate_scale=None):
+                 alpha_hp=None, bscale_g=None, keyside=False, x_scale_hp=None, b_fp=None, b_gate_scale=None,
+                 initial_carry=None):
     B, L, H, P = x.shape
     dA, dtc = chunk_cumsum(dt, dt_scale, A_log, A_log_scale, chunk, dt_bias, dt_softplus, dt_limit)
     if keyside:
@@ -172,11 +177,11 @@ def ssd_combined(x, dt, dt_scale, A_log, A_log_scale, q_B, B_scale, q_C, C_scale
     else:
         st = chunk_state_value(x, q_B, dtc, dA, alpha_hp, bscale_g, static_state_scale)
     N = st.shape[-1]
-    passed, _ = state_passing(st.reshape(B, -1, H, P * N), dA[..., -1])
+    passed, _, carry = state_passing(st.reshape(B, -1, H, P * N), dA[..., -1], initial_carry=initial_carry, return_carry=True)
     passed = passed.reshape(B, -1, H, P, N)
     cb = bmm_chunk(q_C, C_scale, b_fp if keyside else q_B, B_scale, chunk, static_cb_scale, b_is_fp=keyside)
     out = chunk_scan(cb, x, dtc, dA, q_C, C_scale, passed, q_D, D_scale, static_state_scale, static_cb_scale)
-    return out, dict(dA=dA, dt=dtc, states=st, passed=passed, cb=cb)
+    return out, dict(dA=dA, dt=dtc, states=st, passed=passed, cb=cb, carry=carry)
 
 
 def hadamard_matrix(d):

@@ -31,7 +31,7 @@ class OracleRun:
     output, the exact-arithmetic output (noise floor) and the recorded codes."""
 
     def __init__(self, q, k, v, g, beta, *, family, decay, policy="kernel_static", bits=8, eta=1.0, sigma=1.0, tau=1.0,
-                 rot_qk=None, scale=None, chunk=64, dqk=None, rot_v=None, storage="rotated"):
+                 rot_qk=None, scale=None, chunk=64, dqk=None, rot_v=None, storage="rotated", calib=None):
         K = q.shape[-1]
         self.qz = zo.RoleQuantizer(policy, bits, 8, True)
         qd, kd = q, k
@@ -41,7 +41,15 @@ class OracleRun:
                        rot_v=rot_v, storage=storage, eta=eta, sigma=sigma, tau=tau, chunk=chunk, read_post=True, out_dtype=torch.float64,
                        act_dtype=q.dtype)
         self.args = (qd, kd, v, g, beta)
-        zo.calibrate(self.qz, self.run)
+        if calib is None:
+            zo.calibrate(self.qz, self.run)
+        else:  # scales from OTHER batches of the same distribution (a list of (q, k, v, g, beta)), absmax over all
+            self.qz.start_calibration()
+            for cq, ck, cv, cg, cb in calib:
+                if dqk is not None:
+                    cq, ck = cq.double() * dqk.double(), ck.double() / dqk.double()
+                zo.chunk_prefill(cq, ck, cv, cg, cb, **self.kw)
+            self.qz.finish_calibration()
         self.H, self.K, self.V = q.shape[2], K, v.shape[-1]
 
     def run(self, **over):
@@ -92,3 +100,28 @@ def reference_check(out, ref, exact, label):
     noise_max, noise_mean = n.max().item() / ref.abs().max().item(), n.mean().item() / ref.abs().mean().item()
     assert torch.isfinite(out).all() and err_max <= max(5e-3, 2 * noise_max) and err_mean <= max(2e-4, 2 * noise_mean), \
         f"{label}: rel max {err_max:.2e} rel mean {err_mean:.2e} (noise floor {noise_max:.2e} / {noise_mean:.2e})"
+
+
+def passed_states_mismatch(got, want, dA_last, label):
+    """Fixed-point state passing is integer arithmetic once the Q0.7 gate code round(exp(dA_last) * 128) is formed, so
+    its outputs must equal the oracle's exactly -- except downstream of a chunk whose gate sits on a rounding boundary,
+    where the GPU's exp and the CPU's may round the code to different sides. ``got`` / ``want`` are the entering states
+    [B,NC,H,D] (or a final state [B,H,D], treated as the state after the last chunk). Sequences (b,h) with no gate within
+    1e-4 of a boundary must match bit for bit; a sequence with such a gate at chunk c must match up to and including the
+    state entering chunk c. Returns (number of boundary gates, number of differing codes, all of them excused)."""
+    got, want = got.cpu().to(torch.int16), want.cpu().to(torch.int16)
+    final = got.dim() == 3
+    g = torch.exp(dA_last.detach().cpu().float()) * 128.0  # [B,H,NC]
+    tie = ((g - torch.floor(g)) - 0.5).abs() < 1e-4
+    B, H, NC = g.shape
+    first = torch.where(tie.any(-1), tie.float().argmax(-1), torch.full((B, H), NC + 1))  # first boundary chunk per (b,h)
+    if final:
+        strict = (first > NC).view(B, H, 1)  # the final state is downstream of every chunk
+        bad = (got != want) & strict
+    else:
+        c = torch.arange(NC).view(1, NC, 1)
+        strict = (c <= first.unsqueeze(1)).unsqueeze(-1)  # [B,NC,H,1]
+        bad = (got != want) & strict
+    nbad, ndiff = int(bad.sum()), int((got != want).sum())
+    assert nbad == 0, f"{label}: {nbad} codes differ where no gate code is on a rounding boundary (of {ndiff} differing)"
+    return int(tie.sum()), ndiff

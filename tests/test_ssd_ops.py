@@ -10,7 +10,7 @@ import torch
 import torch.nn.functional as F
 
 from oracle import ssd_oracle as so
-from tests.helpers import code_mismatch, rel_l2
+from tests.helpers import code_mismatch, passed_states_mismatch, rel_l2
 
 pytestmark = pytest.mark.gpu
 
@@ -74,8 +74,9 @@ def test_sub_ops_match_oracle(chunk, N, dtype):
     B, nc, H, P, Nn = st_ref.shape
     sp_ref, fin_ref = so.state_passing(st_ref.reshape(B, nc, H, P * Nn), k["dA"][..., -1])
     sp, fin = sc._fixedpoint_state_passing_fwd(cu(st_ref).reshape(B, nc, H, P * Nn), dAd[..., -1])
-    code_mismatch(sp, sp_ref, "passed states", budget=1e-3, max_step=2)
-    code_mismatch(fin, fin_ref, "final state", budget=1e-3, max_step=2)
+    ties, nd = passed_states_mismatch(sp, sp_ref, k["dA"][..., -1], "passed states")
+    passed_states_mismatch(fin, fin_ref, k["dA"][..., -1], "final state")
+    print(f"\nstate passing chunk={chunk} N={N}: {ties} gate codes on a rounding boundary, {nd} stored codes differ downstream of them")
     cb_ref = so.bmm_chunk(k["qC"], k["sC"], k["qB"], k["sB"], chunk, k["cb_scale"])
     cb = sc._quant_bmm_chunk_fwd(cu(k["qC"]), cu(k["sC"]), cu(k["qB"]), cu(k["sB"]), chunk, cu(k["cb_scale"]))
     code_mismatch(cb, cb_ref, "CB codes")
@@ -116,8 +117,8 @@ def test_cumsum_and_state_passing_many_heads(H, chunk):
     dAd = cu(dA_ref)
     for arg in (dAd[..., -1], dAd[..., -1].contiguous()):
         sp, fin = sc._fixedpoint_state_passing_fwd(cu(states), arg)
-        code_mismatch(sp, sp_ref, "passed states", budget=1e-3, max_step=2)
-        code_mismatch(fin, fin_ref, "final state", budget=1e-3, max_step=2)
+        passed_states_mismatch(sp, sp_ref, dA_ref[..., -1], "passed states")
+        passed_states_mismatch(fin, fin_ref, dA_ref[..., -1], "final state")
 
 
 @pytest.mark.parametrize("keyside", [False, True])
@@ -203,8 +204,8 @@ def test_ops_match_reference_kernel_golden(name):
     code_mismatch(st, g["states"], f"{name}: chunk states vs the reference kernel")
     B, NC, H, P, N = g["states"].shape
     sp, fin = sc._fixedpoint_state_passing_fwd(cu(g["states"]).reshape(B, NC, H, P * N), dAd[..., -1])
-    code_mismatch(sp, g["passed"], f"{name}: entering states vs the reference kernel", budget=1e-3, max_step=2)
-    code_mismatch(fin, g["final"], f"{name}: final state vs the reference kernel", budget=1e-3, max_step=2)
+    passed_states_mismatch(sp, g["passed"], g["dA"][..., -1], f"{name}: entering states vs the reference kernel")
+    passed_states_mismatch(fin, g["final"], g["dA"][..., -1], f"{name}: final state vs the reference kernel")
     cb = sc._quant_bmm_chunk_fwd(cu(g["q_C"]), cu(g["C_scale"]), cu(g["b_fp"] if key else g["q_B"]), cu(g["B_scale"]), C,
                                  cu(g["cb_scale"]), b_is_fp=key)
     code_mismatch(cb, g["cb"], f"{name}: CB codes vs the reference kernel")
