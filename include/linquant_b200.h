@@ -199,8 +199,9 @@ typedef struct {
   const float* D;       /* [H] or [H,P] (already multiplied by its scale) or null */
   int D_has_hdim;
   void* out;
-  int scan_kernel;      /* lq_ssd_chunk_scan: 0 = the library's choice (the faster one as measured on B200), 1 = warp-level MMA
-                           kernel, 2 = tcgen05 + TMA kernel (d_state 128 and chunk 128 or 256 only) */
+  int scan_kernel;      /* lq_ssd_chunk_scan: 0 = the library's choice (the faster one as measured on B200: the tcgen05 kernel
+                           where it applies), 1 = warp-level MMA kernel, 2 = persistent tcgen05 + TMA kernel (d_state 128
+                           and chunk 128 or 256 only) */
   int* status;          /* optional device int32: set to 1 by a kernel whose bounded wait on a TMA / MMA barrier ran out
                            (its output is then not valid); the caller zeroes it and reads it after synchronising */
   /* ---- lq_ssd_state_passing only: the integer carry across calls / GPUs (all optional, null = a zero carry, nothing

@@ -746,45 +746,67 @@ __global__ void __launch_bounds__(256) ssd_rotate_rows_kernel(const T* x, long l
                                                               long long off_b, long long off_c, int T_len, int G,
                                                               const float* signs, const float* inv_b, const float* inv_c,
                                                               const float* dqk_b, const float* dqk_c, int8_t* q_b,
-                                                              int8_t* q_c, T* y) {
+                                                              int8_t* q_c, T* y, int rows_per_cta) {
   // QUANT: blockIdx.y in [0, 2G) selects (B|C, group); otherwise blockIdx.y is the head and y is the dense output.
-  constexpr int LPR = N / 8, RPW = 32 / LPR;
+  // A CTA walks rows_per_cta consecutive tokens: a row is short (N values), so the per-row constants (signs, D_QK,
+  // reciprocal scale) are loaded once per thread and four rows per thread are in flight at a time.
+  constexpr int LPR = N / 8, RPW = 32 / LPR, STEP = 8 * RPW, UNROLL = 4;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int r = lane % LPR, sub = lane / LPR;
   const int b = blockIdx.z;
   const int which = QUANT ? blockIdx.y / G : 0, grp = QUANT ? blockIdx.y % G : blockIdx.y;
-  int t = (blockIdx.x * 8 + warp) * RPW + sub;
-  const bool live = t < T_len;
-  if (!live) t = T_len - 1;
-  const T* src = x + (size_t)b * stride_b + (size_t)t * stride_t + (which ? off_c : off_b) + (size_t)grp * N + 8 * r;
-  float v[8];
-  Act<T>::unpack8(__ldg(reinterpret_cast<const uint4*>(src)), v);
+  const T* src0 = x + (size_t)b * stride_b + (which ? off_c : off_b) + (size_t)grp * N + 8 * r;
   const float* dq = QUANT ? (which ? dqk_c : dqk_b) : nullptr;
-  if (dq != nullptr) {
+  float sg[8], dqv[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = fp16r(__fmul_rn(v[i], fp16r(dq[grp * N + 8 * r + i])));
+  for (int i = 0; i < 8; ++i) {
+    sg[i] = signs != nullptr ? signs[grp * N + 8 * r + i] : 1.f;
+    dqv[i] = dq != nullptr ? fp16r(dq[grp * N + 8 * r + i]) : 1.f;
   }
-  if (signs != nullptr) {
+  const float inv = QUANT ? (which ? inv_c[grp] : inv_b[grp]) : 1.f;
+  const float hs = bf16r(N == 128 ? 0.125f : 0.17677669529663687f);
+  const int row_end = min(T_len, (int)(blockIdx.x + 1) * rows_per_cta);
+  // the loop bound is warp-uniform (the butterfly shuffles across all lanes of the warp)
+  for (int tw = blockIdx.x * rows_per_cta + warp * RPW; tw < row_end; tw += STEP * UNROLL) {
+    const int t0 = tw + sub;
+    uint4 raw[UNROLL];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = bf16r(__fmul_rn(v[i], signs[grp * N + 8 * r + i]));
-    fwht8<LPR>(v, r);
-    const float hs = bf16r(N == 128 ? 0.125f : 0.17677669529663687f);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(v[i], hs), 0.70710678118654752f);
-  }
-  if (QUANT) {
-    const float inv = which ? inv_c[grp] : inv_b[grp];
-    int cd[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) cd[i] = round_rint(__fmul_rn(fp16r(v[i]), inv), -128.f, 127.f);
-    if (live) {
-      int8_t* dst = (which ? q_c : q_b) + (((size_t)b * T_len + t) * G + grp) * N + 8 * r;
-      *reinterpret_cast<uint2*>(dst) = make_uint2(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4], cd[5], cd[6], cd[7]));
+    for (int u = 0; u < UNROLL; ++u) {
+      const int t = t0 + u * STEP;
+      // rows past the end are clamped for the load (the shuffles below need every lane) and never stored
+      raw[u] = __ldg(reinterpret_cast<const uint4*>(src0 + (size_t)min(t, T_len - 1) * stride_t));
     }
-  } else if (live) {
-    T* dst = y + (((size_t)b * T_len + t) * G + grp) * N + 8 * r;
-    *reinterpret_cast<uint4*>(dst) = make_uint4(Act<T>::pack2(v[0], v[1]), Act<T>::pack2(v[2], v[3]),
-                                                Act<T>::pack2(v[4], v[5]), Act<T>::pack2(v[6], v[7]));
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int t = t0 + u * STEP;
+      const bool live = t < row_end;
+      float v[8];
+      Act<T>::unpack8(raw[u], v);
+      if (dq != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = fp16r(__fmul_rn(v[i], dqv[i]));
+      }
+      if (signs != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = bf16r(__fmul_rn(v[i], sg[i]));
+        fwht8<LPR>(v, r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(v[i], hs), 0.70710678118654752f);
+      }
+      if (QUANT) {
+        int cd[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) cd[i] = round_rint(__fmul_rn(fp16r(v[i]), inv), -128.f, 127.f);
+        if (live) {
+          int8_t* dst = (which ? q_c : q_b) + (((size_t)b * T_len + t) * G + grp) * N + 8 * r;
+          *reinterpret_cast<uint2*>(dst) = make_uint2(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4], cd[5], cd[6], cd[7]));
+        }
+      } else if (live) {
+        T* dst = y + (((size_t)b * T_len + t) * G + grp) * N + 8 * r;
+        *reinterpret_cast<uint4*>(dst) = make_uint4(Act<T>::pack2(v[0], v[1]), Act<T>::pack2(v[2], v[3]),
+                                                    Act<T>::pack2(v[4], v[5]), Act<T>::pack2(v[6], v[7]));
+      }
+    }
   }
 }
 
@@ -960,13 +982,12 @@ extern "C" int lq_ssd_chunk_scan(const lq_ssd_problem* p, lq_stream stream) {
   if (!p->cb || !p->dt || !p->dA || !p->q_C || !p->C_scale || !p->passed || !p->state_scale || !p->cb_scale || !p->out)
     return fail(LQ_ERR_NULL, "chunk_scan: cb, dt, dA, q_C, C_scale, passed, state_scale, cb_scale, out required");
   cudaStream_t st = (cudaStream_t)stream;
-  // Two kernels: the warp-level MMA kernel (every supported shape) and a tcgen05 + TMA kernel (d_state 128, chunks of
-  // 128 or 256 tokens). Building the decay-masked operand dominates both; at the Mamba-2 2.7B shape the warp-level
-  // kernel, with 16 resident warps hiding each other's latencies, is the faster one on B200 and is the default.
+  // Two kernels: a persistent, software-pipelined tcgen05 + TMA kernel (d_state 128, chunks of 128 or 256 tokens: the
+  // Mamba-2 shapes), which is the library's choice where it applies, and the warp-level MMA kernel (every supported shape).
   const bool tc_ok = p->N == 128 && p->chunk % 128 == 0;
   if (p->scan_kernel == 2 && !tc_ok) return fail(LQ_ERR_UNSUPPORTED, "chunk_scan: the tcgen05 kernel needs d_state 128 and chunk 128 or 256");
   if (p->scan_kernel < 0 || p->scan_kernel > 2) return fail(LQ_ERR_SHAPE, "chunk_scan: scan_kernel must be 0, 1 or 2");
-  if (p->scan_kernel == 2) return run_chunk_scan_tc(p, p->status, st);
+  if (p->scan_kernel == 2 || (p->scan_kernel == 0 && tc_ok)) return run_chunk_scan_tc(p, p->status, st);
   if (p->x_dtype == LQ_F16) return p->N == 128 ? launch_scan<__half, 128>(p, st) : launch_scan<__half, 64>(p, st);
   return p->N == 128 ? launch_scan<__nv_bfloat16, 128>(p, st) : launch_scan<__nv_bfloat16, 64>(p, st);
 }
@@ -975,10 +996,10 @@ template <typename T, bool QUANT>
 static int launch_rotate(const T* x, long long sb, long long stt, long long ob, long long oc, int B, int T_len, int G, int N,
                          int gy, const float* signs, const float* ib, const float* ic, const float* db, const float* dc,
                          int8_t* qb, int8_t* qc, T* y, cudaStream_t st) {
-  const int rows_per_cta = 8 * (32 / (N / 8));
+  const int rows_per_cta = 256;
   dim3 grid((T_len + rows_per_cta - 1) / rows_per_cta, gy, B);
-  if (N == 128) ssd_rotate_rows_kernel<T, 128, QUANT><<<grid, 256, 0, st>>>(x, sb, stt, ob, oc, T_len, G, signs, ib, ic, db, dc, qb, qc, y);
-  else if (N == 64) ssd_rotate_rows_kernel<T, 64, QUANT><<<grid, 256, 0, st>>>(x, sb, stt, ob, oc, T_len, G, signs, ib, ic, db, dc, qb, qc, y);
+  if (N == 128) ssd_rotate_rows_kernel<T, 128, QUANT><<<grid, 256, 0, st>>>(x, sb, stt, ob, oc, T_len, G, signs, ib, ic, db, dc, qb, qc, y, rows_per_cta);
+  else if (N == 64) ssd_rotate_rows_kernel<T, 64, QUANT><<<grid, 256, 0, st>>>(x, sb, stt, ob, oc, T_len, G, signs, ib, ic, db, dc, qb, qc, y, rows_per_cta);
   else return fail(LQ_ERR_UNSUPPORTED, "Hadamard rows: width %d (64 or 128 supported)", N);
   return check_launch("ssd_rotate_rows_kernel");
 }

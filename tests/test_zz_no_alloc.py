@@ -27,10 +27,12 @@ def test_no_alloc_entry_matches_regular_entry_twice():
     from linquant_b200.kernels.mamba2.chunk_state import (_quant_chunk_state_fwd_xfp_static_int8,
                                                           chunk_state_value_no_alloc)
 
+    keep = []  # nothing is freed between the two measurements below
     for seed in (11, 12):  # second call reuses the array that still holds the first call's bytes
         x, qB, dt, dA, alpha, bscale, out_scale = _inputs(seed)
         want = _quant_chunk_state_fwd_xfp_static_int8(x, qB, dt, dA, alpha, bscale, out_scale)
         out = torch.full_like(want, 77)
+        keep.append((x, qB, dt, dA, alpha, bscale, out_scale, want, out))
         torch.cuda.synchronize()
         held, free = torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]
         got = chunk_state_value_no_alloc(x, qB, dt, dA, alpha, bscale, out_scale, out)
