@@ -144,7 +144,8 @@ class M2Layer:
     """One layer's operands on the device: xBC (x | B | C lanes, bf16), raw dt, A_log, D, rotation signs, scales. Seeds
     are per (layer, batch element), so a batch shard holds the same data on any number of GPUs."""
 
-    def __init__(self, layer, batch_ids, dev, L=None):
+    def __init__(self, layer, batch_ids, dev, L=None, segment=None):
+        """segment = (r, W): keep only tokens [r L/W, (r+1) L/W) of every batch element (sequence-parallel mode)."""
         H, P, N, G = M2["H"], M2["P"], M2["N"], M2["G"]
         L = L or M2["L"]
         width = H * P + 2 * G * N
@@ -154,10 +155,12 @@ class M2Layer:
         self.D = torch.randn(H, generator=gl, device=dev)
         self.signs = (torch.randint(0, 2, (G, N), generator=gl, device=dev).float() * 2 - 1)
         self.heavy = torch.randperm(width, generator=gl, device=dev)[: max(1, round(0.01 * width))]
-        self.xBC = torch.empty(len(batch_ids), L, width, dtype=torch.bfloat16, device=dev)
-        self.dt_raw = torch.empty(len(batch_ids), L, H, dtype=torch.float32, device=dev)
+        lo, hi = (0, L) if segment is None else (segment[0] * (L // segment[1]), (segment[0] + 1) * (L // segment[1]))
+        self.xBC = torch.empty(len(batch_ids), hi - lo, width, dtype=torch.bfloat16, device=dev)
+        self.dt_raw = torch.empty(len(batch_ids), hi - lo, H, dtype=torch.float32, device=dev)
         for i, b in enumerate(batch_ids):
-            self.xBC[i], self.dt_raw[i] = m2_draw(1_000_003 * layer + b, L, self.heavy, dev)
+            xb, db = m2_draw(1_000_003 * layer + b, L, self.heavy, dev)
+            self.xBC[i], self.dt_raw[i] = xb[lo:hi], db[lo:hi]
         self.scales = None
 
     def calibrate(self, dev, batches=4, Lc=1024):
@@ -180,8 +183,9 @@ class M2Layer:
         return self
 
 
-def m2_layer_forward(Lr, keyside=False):
-    """The product path of one layer: prologue on xBC, then the combined SSD forward. Returns out [B,L,H,P] fp16."""
+def m2_layer_forward(Lr, keyside=False, link=None):
+    """The product path of one layer: prologue on xBC, then the combined SSD forward. Returns out [B,L,H,P] fp16.
+    With `link` the layer is one rank's segment of the sequence and the state passing hands its carry to the next rank."""
     from linquant_b200.kernels.hadamard import kronecker_hadamard_fwd
     from linquant_b200.kernels.mamba2 import ssd_combined as sc
     from linquant_b200.kernels.mamba2.fused_split_rotate_xBC import fused_split_rotate_quant_xBC
@@ -193,10 +197,12 @@ def m2_layer_forward(Lr, keyside=False):
     if keyside:  # the key side quantises the gate-weighted, rotated B inside the chunk-state kernel
         Bl = Lr.xBC[..., H * P: H * P + G * N].unflatten(-1, (G, N))
         b_fp = kronecker_hadamard_fwd(Bl, Lr.signs, G)
+    if link is not None:
+        link.next_call()
     out, _ = sc._quant_mamba_chunk_scan_combined_fwd(
         x, Lr.dt_raw, 1.0, Lr.A_log, 1.0, qB, S["B_scale"], qC, S["C_scale"], C, Lr.D, 1.0, dt_softplus=True,
         static_state_scale=S["state_scale"], static_cb_scale=S["cb_scale"], alpha_hp=S["alpha_hp"], bscale_g=S["B_scale"],
-        keyside=keyside, x_scale_hp=S["x_scale_hp"], b_fp=b_fp, b_gate_scale=S["b_gate_scale"])
+        keyside=keyside, x_scale_hp=S["x_scale_hp"], b_fp=b_fp, b_gate_scale=S["b_gate_scale"], _link=link)
     return out
 
 
@@ -563,16 +569,55 @@ def m2_keyside_config(dev, world, rank, reps=3):
                 shape="one layer of the stack, key-side absorption (INT8 x against gate-weighted B quantised in-kernel)")
 
 
+def m2_seqpar_config(dev, world, rank, barrier, reps=3):
+    """One layer of the stack with the SEQUENCE split over the ranks (every rank holds all 8 batch elements and 80 heads of
+    its L / world tokens): cumsum, chunk state and C.B^T run at once on all ranks, the fixed-point state passing forms a
+    chain in which each rank's kernel stores its INT32 carry straight into the next rank's memory over NVLink, the chunk
+    scans run at once again."""
+    from linquant_b200 import _cabi, seqpar
+
+    Lr = M2Layer(0, list(range(M2["B"])), dev, segment=(rank, world)).calibrate(dev)
+    link = seqpar.SsdLink(M2["B"], M2["H"], M2["P"] * M2["N"], dev, wait_ns=5_000_000_000)
+    m2_layer_forward(Lr, link=link)
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with StageTimer() as st:
+        a.record()
+        for _ in range(reps):
+            m2_layer_forward(Lr, link=link)
+        b.record()
+        stage_ms, _ = st.totals_ms()
+    _cabi.check_status(dev)
+    barrier()
+    link.close()
+    ab = m2_algorithmic_bytes()
+    return dict(total_ms=a.elapsed_time(b) / reps, stage_ms={k: v / reps for k, v in stage_ms.items()}, tokens=M2["B"] * M2["L"],
+                ht_rank=M2["B"] * M2["H"] * M2["L"] // world, path_bytes=ab["path"], stage_bytes={k: ab.get(k) for k in stage_ms},
+                shape=f"one layer of the stack, sequence split over {world} GPUs, INT32 carry stored into the next GPU's memory by the state-passing kernel")
+
+
 def side_configs(dev, world, rank, barrier):
     import torch.distributed as dist
 
     peak, _ = measured_peak()
     out = {}
-    for name in list(ZOO) + ["mamba2_layer_keyside"]:
+    names = list(ZOO) + ["mamba2_layer_keyside"] + (["mamba2_layer_seqpar"] if world > 1 and M2["L"] % (world * M2["C"]) == 0 else [])
+    for name in names:
         try:
-            r = m2_keyside_config(dev, world, rank) if name == "mamba2_layer_keyside" else zoo_config(name, dev, world, rank)
+            if name == "mamba2_layer_seqpar":
+                r = m2_seqpar_config(dev, world, rank, barrier)
+            else:
+                r = m2_keyside_config(dev, world, rank) if name == "mamba2_layer_keyside" else zoo_config(name, dev, world, rank)
+            err = None
         except Exception as e:  # a side record must not take the headline down
-            out[name] = {"error": f"{type(e).__name__}: {e}"[:200]}
+            err = f"{type(e).__name__}: {e}"[:200]
+        if world > 1:  # every rank learns whether any rank failed, so that all skip the reductions below together
+            flag = torch.tensor([0 if err is None else 1], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+            if int(flag.item()) and err is None:
+                err = "another rank failed"
+        if err is not None:
+            out[name] = {"error": err}
             torch.cuda.empty_cache()
             continue
         keys = sorted(r["stage_ms"])

@@ -19,40 +19,44 @@ __device__ __forceinline__ int round_rint(float y, float lo, float hi) {
 }
 
 // ------------------------------------------------------------------------------------------------ cumsum
-// mamba2/chunk_cumsum.py:52-74. One CTA per (chunk, batch, block of 32 heads). The dt tile is read with the head
-// index contiguous (as it lies in memory), transformed and parked in shared memory; each warp then scans four heads
-// with the token index across its lanes, so both outputs are written with the token index contiguous. The running sum
-// is kept in double: a warp scan per 32 tokens plus a carry.
+// mamba2/chunk_cumsum.py:52-74. One CTA per (chunk, batch) takes the chunk's dt rows for ALL heads, which are one
+// contiguous block of C * H floats in memory (16-byte loads, fully coalesced), transforms them and parks them in shared
+// memory; each warp then scans heads with the token index across its lanes, so both outputs are written with the token
+// index contiguous. The running sum is kept in double and rounded to fp32 per prefix: a warp scan per 32 tokens plus a
+// carry.
 __global__ void __launch_bounds__(256) ssd_cumsum_kernel(lq_ssd_problem p) {
-  extern __shared__ float s_dtv[];  // [C][33]
-  const int c = blockIdx.x, b = blockIdx.y, h0 = blockIdx.z * 32;
-  const int C = p.chunk, NC = p.L / C;
+  extern __shared__ float s_dtv[];  // [C][H + 1]
+  const int c = blockIdx.x, b = blockIdx.y;
+  const int C = p.chunk, NC = p.L / C, H = p.H, LD = H + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float a_scale = p.A_log_scale_dev ? *p.A_log_scale_dev : p.A_log_scale;
   const float d_scale = p.dt_scale_dev ? *p.dt_scale_dev : p.dt_scale;
   {
-    const int h = h0 + lane;
-    const bool live = h < p.H;
-    const float bias = (p.dt_bias && live) ? p.dt_bias[h] : 0.f;
-    const float* src = p.dt_in + ((size_t)b * p.L + (size_t)c * C) * p.H + h;
-    for (int t = warp; t < C; t += 8) {
-      float x = live ? __ldg(src + (size_t)t * p.H) : 0.f;
+    const float* src = p.dt_in + ((size_t)b * p.L + (size_t)c * C) * H;
+    const int total = C * H;
+    auto put = [&](int i, float x) {
+      const int t = i / H, h = i - t * H;
       x = __fmul_rn(d_scale, x);
-      if (p.dt_bias) x = __fadd_rn(x, bias);
+      if (p.dt_bias) x = __fadd_rn(x, p.dt_bias[h]);
       if (p.dt_softplus) x = x > 20.f ? x : logf(__fadd_rn(1.0f, expf(x)));
-      x = fminf(fmaxf(x, p.dt_min), p.dt_max);
-      s_dtv[t * 33 + lane] = x;
+      s_dtv[t * LD + h] = fminf(fmaxf(x, p.dt_min), p.dt_max);
+    };
+    if ((total & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+      for (int i = 4 * threadIdx.x; i < total; i += 1024) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(src + i));
+        put(i, v.x); put(i + 1, v.y); put(i + 2, v.z); put(i + 3, v.w);
+      }
+    } else {
+      for (int i = threadIdx.x; i < total; i += 256) put(i, __ldg(src + i));
     }
   }
   __syncthreads();
-  for (int hl = warp; hl < 32; hl += 8) {
-    const int h = h0 + hl;
-    if (h >= p.H) break;
+  for (int h = warp; h < H; h += 8) {
     const float A = -expf(__fmul_rn(a_scale, p.A_log[h]));
-    const size_t obase = (((size_t)b * p.H + h) * NC + c) * C;
+    const size_t obase = (((size_t)b * H + h) * NC + c) * C;
     double carry = 0.0;
     for (int t0 = 0; t0 < C; t0 += 32) {
-      const float x = s_dtv[(t0 + lane) * 33 + hl];
+      const float x = s_dtv[(t0 + lane) * LD + h];
       p.dt[obase + t0 + lane] = x;
       double v = (double)__fmul_rn(x, A);
 #pragma unroll
@@ -862,7 +866,10 @@ using namespace lq;
 extern "C" int lq_ssd_chunk_cumsum(const lq_ssd_problem* p, lq_stream stream) {
   if (int e = ssd_check(p, "chunk_cumsum")) return e;
   if (!p->dt_in || !p->A_log || !p->dt || !p->dA) return fail(LQ_ERR_NULL, "chunk_cumsum: dt_in, A_log, dt, dA required");
-  ssd_cumsum_kernel<<<dim3(p->L / p->chunk, p->B, (p->H + 31) / 32), 256, (size_t)p->chunk * 33 * sizeof(float), (cudaStream_t)stream>>>(*p);
+  const size_t smem = (size_t)p->chunk * (p->H + 1) * sizeof(float);
+  if (smem > 200 * 1024) return fail(LQ_ERR_UNSUPPORTED, "chunk_cumsum: chunk * nheads = %d * %d exceeds the shared-memory tile", p->chunk, p->H);
+  cudaFuncSetAttribute(ssd_cumsum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  ssd_cumsum_kernel<<<dim3(p->L / p->chunk, p->B), 256, smem, (cudaStream_t)stream>>>(*p);
   return check_launch("ssd_cumsum_kernel");
 }
 
@@ -885,9 +892,12 @@ extern "C" int lq_ssd_state_passing(const lq_ssd_problem* p, lq_stream stream) {
 
 namespace lq {
 int run_chunk_state_value_tc(const lq_ssd_problem* p, int* status, cudaStream_t st);
+bool chunk_state_value_tc2_applies(const lq_ssd_problem* p);
+int run_chunk_state_value_tc2(const lq_ssd_problem* p, int* status, cudaStream_t st);
 int run_chunk_scan_tc(const lq_ssd_problem* p, int* status, cudaStream_t st);
 }
-static int ssd_chunk_state(const lq_ssd_problem* p, bool keyside, lq_stream stream) {
+// with_qbt: take the path that goes through the transposed copy of q_B even where the transposition-free kernel applies
+static int ssd_chunk_state(const lq_ssd_problem* p, bool keyside, lq_stream stream, bool with_qbt = false) {
   const char* what = keyside ? "chunk_state_key" : "chunk_state_value";
   if (int e = ssd_check(p, what)) return e;
   if (int e = ssd_check_pn(p, what)) return e;
@@ -898,7 +908,10 @@ static int ssd_chunk_state(const lq_ssd_problem* p, bool keyside, lq_stream stre
     if (!p->b_fp || !p->x_scale_hp || !p->b_gate_scale) return fail(LQ_ERR_NULL, "%s: b_fp, x_scale_hp, b_gate_scale required", what);
     launch_chunk_state<true>(p, grid, st);
   } else {
-    if (!p->q_B || !p->q_BT || !p->alpha_hp || !p->bscale_g) return fail(LQ_ERR_NULL, "%s: q_B, q_BT, alpha_hp, bscale_g required", what);
+    if (!p->q_B || !p->alpha_hp || !p->bscale_g) return fail(LQ_ERR_NULL, "%s: q_B, alpha_hp, bscale_g required", what);
+    // d_state 128 with chunks of 128 / 256 tokens: both tcgen05 operands in their natural layouts, no scratch at all
+    if (!with_qbt && chunk_state_value_tc2_applies(p)) return run_chunk_state_value_tc2(p, p->status, st);
+    if (!p->q_BT) return fail(LQ_ERR_NULL, "%s: q_BT (scratch for the transposed q_B) required for this shape", what);
     ssd_transpose_b_kernel<<<dim3(p->L / 64, p->G, p->B), 256, 0, st>>>(p->q_B, p->q_BT, p->L, p->G, p->N, p->chunk);
     if (int e = check_launch("ssd_transpose_b_kernel")) return e;
     // chunks of 128 or 256 tokens run on tcgen05 + TMA; 64- and 192-token chunks on the warp-level MMA kernel
@@ -951,7 +964,7 @@ extern "C" int lq_ssd_chunk_state_value_static(const lq_ssd_problem* p, lq_strea
                 "use lq_ssd_chunk_state_value with a caller-owned q_BT for larger problems", need, lq::kStaticScratchBytes);
   lq_ssd_problem q = *p;
   if (int e = lq::static_scratch(&q.q_BT)) return e;
-  return ssd_chunk_state(&q, false, stream);
+  return ssd_chunk_state(&q, false, stream, true);
 }
 extern "C" int lq_ssd_chunk_state_key(const lq_ssd_problem* p, lq_stream stream) { return ssd_chunk_state(p, true, stream); }
 
