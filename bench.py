@@ -411,12 +411,12 @@ def run_ours(args):
         if peak_i8 and k in M2_INT8_OPS:
             rec["int8_tensor_frac"] = round(M2_INT8_OPS[k] * ht_rank / (us * 1e-6) / 1e12 / peak_i8, 4)
         kernels[k] = rec
-    reduced = (n_layers, B) != (M2["layers"], M2["B"])
+    reduced = (n_layers, B, L) != (M2["layers"], M2["B"], 16384)
     line = {
         "metric": "INT8 chunk-prefill Mtokens/s", "value": tokens * args.steps / (ms * 1e-3) / 1e6, "unit": "Mtokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": WORKLOAD if not reduced else f"REDUCED ({n_layers} layers, batch {B}): not a bench value; " + WORKLOAD,
+        "config": {"workload": WORKLOAD if not reduced else f"REDUCED ({n_layers} layers, batch {B}, L {L}): not a bench value; " + WORKLOAD,
                    "sharding": f"batch x heads over {world} GPU(s): {len(bids)} batch element(s) per rank, no collective",
                    "launch": mode, "distinct_layer_inputs_in_hbm": distinct,
                    "l2": f"each layer reads {per_layer / 1e6:.0f} MB of fresh inputs per rank (L2 is 126 MB); no flush",
@@ -763,11 +763,13 @@ def main():
     ap.add_argument("--eager", action="store_true", help="launch the step kernel by kernel from Python instead of replaying a CUDA graph")
     ap.add_argument("--layers", type=int, default=M2["layers"], help="fewer layers: a reduced run for profiling, not a bench value")
     ap.add_argument("--batch", type=int, default=M2["B"], help="smaller batch: a reduced run for profiling, not a bench value")
+    ap.add_argument("--seqlen", type=int, default=M2["L"], help="shorter sequences: a reduced run for profiling, not a bench value")
     ap.add_argument("--kernels-only", action="store_true",
                     help="device-resident loop and per-kernel times only (no host-buffer leg, no side records, no CPU baseline)")
     ap.add_argument("--stages", default=None, metavar="CONFIG",
                     help="per-kernel times of one configuration (simple_gla, gated_deltanet, kda, mamba2_layer, mamba2_layer_keyside)")
     args = ap.parse_args()
+    M2["L"] = args.seqlen
     if args.stages:
         return run_stages(args)
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:  # plain `python bench.py --gpus N`: become N ranks

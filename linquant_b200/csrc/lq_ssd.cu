@@ -24,7 +24,7 @@ __device__ __forceinline__ int round_rint(float y, float lo, float hi) {
 // memory; each warp then scans heads with the token index across its lanes, so both outputs are written with the token
 // index contiguous. The running sum is kept in double and rounded to fp32 per prefix: a warp scan per 32 tokens plus a
 // carry.
-__global__ void __launch_bounds__(256) ssd_cumsum_kernel(lq_ssd_problem p) {
+__global__ void __launch_bounds__(1024) ssd_cumsum_kernel(lq_ssd_problem p) {
   extern __shared__ float s_dtv[];  // [C][H + 1]
   const int c = blockIdx.x, b = blockIdx.y;
   const int C = p.chunk, NC = p.L / C, H = p.H, LD = H + 1;
@@ -42,16 +42,16 @@ __global__ void __launch_bounds__(256) ssd_cumsum_kernel(lq_ssd_problem p) {
       s_dtv[t * LD + h] = fminf(fmaxf(x, p.dt_min), p.dt_max);
     };
     if ((total & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
-      for (int i = 4 * threadIdx.x; i < total; i += 1024) {
+      for (int i = 4 * threadIdx.x; i < total; i += 4 * blockDim.x) {
         const float4 v = __ldg(reinterpret_cast<const float4*>(src + i));
         put(i, v.x); put(i + 1, v.y); put(i + 2, v.z); put(i + 3, v.w);
       }
     } else {
-      for (int i = threadIdx.x; i < total; i += 256) put(i, __ldg(src + i));
+      for (int i = threadIdx.x; i < total; i += blockDim.x) put(i, __ldg(src + i));
     }
   }
   __syncthreads();
-  for (int h = warp; h < H; h += 8) {
+  for (int h = warp; h < H; h += (int)(blockDim.x >> 5)) {
     const float A = -expf(__fmul_rn(a_scale, p.A_log[h]));
     const size_t obase = (((size_t)b * H + h) * NC + c) * C;
     double carry = 0.0;
@@ -869,7 +869,7 @@ extern "C" int lq_ssd_chunk_cumsum(const lq_ssd_problem* p, lq_stream stream) {
   const size_t smem = (size_t)p->chunk * (p->H + 1) * sizeof(float);
   if (smem > 200 * 1024) return fail(LQ_ERR_UNSUPPORTED, "chunk_cumsum: chunk * nheads = %d * %d exceeds the shared-memory tile", p->chunk, p->H);
   cudaFuncSetAttribute(ssd_cumsum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  ssd_cumsum_kernel<<<dim3(p->L / p->chunk, p->B), 256, smem, (cudaStream_t)stream>>>(*p);
+  ssd_cumsum_kernel<<<dim3(p->L / p->chunk, p->B), 1024, smem, (cudaStream_t)stream>>>(*p);
   return check_launch("ssd_cumsum_kernel");
 }
 

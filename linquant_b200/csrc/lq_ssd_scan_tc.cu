@@ -53,6 +53,10 @@ __device__ __forceinline__ void sts_h(uint32_t addr, __half v) {
 __device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
+__device__ __forceinline__ uint32_t hfma2u(uint32_t a, uint32_t b, uint32_t c) {
+  const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b), *reinterpret_cast<const __half2*>(&c));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
 __device__ __forceinline__ uint32_t hmul2u(uint32_t a, uint32_t b) {
   const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
   return *reinterpret_cast<const uint32_t*>(&r);
@@ -158,7 +162,8 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
   const uint32_t s_dts = s_dg + 8192;                             // f32 [C] S_cb * dt
   const uint32_t s_ratio = s_dts + 1024;                          // f32 [16] exp(dA[16 g] - dA[16 (g-1)])
   const uint32_t s_zero = s_ratio + 64;                           // 32 bytes of zeros: the weights of a group above the diagonal
-  const uint32_t s_cs = s_zero + 64;                              // f32 [2][64] s_C * state scale, per stage
+  const uint32_t s_dvec = s_zero + 64;                            // fp16 [16][16]: D on the diagonal (a per-head D joins M there)
+  const uint32_t s_cs = s_dvec + 512;                             // f32 [2][64] s_C * state scale, per stage
   const uint32_t s_D = s_cs + 512;                                // f32 [2][64]
   const uint32_t s_bars = s_D + 512;                              // full_in[2] out_ready[2] ring_full[2] ring_empty[2] acc_full[2]
   const uint32_t s_tbase = s_bars + 80;
@@ -168,6 +173,9 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   constexpr int kProducerWarp = kWorkers / 32, kMmaWarp = kProducerWarp + 1;
   const int n_mine = (n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;  // items blockIdx.x + j * gridDim.x
+  // The D x residual: a per-head D is added to the diagonal of M (M[t,t] + D, then one product with x on the tensor core);
+  // a per-channel D cannot be, and is applied in the epilogue from the x row.
+  const int dmode = p.D == nullptr ? 0 : (p.D_has_hdim ? 2 : 1);
 
   if (tid == 0) {
 #pragma unroll
@@ -304,29 +312,44 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
           tmem_ld16(tacc_i + lane_addr + 64 * e_mb + col0, ri);
           tmem_ld16(tacc_f + lane_addr + 64 * e_mb + col0, rf);
           const uint32_t pa = xrow + (((2 * ch) ^ (t & 7)) << 4), pb = xrow + (((2 * ch + 1) ^ (t & 7)) << 4);
-          const uint4 xa = lds128(pa), xb = lds128(pb);
-          float csv[16], Dv[16];
+          float csv[16];
 #pragma unroll
           for (int v4 = 0; v4 < 4; ++v4) {
-            const float4 a = lds_f4(s_cs + 256 * s + 4 * (col0 + 4 * v4)), d = lds_f4(s_D + 256 * s + 4 * (col0 + 4 * v4));
+            const float4 a = lds_f4(s_cs + 256 * s + 4 * (col0 + 4 * v4));
             csv[4 * v4] = a.x; csv[4 * v4 + 1] = a.y; csv[4 * v4 + 2] = a.z; csv[4 * v4 + 3] = a.w;
-            Dv[4 * v4] = d.x; Dv[4 * v4 + 1] = d.y; Dv[4 * v4 + 2] = d.z; Dv[4 * v4 + 3] = d.w;
           }
-          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-          float xv[16];
-          Act<__half>::unpack8(xa, *reinterpret_cast<float (*)[8]>(&xv[0]));
-          Act<__half>::unpack8(xb, *reinterpret_cast<float (*)[8]>(&xv[8]));
           uint32_t o[8];
+          if (dmode == 2) {
+            const uint4 xa = lds128(pa), xb = lds128(pb);
+            float Dv[16];
 #pragma unroll
-          for (int e2 = 0; e2 < 8; ++e2) {
-            float v[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int e = 2 * e2 + u;
-              const float sread = __fmul_rn(__fmul_rn((float)(int)ri[e], csv[e]), ga);
-              v[u] = fmaf(xv[e], Dv[e], __fadd_rn(sread, __uint_as_float(rf[e])));
+            for (int v4 = 0; v4 < 4; ++v4) {
+              const float4 d = lds_f4(s_D + 256 * s + 4 * (col0 + 4 * v4));
+              Dv[4 * v4] = d.x; Dv[4 * v4 + 1] = d.y; Dv[4 * v4 + 2] = d.z; Dv[4 * v4 + 3] = d.w;
             }
-            o[e2] = Act<__half>::pack2(v[0], v[1]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            float xv[16];
+            Act<__half>::unpack8(xa, *reinterpret_cast<float (*)[8]>(&xv[0]));
+            Act<__half>::unpack8(xb, *reinterpret_cast<float (*)[8]>(&xv[8]));
+#pragma unroll
+            for (int e2 = 0; e2 < 8; ++e2) {
+              float v[2];
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                const int e = 2 * e2 + u;
+                const float sread = __fmul_rn(__fmul_rn((float)(int)ri[e], csv[e]), ga);
+                v[u] = fmaf(xv[e], Dv[e], __fadd_rn(sread, __uint_as_float(rf[e])));
+              }
+              o[e2] = Act<__half>::pack2(v[0], v[1]);
+            }
+          } else {
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+            for (int e2 = 0; e2 < 8; ++e2) {
+              const float v0 = fmaf(__fmul_rn((float)(int)ri[2 * e2], csv[2 * e2]), ga, __uint_as_float(rf[2 * e2]));
+              const float v1 = fmaf(__fmul_rn((float)(int)ri[2 * e2 + 1], csv[2 * e2 + 1]), ga, __uint_as_float(rf[2 * e2 + 1]));
+              o[e2] = Act<__half>::pack2(v0, v1);
+            }
           }
           sts128(pa, make_uint4(o[0], o[1], o[2], o[3]));
           sts128(pb, make_uint4(o[4], o[5], o[6], o[7]));
@@ -347,10 +370,9 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
       const int grp = h / (p.H / p.G);
       // per-head constants of this item (global loads issued before the epilogue below, used after it)
       float cs_v = 0.f, D_v = 0.f;
-      if (tid < P) {
-        cs_v = __fmul_rn(p.C_scale[grp], p.state_scale[h * P + tid]);
-        D_v = p.D == nullptr ? 0.f : (p.D_has_hdim ? p.D[h * P + tid] : p.D[h]);
-      }
+      if (tid < P) cs_v = __fmul_rn(p.C_scale[grp], p.state_scale[h * P + tid]);
+      if (dmode == 2 && tid < P) D_v = p.D[h * P + tid];
+      if (dmode == 1) D_v = p.D[h];
       const float Scb = p.cb_scale[grp];
       // CB rows of this thread: row block 0 and (C = 256) row block 1, at its quarter of a 64-token source block
       const int8_t* cb0 = p.cb + (((size_t)b * NC + c) * p.G + grp) * (size_t)C * C + (size_t)r * C + 16 * qt;
@@ -385,6 +407,10 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
         }
       }
       if (!worker_and(ok)) { failed = true; break; }  // s_dts, ratio complete (and the tables of the previous item no longer read)
+      if (dmode == 1 && tid >= kWorkers - 256) {  // D on the diagonal of a 16 x 16 block, fp16
+        const int i = tid - (kWorkers - 256);
+        sts_h(s_dvec + 2 * i, __float2half_rn((i >> 4) == (i & 15) ? D_v : 0.f));
+      }
       if (tid < C) {  // the row's own 16-token group, masked to k <= t
         const int t = tid, kq = t & ~15;
         const float dAt = lds_f(dAs + 4 * t);
@@ -441,7 +467,10 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
         // group table times the row factor below it (selected, not branched)
         const uint32_t wp = kq > t ? s_zero : (kq == g0 ? s_dg + 32 * t : s_tab + 2 * ((g0 >> 4) * C + kq));
         const uint32_t mult = kq < g0 ? rfu[mb] : 0x3C003C00u;  // half2(1, 1)
+        const uint32_t ap = (dmode == 1 && kq == g0) ? s_dvec + 32 * (t & 15) : s_zero;  // + D on the diagonal element
         const uint4 wa = lds128(wp), wb = lds128(wp + 16);
+        const uint4 aa = lds128(ap), ab = lds128(ap + 16);
+        const uint32_t av[8] = {aa.x, aa.y, aa.z, aa.w, ab.x, ab.y, ab.z, ab.w};
         const uint32_t wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
         const uint32_t cw[4] = {cq.x, cq.y, cq.z, cq.w};
         uint32_t hw[8];
@@ -449,8 +478,8 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
         for (int e4 = 0; e4 < 4; ++e4) {
           uint32_t h01, h23;
           s8x4_to_h2x2(cw[e4], h01, h23);
-          hw[2 * e4] = hmul2u(hmul2u(h01, wv[2 * e4]), mult);
-          hw[2 * e4 + 1] = hmul2u(hmul2u(h23, wv[2 * e4 + 1]), mult);
+          hw[2 * e4] = hfma2u(hmul2u(h01, wv[2 * e4]), mult, av[2 * e4]);
+          hw[2 * e4 + 1] = hfma2u(hmul2u(h23, wv[2 * e4 + 1]), mult, av[2 * e4 + 1]);
         }
         sts128(srow + (((2 * qt) ^ (r & 7)) << 4), make_uint4(hw[0], hw[1], hw[2], hw[3]));
         sts128(srow + (((2 * qt + 1) ^ (r & 7)) << 4), make_uint4(hw[4], hw[5], hw[6], hw[7]));
@@ -527,7 +556,7 @@ int run_chunk_scan_tc(const lq_ssd_problem* p, int* status, cudaStream_t st) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const size_t smem = 2 * (size_t)scantc::kStageBytes + 32768 + 2 * 8192 + 1024 + 64 + 64 + 512 + 512 + 80 + 16 + 1024;
+  const size_t smem = 2 * (size_t)scantc::kStageBytes + 32768 + 2 * 8192 + 1024 + 64 + 64 + 512 + 512 + 512 + 80 + 16 + 1024;
   const int grid = (int)(items < sms ? items : sms);
   cudaError_t e;
   if (p->x_dtype == LQ_F16) e = C == 256 ? launch_scan_tc<__half, 2>(grid, smem, st, tq, ts, tx, to, p, status, (int)items)
