@@ -464,22 +464,28 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
         const uint32_t srow = s_ring + slot * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
         const int kq = 64 * kb + 16 * qt;
         // weights of this 16-token group for this row: zeros above the diagonal, the row's own masked weights on it, the
-        // group table times the row factor below it (selected, not branched)
-        const uint32_t wp = kq > t ? s_zero : (kq == g0 ? s_dg + 32 * t : s_tab + 2 * ((g0 >> 4) * C + kq));
-        const uint32_t mult = kq < g0 ? rfu[mb] : 0x3C003C00u;  // half2(1, 1)
-        const uint32_t ap = (dmode == 1 && kq == g0) ? s_dvec + 32 * (t & 15) : s_zero;  // + D on the diagonal element
-        const uint4 wa = lds128(wp), wb = lds128(wp + 16);
-        const uint4 aa = lds128(ap), ab = lds128(ap + 16);
-        const uint32_t av[8] = {aa.x, aa.y, aa.z, aa.w, ab.x, ab.y, ab.z, ab.w};
-        const uint32_t wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
-        const uint32_t cw[4] = {cq.x, cq.y, cq.z, cq.w};
+        // group table times the row factor below it (selected, not branched); a warp whose 32 rows all lie above the
+        // diagonal of this group (about a quarter of all groups) only stores zeros
         uint32_t hw[8];
+        if (__all_sync(0xffffffffu, kq > t)) {
 #pragma unroll
-        for (int e4 = 0; e4 < 4; ++e4) {
-          uint32_t h01, h23;
-          s8x4_to_h2x2(cw[e4], h01, h23);
-          hw[2 * e4] = hfma2u(hmul2u(h01, wv[2 * e4]), mult, av[2 * e4]);
-          hw[2 * e4 + 1] = hfma2u(hmul2u(h23, wv[2 * e4 + 1]), mult, av[2 * e4 + 1]);
+          for (int e = 0; e < 8; ++e) hw[e] = 0u;
+        } else {
+          const uint32_t wp = kq > t ? s_zero : (kq == g0 ? s_dg + 32 * t : s_tab + 2 * ((g0 >> 4) * C + kq));
+          const uint32_t mult = kq < g0 ? rfu[mb] : 0x3C003C00u;  // half2(1, 1)
+          const uint32_t ap = (dmode == 1 && kq == g0) ? s_dvec + 32 * (t & 15) : s_zero;  // + D on the diagonal element
+          const uint4 wa = lds128(wp), wb = lds128(wp + 16);
+          const uint4 aa = lds128(ap), ab = lds128(ap + 16);
+          const uint32_t av[8] = {aa.x, aa.y, aa.z, aa.w, ab.x, ab.y, ab.z, ab.w};
+          const uint32_t wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+          const uint32_t cw[4] = {cq.x, cq.y, cq.z, cq.w};
+#pragma unroll
+          for (int e4 = 0; e4 < 4; ++e4) {
+            uint32_t h01, h23;
+            s8x4_to_h2x2(cw[e4], h01, h23);
+            hw[2 * e4] = hfma2u(hmul2u(h01, wv[2 * e4]), mult, av[2 * e4]);
+            hw[2 * e4 + 1] = hfma2u(hmul2u(h23, wv[2 * e4 + 1]), mult, av[2 * e4 + 1]);
+          }
         }
         sts128(srow + (((2 * qt) ^ (r & 7)) << 4), make_uint4(hw[0], hw[1], hw[2], hw[3]));
         sts128(srow + (((2 * qt + 1) ^ (r & 7)) << 4), make_uint4(hw[4], hw[5], hw[6], hw[7]));

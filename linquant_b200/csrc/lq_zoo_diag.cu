@@ -328,33 +328,97 @@ __global__ void __launch_bounds__(256) zoo_diag_amat_kernel(DiagArgs a) {
     __syncthreads();
   }
 
-  // diagonal blocks: 4 x 136 (i >= j) pairs, eight lanes per pair, four channels per lane and step (128-bit loads)
-  for (int pass = 0; pass < 17; ++pass) {
-    const int p = pass * 32 + (tid >> 3);
-    const int I = p / 136, rem = p % 136;
-    int i = (int)((sqrtf(8.f * rem + 1.f) - 1.f) * 0.5f);
-    while ((i + 1) * (i + 2) / 2 <= rem) ++i;
-    while (i * (i + 1) / 2 > rem) --i;
-    const int jj = rem - i * (i + 1) / 2;
-    const int ti = SUB * I + i, tj = SUB * I + jj;
-    const int l8 = tid & 7;
-    float sum = 0.f;
+  // diagonal blocks: A_ij = s_q s_k sum_n q^_in k^_jn exp(g_in - g_jn), i >= j inside a 16 x 16 block. The weight factors
+  // around the block's first row a: exp(g_in - a_n) exp(a_n - g_jn). The first factor is <= 1; the second is >= 1 and grows
+  // with the decay across at most 15 tokens, so per block the spread max_n (a_n - g_last,n) decides: up to 60 (a factor
+  // below 1.2e26, far inside fp32) the block is two sets of 16 scaled rows (one exp per row element, 16 x fewer) and a
+  // 16 x 16 x K fp32 product; beyond it (decays as strong as the g x 40 cases) the block takes one exp per (i, j, n).
+  float* s_qd = reinterpret_cast<float*>(s_ka + 48 * K);  // [16][LD] q^ exp(g_i - a), then [16][LD] k^ exp(a - g_j)
+  float* s_kd = s_qd + SUB * LD;
+  __shared__ int s_exact[C / SUB];
+  if (tid < C / SUB) s_exact[tid] = 0;
+  __syncthreads();
+  for (int i = tid; i < (C / SUB) * K; i += 256) {
+    const int I = i / K, n = i - I * K;
+    if (__fsub_rn(s_gc[(SUB * I) * LD + n], s_gc[(SUB * I + SUB - 1) * LD + n]) > 60.f) s_exact[I] = 1;
+  }
+  __syncthreads();
+  for (int I = 0; I < C / SUB; ++I) {
+    if (s_exact[I]) {  // 136 (i >= j) pairs, eight lanes per pair, four channels per lane and step (128-bit loads)
+      for (int pass = 0; pass < 5; ++pass) {
+        const int rem_raw = pass * 32 + (tid >> 3);
+        const bool valid = rem_raw < 136;  // the last pass has idle pairs: they compute a clamped pair and store nothing
+        const int rem = valid ? rem_raw : 135;
+        {
+          int i = (int)((sqrtf(8.f * rem + 1.f) - 1.f) * 0.5f);
+          while ((i + 1) * (i + 2) / 2 <= rem) ++i;
+          while (i * (i + 1) / 2 > rem) --i;
+          const int jj = rem - i * (i + 1) / 2;
+          const int ti = SUB * I + i, tj = SUB * I + jj;
+          const int l8 = tid & 7;
+          float sum = 0.f;
 #pragma unroll
-    for (int n4 = 0; n4 < K / 32; ++n4) {
-      const int n = 4 * l8 + 32 * n4;  // the eight lanes of a pair read 128 consecutive bytes of a gc row
-      const float4 gi = *reinterpret_cast<const float4*>(s_gc + ti * LD + n);
-      const float4 gj = *reinterpret_cast<const float4*>(s_gc + tj * LD + n);
-      const uint32_t qw = *reinterpret_cast<const uint32_t*>(s_qc + ti * K + n) ^ 0x80808080u;
-      const uint32_t kw = *reinterpret_cast<const uint32_t*>(s_kc + tj * K + n) ^ 0x80808080u;
-      sum = fmaf(__fmul_rn(s8_to_float<0>(qw), s8_to_float<0>(kw)), __expf(gi.x - gj.x), sum);
-      sum = fmaf(__fmul_rn(s8_to_float<1>(qw), s8_to_float<1>(kw)), __expf(gi.y - gj.y), sum);
-      sum = fmaf(__fmul_rn(s8_to_float<2>(qw), s8_to_float<2>(kw)), __expf(gi.z - gj.z), sum);
-      sum = fmaf(__fmul_rn(s8_to_float<3>(qw), s8_to_float<3>(kw)), __expf(gi.w - gj.w), sum);
+          for (int n4 = 0; n4 < K / 32; ++n4) {
+            const int n = 4 * l8 + 32 * n4;  // the eight lanes of a pair read 128 consecutive bytes of a gc row
+            const float4 gi = *reinterpret_cast<const float4*>(s_gc + ti * LD + n);
+            const float4 gj = *reinterpret_cast<const float4*>(s_gc + tj * LD + n);
+            const uint32_t qw = *reinterpret_cast<const uint32_t*>(s_qc + ti * K + n) ^ 0x80808080u;
+            const uint32_t kw = *reinterpret_cast<const uint32_t*>(s_kc + tj * K + n) ^ 0x80808080u;
+            sum = fmaf(__fmul_rn(s8_to_float<0>(qw), s8_to_float<0>(kw)), __expf(gi.x - gj.x), sum);
+            sum = fmaf(__fmul_rn(s8_to_float<1>(qw), s8_to_float<1>(kw)), __expf(gi.y - gj.y), sum);
+            sum = fmaf(__fmul_rn(s8_to_float<2>(qw), s8_to_float<2>(kw)), __expf(gi.z - gj.z), sum);
+            sum = fmaf(__fmul_rn(s8_to_float<3>(qw), s8_to_float<3>(kw)), __expf(gi.w - gj.w), sum);
+          }
+          sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+          if (l8 == 0 && valid) s_A[ti * 65 + tj] = __fmul_rn(sum, sqk);
+        }
+      }
+      __syncthreads();
+      continue;
     }
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-    if (l8 == 0) s_A[ti * 65 + tj] = __fmul_rn(sum, sqk);
+    // scaled rows: thread = (row of the block, 4-channel piece); 2 x 16 x K elements over 256 threads
+    for (int i = tid; i < SUB * (K / 4); i += 256) {
+      const int rr = i / (K / 4), n = 4 * (i - rr * (K / 4));
+      const int t = SUB * I + rr;
+      const float4 an = *reinterpret_cast<const float4*>(s_gc + (SUB * I) * LD + n);
+      const float4 gt = *reinterpret_cast<const float4*>(s_gc + t * LD + n);
+      const uint32_t qw = *reinterpret_cast<const uint32_t*>(s_qc + t * K + n) ^ 0x80808080u;
+      const uint32_t kw = *reinterpret_cast<const uint32_t*>(s_kc + t * K + n) ^ 0x80808080u;
+      *reinterpret_cast<float4*>(s_qd + rr * LD + n) =
+          make_float4(__fmul_rn(s8_to_float<0>(qw), __expf(gt.x - an.x)), __fmul_rn(s8_to_float<1>(qw), __expf(gt.y - an.y)),
+                      __fmul_rn(s8_to_float<2>(qw), __expf(gt.z - an.z)), __fmul_rn(s8_to_float<3>(qw), __expf(gt.w - an.w)));
+      *reinterpret_cast<float4*>(s_kd + rr * LD + n) =
+          make_float4(__fmul_rn(s8_to_float<0>(kw), __expf(an.x - gt.x)), __fmul_rn(s8_to_float<1>(kw), __expf(an.y - gt.y)),
+                      __fmul_rn(s8_to_float<2>(kw), __expf(an.z - gt.z)), __fmul_rn(s8_to_float<3>(kw), __expf(an.w - gt.w)));
+    }
+    __syncthreads();
+    {  // 16 x 16 x K product: eight lanes per (i, j) pair as above would leave half the block idle; here one (i, j)
+       // per thread pair-of-halves: thread = (i, j, half of K), two partial sums joined by one shuffle
+      const int pr = tid >> 1, hf = tid & 1;
+      const int i = pr >> 3, j2 = (pr & 7) * 2;  // this thread: row i, columns j2 and j2 + 1
+      const float* qr = s_qd + i * LD + hf * (K / 2);
+      const float* k0 = s_kd + j2 * LD + hf * (K / 2);
+      const float* k1 = k0 + LD;
+      float s0 = 0.f, s1 = 0.f;
+      if (j2 <= i) {
+#pragma unroll 4
+        for (int n = 0; n < K / 2; n += 4) {
+          const float4 qv = *reinterpret_cast<const float4*>(qr + n);
+          const float4 ka = *reinterpret_cast<const float4*>(k0 + n), kb = *reinterpret_cast<const float4*>(k1 + n);
+          s0 = fmaf(qv.x, ka.x, s0); s0 = fmaf(qv.y, ka.y, s0); s0 = fmaf(qv.z, ka.z, s0); s0 = fmaf(qv.w, ka.w, s0);
+          s1 = fmaf(qv.x, kb.x, s1); s1 = fmaf(qv.y, kb.y, s1); s1 = fmaf(qv.z, kb.z, s1); s1 = fmaf(qv.w, kb.w, s1);
+        }
+      }
+      s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
+      s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+      if (hf == 0 && j2 <= i) {
+        s_A[(SUB * I + i) * 65 + SUB * I + j2] = __fmul_rn(s0, sqk);
+        if (j2 + 1 <= i) s_A[(SUB * I + i) * 65 + SUB * I + j2 + 1] = __fmul_rn(s1, sqk);
+      }
+    }
+    __syncthreads();
   }
   __syncthreads();
   uint32_t* out = reinterpret_cast<uint32_t*>(a.amat + tile * (size_t)(C * C));
@@ -440,33 +504,91 @@ __global__ void __launch_bounds__(256) zoo_kda_wy_kernel(DiagArgs a) {
   for (int i = tid; i < C * 68; i += 256) s_G[i] = 0.f;
   __syncthreads();
 
-  // ---- diagonal blocks: 4 x 120 strictly-lower pairs, eight lanes per pair, exact per-channel weights
-  for (int pass = 0; pass < 15; ++pass) {
-    const int p = pass * 32 + (tid >> 3);
-    const int I = p / 120, rem = p % 120;
-    int i = (int)((sqrtf(8.f * rem + 1.f) + 1.f) * 0.5f);
-    while (i * (i + 1) / 2 <= rem) ++i;
-    while (i * (i - 1) / 2 > rem) --i;
-    const int jj = rem - i * (i - 1) / 2;
-    const int ti = SUB * I + i, tj = SUB * I + jj;
-    const int l8 = tid & 7;
-    float sum = 0.f;
-#pragma unroll
-    for (int n4 = 0; n4 < K / 32; ++n4) {
-      const int n = 4 * l8 + 32 * n4;  // the eight lanes of a pair read 128 consecutive bytes of each row
-      const float4 gi = *reinterpret_cast<const float4*>(s_gc + ti * LD + n), gj = *reinterpret_cast<const float4*>(s_gc + tj * LD + n);
-      const float4 xi = *reinterpret_cast<const float4*>(s_x + ti * LD + n), xj = *reinterpret_cast<const float4*>(s_x + tj * LD + n);
-      sum = fmaf(xi.x * xj.x, __expf(gi.x - gj.x), sum);
-      sum = fmaf(xi.y * xj.y, __expf(gi.y - gj.y), sum);
-      sum = fmaf(xi.z * xj.z, __expf(gi.z - gj.z), sum);
-      sum = fmaf(xi.w * xj.w, __expf(gi.w - gj.w), sum);
+  // ---- diagonal blocks (strictly lower pairs of each 16 x 16 block). As in the A matrix the per-channel weight
+  // exp(gc_in - gc_jn) factors around the block's first row a into exp(gc_in - a_n) (<= 1) and exp(a_n - gc_jn) (>= 1): two
+  // sets of 16 scaled rows (in the space of T, which is not needed yet) and a 16 x 16 x K fp32 product. A block whose
+  // decay spread max_n (a_n - gc_last,n) exceeds 60 keeps one exp per (i, j, n).
+  {
+    float* s_kq = s_T;             // [16][LD] k exp(gc_i - a)
+    float* s_kk = s_T + SUB * LD;  // [16][LD] k exp(a - gc_j)
+    __shared__ int s_exact[C / SUB];
+    if (tid < C / SUB) s_exact[tid] = 0;
+    __syncthreads();
+    for (int i = tid; i < (C / SUB) * K; i += 256) {
+      const int I = i / K, n = i - I * K;
+      if (__fsub_rn(s_gc[(SUB * I) * LD + n], s_gc[(SUB * I + SUB - 1) * LD + n]) > 60.f) s_exact[I] = 1;
     }
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-    if (l8 == 0) s_G[ti * 68 + tj] = s_bs[ti] * s_b1[tj] * sum;
+    __syncthreads();
+    for (int I = 0; I < C / SUB; ++I) {
+      if (s_exact[I]) {  // 120 strictly-lower pairs, eight lanes per pair
+        for (int pass = 0; pass < 4; ++pass) {
+          const int rem_raw = pass * 32 + (tid >> 3);
+          const bool valid = rem_raw < 120;  // idle pairs of the last pass compute a clamped pair and store nothing
+          const int rem = valid ? rem_raw : 119;
+          int i = (int)((sqrtf(8.f * rem + 1.f) + 1.f) * 0.5f);
+          while (i * (i + 1) / 2 <= rem) ++i;
+          while (i * (i - 1) / 2 > rem) --i;
+          const int jj = rem - i * (i - 1) / 2;
+          const int ti = SUB * I + i, tj = SUB * I + jj;
+          const int l8 = tid & 7;
+          float sum = 0.f;
+#pragma unroll
+          for (int n4 = 0; n4 < K / 32; ++n4) {
+            const int n = 4 * l8 + 32 * n4;  // the eight lanes of a pair read 128 consecutive bytes of each row
+            const float4 gi = *reinterpret_cast<const float4*>(s_gc + ti * LD + n), gj = *reinterpret_cast<const float4*>(s_gc + tj * LD + n);
+            const float4 xi = *reinterpret_cast<const float4*>(s_x + ti * LD + n), xj = *reinterpret_cast<const float4*>(s_x + tj * LD + n);
+            sum = fmaf(xi.x * xj.x, __expf(gi.x - gj.x), sum);
+            sum = fmaf(xi.y * xj.y, __expf(gi.y - gj.y), sum);
+            sum = fmaf(xi.z * xj.z, __expf(gi.z - gj.z), sum);
+            sum = fmaf(xi.w * xj.w, __expf(gi.w - gj.w), sum);
+          }
+          sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+          if (l8 == 0 && valid) s_G[ti * 68 + tj] = s_bs[ti] * s_b1[tj] * sum;
+        }
+        __syncthreads();
+        continue;
+      }
+      for (int i = tid; i < SUB * (K / 4); i += 256) {
+        const int rr = i / (K / 4), n = 4 * (i - rr * (K / 4));
+        const int t = SUB * I + rr;
+        const float4 an = *reinterpret_cast<const float4*>(s_gc + (SUB * I) * LD + n);
+        const float4 gt = *reinterpret_cast<const float4*>(s_gc + t * LD + n);
+        const float4 xv = *reinterpret_cast<const float4*>(s_x + t * LD + n);
+        *reinterpret_cast<float4*>(s_kq + rr * LD + n) = make_float4(__fmul_rn(xv.x, __expf(gt.x - an.x)), __fmul_rn(xv.y, __expf(gt.y - an.y)),
+                                                                     __fmul_rn(xv.z, __expf(gt.z - an.z)), __fmul_rn(xv.w, __expf(gt.w - an.w)));
+        *reinterpret_cast<float4*>(s_kk + rr * LD + n) = make_float4(__fmul_rn(xv.x, __expf(an.x - gt.x)), __fmul_rn(xv.y, __expf(an.y - gt.y)),
+                                                                     __fmul_rn(xv.z, __expf(an.z - gt.z)), __fmul_rn(xv.w, __expf(an.w - gt.w)));
+      }
+      __syncthreads();
+      {  // thread = (row i, columns j2 and j2 + 1, half of K); the two halves are joined by one shuffle
+        const int pr = tid >> 1, hf = tid & 1;
+        const int i = pr >> 3, j2 = (pr & 7) * 2;
+        const float* qr = s_kq + i * LD + hf * (K / 2);
+        const float* k0 = s_kk + j2 * LD + hf * (K / 2);
+        const float* k1 = k0 + LD;
+        float s0 = 0.f, s1 = 0.f;
+        if (j2 < i) {
+#pragma unroll 4
+          for (int n = 0; n < K / 2; n += 4) {
+            const float4 qv = *reinterpret_cast<const float4*>(qr + n);
+            const float4 ka = *reinterpret_cast<const float4*>(k0 + n), kb = *reinterpret_cast<const float4*>(k1 + n);
+            s0 = fmaf(qv.x, ka.x, s0); s0 = fmaf(qv.y, ka.y, s0); s0 = fmaf(qv.z, ka.z, s0); s0 = fmaf(qv.w, ka.w, s0);
+            s1 = fmaf(qv.x, kb.x, s1); s1 = fmaf(qv.y, kb.y, s1); s1 = fmaf(qv.z, kb.z, s1); s1 = fmaf(qv.w, kb.w, s1);
+          }
+        }
+        s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+        const int ti = SUB * I + i;
+        if (hf == 0 && j2 < i) {
+          s_G[ti * 68 + SUB * I + j2] = s_bs[ti] * s_b1[SUB * I + j2] * s0;
+          if (j2 + 1 < i) s_G[ti * 68 + SUB * I + j2 + 1] = s_bs[ti] * s_b1[SUB * I + j2 + 1] * s1;
+        }
+      }
+      __syncthreads();
+    }
   }
-  __syncthreads();
 
   // ---- off-diagonal blocks: block row I against tokens [0, 16 I), anchored at row 16 I
   for (int I = 1; I < C / SUB; ++I) {
@@ -592,7 +714,7 @@ static int run_diag_T(const lq_zoo_problem* p, const DiagArgs& a, bool delta, in
     return launch_big_smem(zoo_diag_rows_kernel<T, K, V, false>, "zoo_diag_rows_kernel", grid, smem, a, st);
   }
   if (stage == 1) {
-    const size_t smem = sizeof(float) * (64 * (K + 4) + 64 * 65 + 64) + (size_t)(64 * K * 2 + 16 * K + 48 * K);
+    const size_t smem = sizeof(float) * (64 * (K + 4) + 64 * 65 + 64 + 2 * 16 * (K + 4)) + (size_t)(64 * K * 2 + 16 * K + 48 * K);
     return launch_big_smem(zoo_diag_amat_kernel<T, K>, "zoo_diag_amat_kernel", grid, smem, a, st);
   }
   const size_t smem = sizeof(float) * (64 * ((K + 4) > (V + 8) ? (K + 4) : (V + 8)) + 64 * (K + 4) + 2 * 64 * 68 + 128);
