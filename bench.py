@@ -509,7 +509,7 @@ def _time_stages(fns, reps):
     return a.elapsed_time(b) / reps, {n: sum(x.elapsed_time(y) for x, y in p) / reps for n, p in ev.items()}
 
 
-def zoo_config(name, dev, world, rank, reps=10):
+def zoo_config(name, dev, world, rank, reps=10, batch=None):
     from linquant_b200 import _cabi, sharding
     from linquant_b200 import invariances as inv
     from linquant_b200.kernels.zoo import _common
@@ -517,7 +517,7 @@ def zoo_config(name, dev, world, rank, reps=10):
 
     syn, delta, diag, stages, path_bytes = ZOO[name]
     c = CONFIGS[syn]
-    B, T, H, K, V = c["B"], c["T"], c["H"], c["K"], c["V"]
+    B, T, H, K, V = batch or c["B"], c["T"], c["H"], c["K"], c["V"]
     sh = sharding.plan(B, H, world, rank)
     signs = inv.hadamard_signs(K, 0).to(dev)
     # scales (and D_QK) from four further seeded batches of one element, 1024 tokens each
@@ -745,7 +745,7 @@ def run_stages(args):
     if args.stages == "mamba2_layer_keyside":
         r = m2_keyside_config(dev, 1, 0)
     elif args.stages in ZOO:
-        r = zoo_config(args.stages, dev, 1, 0, reps=args.steps)
+        r = zoo_config(args.stages, dev, 1, 0, reps=args.steps, batch=args.zoo_batch)
     else:
         raise SystemExit(f"--stages: one of {sorted(ZOO) + ['mamba2_layer', 'mamba2_layer_keyside']}")
     print(json.dumps({"stages": args.stages, "total_us": round(1e3 * r["total_ms"], 1),
@@ -764,6 +764,7 @@ def main():
     ap.add_argument("--layers", type=int, default=M2["layers"], help="fewer layers: a reduced run for profiling, not a bench value")
     ap.add_argument("--batch", type=int, default=M2["B"], help="smaller batch: a reduced run for profiling, not a bench value")
     ap.add_argument("--seqlen", type=int, default=M2["L"], help="shorter sequences: a reduced run for profiling, not a bench value")
+    ap.add_argument("--zoo-batch", type=int, default=None, help="with --stages: fewer batch elements of a zoo configuration (profiling)")
     ap.add_argument("--kernels-only", action="store_true",
                     help="device-resident loop and per-kernel times only (no host-buffer leg, no side records, no CPU baseline)")
     ap.add_argument("--stages", default=None, metavar="CONFIG",

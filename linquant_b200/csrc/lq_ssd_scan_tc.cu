@@ -12,10 +12,11 @@
 //   MMA warp          state read of item i as soon as its tiles land (tcgen05.mma.kind::i8, M = 128, N = 64), then the causal
 //                     product tile by tile (kind::f16, A = decay-masked matrix tile from the ring, B = the x tile in its
 //                     natural channel-contiguous layout); commits free the ring slots and publish the accumulators
-//   512 worker threads  per item: the epilogue of the PREVIOUS item (both accumulators from tensor memory, D x residual,
-//                     fp16 row written over the x row), then this item's weight tables, the fp16 rounding of a bf16 x tile
-//                     in place, and the six (two) tiles of the decay-masked matrix M, one 16-token group of one row per
-//                     thread and tile
+//   512 worker threads  per item: the epilogue of the PREVIOUS item (both accumulators from tensor memory, fp16 row written
+//                     over the x row, one arrival per warp on the stage's out_ready barrier; placing it after this item's
+//                     tables instead measured 8 % slower), then the fp16 rounding of a bf16 x tile in place, this
+//                     item's weight tables, and the six (two) tiles of the decay-masked matrix M into a ring of three
+//                     slots, one 16-token group of one row per thread and tile
 //
 // so the tensor core works on item i while the workers finish item i-1 and build item i, and the loads of item i+1 are
 // in flight. Decay weights as fp16 tables: for source tokens before the row's 16-token group  S_cb dt_k exp(dA[16 g] -
@@ -90,6 +91,7 @@ __device__ __forceinline__ float exp_decay(float x) {  // ex2.approx.ftz(x log2 
   return y;
 }
 constexpr int kWorkers = 512;
+constexpr int kRing = 3;  // slots of the M-tile ring: the round trip through the tensor core takes longer than building one tile
 // Barrier of the worker threads that also ANDs a predicate: every decision to leave the pipeline is taken here, so
 // all workers take it together (a bounded wait may run out in some warps and not in others).
 __device__ __forceinline__ bool worker_and(bool ok) {
@@ -156,8 +158,8 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
   const int NC = p.L / C;
   extern __shared__ uint8_t smem_dyn[];
   const uint32_t s_stage0 = (smem_u32(smem_dyn) + 1023u) & ~1023u;  // two input stages
-  const uint32_t s_ring = s_stage0 + 2 * kStageBytes;             // two M-tile slots of 16 KB
-  const uint32_t s_tab = s_ring + 32768;                          // fp16 [C/16][C] below-group weights (8 KB at C = 256)
+  const uint32_t s_ring = s_stage0 + 2 * kStageBytes;             // kRing M-tile slots of 16 KB
+  const uint32_t s_tab = s_ring + kRing * 16384;                       // fp16 [C/16][C] below-group weights (8 KB at C = 256)
   const uint32_t s_dg = s_tab + 8192;                             // fp16 [C][16] weights of the row's own group, masked (8 KB)
   const uint32_t s_dts = s_dg + 8192;                             // f32 [C] S_cb * dt
   const uint32_t s_ratio = s_dts + 1024;                          // f32 [16] exp(dA[16 g] - dA[16 (g-1)])
@@ -165,10 +167,10 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
   const uint32_t s_dvec = s_zero + 64;                            // fp16 [16][16]: D on the diagonal (a per-head D joins M there)
   const uint32_t s_cs = s_dvec + 512;                             // f32 [2][64] s_C * state scale, per stage
   const uint32_t s_D = s_cs + 512;                                // f32 [2][64]
-  const uint32_t s_bars = s_D + 512;                              // full_in[2] out_ready[2] ring_full[2] ring_empty[2] acc_full[2]
-  const uint32_t s_tbase = s_bars + 80;
-  auto bar = [&](int which, int idx) { return s_bars + 8u * (2 * which + idx); };
-  enum { FULL_IN = 0, OUT_READY = 1, RING_FULL = 2, RING_EMPTY = 3, ACC_FULL = 4 };
+  const uint32_t s_bars = s_D + 512;                              // full_in[2] out_ready[2] acc_full[2] ring_full[3] ring_empty[3]
+  const uint32_t s_tbase = s_bars + 96;
+  enum { FULL_IN = 0, OUT_READY = 2, ACC_FULL = 4, RING_FULL = 6, RING_EMPTY = 6 + kRing, kBars = 6 + 2 * kRing };
+  auto bar = [&](int which, int idx) { return s_bars + 8u * (which + idx); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   constexpr int kProducerWarp = kWorkers / 32, kMmaWarp = kProducerWarp + 1;
@@ -179,8 +181,10 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
 
   if (tid == 0) {
 #pragma unroll
-    for (int i = 0; i < 10; ++i)  // ring_full takes one arrival per worker warp, the others a single one
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(s_bars + 8u * i), "r"((i == 4 || i == 5) ? (uint32_t)(kWorkers / 32) : 1u));
+    for (int i = 0; i < kBars; ++i) {  // out_ready and ring_full take one arrival per worker warp, the others a single one
+      const bool per_warp = (i >= OUT_READY && i < OUT_READY + 2) || (i >= RING_FULL && i < RING_FULL + kRing);
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(s_bars + 8u * i), "r"(per_warp ? (uint32_t)(kWorkers / 32) : 1u));
+    }
     sts128(s_zero, make_uint4(0u, 0u, 0u, 0u));
     sts128(s_zero + 16, make_uint4(0u, 0u, 0u, 0u));
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -247,7 +251,8 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
     // B operand MN-major (the x tile as it lies in memory). Both operands are fp16: kind::f16 does not take an fp16 A with
     // a bf16 B (the instruction is rejected), so a bf16 x tile is rounded to fp16 in shared memory by the workers first.
     const uint32_t idesc_c = idesc_f16(128, P) | (1u << 16);
-    int g = 0;  // running tile counter: ring slot g & 1
+    int slot = 0;       // ring slot of the next tile
+    uint32_t rph = 0u;  // parity of that slot's use count
     for (int j = 0; j < n_mine && !failed; ++j) {
       const int s = j & 1;
       const uint32_t st = s_stage0 + s * kStageBytes;
@@ -265,9 +270,10 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
       }
       __syncwarp();
 #pragma unroll
-      for (int ti = 0; ti < NT; ++ti, ++g) {
-        const int mb = ti < 2 ? 0 : 1, kb = ti < 2 ? ti : ti - 2, slot = g & 1;
-        if (!warp_wait(bar(RING_FULL, slot), (uint32_t)((g >> 1) & 1))) { failed = true; break; }
+      for (int ti = 0; ti < NT; ++ti) {
+        const int mb = ti < 2 ? 0 : 1, kb = ti < 2 ? ti : ti - 2;
+        if (NT % kRing == 0) { slot = ti % kRing; rph = (uint32_t)((ti / kRing) & 1); }  // whole laps per item: known at compile time
+        if (!warp_wait(bar(RING_FULL, slot), rph)) { failed = true; break; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         if (lane == 0) {
           const uint64_t da = desc_kmajor_sw128(s_ring + slot * 16384);
@@ -278,22 +284,29 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
           if (ti == NT - 1) umma_commit(bar(ACC_FULL, s));
         }
         __syncwarp();
+        if (++slot == kRing) { slot = 0; rph ^= 1u; }
       }
     }
     if (failed && lane == 0 && status != nullptr) atomicExch(status, 1);
   } else {
     // ============================================================ workers (512 threads)
-    // M tiles: thread = (row r of the 128-row block, quarter qt of the tile's 64 source tokens)
+    // M tiles: thread = (row r of the 128-row block, quarter qt of the tile's 64 source tokens). The causal mask leaves a
+    // warp (32 rows, one quarter) between two and six of the six tiles to build; evening that out (mirrored shares in the
+    // last two tiles, or one warp of every row quarter per scheduler) measured no faster.
     const int r = tid & 127, qt = tid >> 7;
     // epilogue: warp w reads TMEM lanes 32 (w & 3) ..; the four warps of a lane quadrant split (row block, column half)
     const int q4 = warp & 3, sel = warp >> 2;
     const int e_mb = MB == 2 ? (sel & 1) : 0, e_ch0 = MB == 2 ? 2 * (sel >> 1) : sel;  // first 16-channel chunk (of 2, or of 1)
     constexpr int E_NCH = MB == 2 ? 2 : 1;
-    int g = 0;  // running tile counter, as in the MMA issuer
+    constexpr int E_STEP = 1;  // chunks loaded per tcgen05.wait::ld; both at once costs registers the tile loop needs
+    int slot = 0, g = 0;  // ring slot of the next tile and the running tile counter, as in the MMA issuer
+    uint32_t rph = 0u;
     ItemWalk w;
     w.init(blockIdx.x, gridDim.x, p.H, NC);
 
-    // returns false (to every worker alike) when a wait ran out
+    // The epilogue of item j: every warp reads its 32 rows of both accumulators and posts its own arrival on the stage's
+    // out_ready barrier (no block barrier). Returns the warp's verdict on its waits; a warp whose wait ran out stores and
+    // posts nothing, and the decision to leave is taken by all workers together at the next block barrier.
     auto epilogue = [&](int j, bool ok_so_far) -> bool {
       const int s = j & 1;
       const bool ok = warp_wait(bar(ACC_FULL, s), (uint32_t)((j >> 1) & 1)) && ok_so_far;
@@ -301,65 +314,68 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
       const uint32_t st = s_stage0 + s * kStageBytes;
       const uint32_t tacc_i = tbase + 256 * s, tacc_f = tacc_i + 64 * MB;
       const int t = 128 * e_mb + 32 * q4 + lane;
-      const float ga = exp_decay(lds_f(st + kOffDa + 4 * t));
       const uint32_t xrow = st + t * 128;
       const uint32_t lane_addr = (uint32_t)(32 * q4) << 16;
       if (ok) {
+        const float ga = exp_decay(lds_f(st + kOffDa + 4 * t));
 #pragma unroll
-        for (int cc = 0; cc < E_NCH; ++cc) {
+        for (int c0 = 0; c0 < E_NCH; c0 += E_STEP) {
+        uint32_t ri[E_NCH][16], rf[E_NCH][16];  // E_STEP chunks of 16 channels are loaded per wait
+#pragma unroll
+        for (int cc = c0; cc < c0 + E_STEP; ++cc) {
+          tmem_ld16(tacc_i + lane_addr + 64 * e_mb + 16 * (e_ch0 + cc), ri[cc]);
+          tmem_ld16(tacc_f + lane_addr + 64 * e_mb + 16 * (e_ch0 + cc), rf[cc]);
+        }
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+        for (int cc = c0; cc < c0 + E_STEP; ++cc) {
           const int ch = e_ch0 + cc, col0 = 16 * ch;
-          uint32_t ri[16], rf[16];
-          tmem_ld16(tacc_i + lane_addr + 64 * e_mb + col0, ri);
-          tmem_ld16(tacc_f + lane_addr + 64 * e_mb + col0, rf);
           const uint32_t pa = xrow + (((2 * ch) ^ (t & 7)) << 4), pb = xrow + (((2 * ch + 1) ^ (t & 7)) << 4);
-          float csv[16];
-#pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4) {
-            const float4 a = lds_f4(s_cs + 256 * s + 4 * (col0 + 4 * v4));
-            csv[4 * v4] = a.x; csv[4 * v4 + 1] = a.y; csv[4 * v4 + 2] = a.z; csv[4 * v4 + 3] = a.w;
-          }
           uint32_t o[8];
           if (dmode == 2) {
             const uint4 xa = lds128(pa), xb = lds128(pb);
-            float Dv[16];
-#pragma unroll
-            for (int v4 = 0; v4 < 4; ++v4) {
-              const float4 d = lds_f4(s_D + 256 * s + 4 * (col0 + 4 * v4));
-              Dv[4 * v4] = d.x; Dv[4 * v4 + 1] = d.y; Dv[4 * v4 + 2] = d.z; Dv[4 * v4 + 3] = d.w;
-            }
-            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
             float xv[16];
             Act<__half>::unpack8(xa, *reinterpret_cast<float (*)[8]>(&xv[0]));
             Act<__half>::unpack8(xb, *reinterpret_cast<float (*)[8]>(&xv[8]));
 #pragma unroll
-            for (int e2 = 0; e2 < 8; ++e2) {
-              float v[2];
+            for (int v4 = 0; v4 < 4; ++v4) {
+              const float4 cs = lds_f4(s_cs + 256 * s + 4 * (col0 + 4 * v4)), d = lds_f4(s_D + 256 * s + 4 * (col0 + 4 * v4));
+              const float csv[4] = {cs.x, cs.y, cs.z, cs.w}, Dv[4] = {d.x, d.y, d.z, d.w};
+              float v[4];
 #pragma unroll
-              for (int u = 0; u < 2; ++u) {
-                const int e = 2 * e2 + u;
-                const float sread = __fmul_rn(__fmul_rn((float)(int)ri[e], csv[e]), ga);
-                v[u] = fmaf(xv[e], Dv[e], __fadd_rn(sread, __uint_as_float(rf[e])));
+              for (int u = 0; u < 4; ++u) {
+                const int e = 4 * v4 + u;
+                const float sread = __fmul_rn(__fmul_rn((float)(int)ri[cc][e], csv[u]), ga);
+                v[u] = fmaf(xv[e], Dv[u], __fadd_rn(sread, __uint_as_float(rf[cc][e])));
               }
-              o[e2] = Act<__half>::pack2(v[0], v[1]);
+              o[2 * v4] = Act<__half>::pack2(v[0], v[1]);
+              o[2 * v4 + 1] = Act<__half>::pack2(v[2], v[3]);
             }
           } else {
-            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
-            for (int e2 = 0; e2 < 8; ++e2) {
-              const float v0 = fmaf(__fmul_rn((float)(int)ri[2 * e2], csv[2 * e2]), ga, __uint_as_float(rf[2 * e2]));
-              const float v1 = fmaf(__fmul_rn((float)(int)ri[2 * e2 + 1], csv[2 * e2 + 1]), ga, __uint_as_float(rf[2 * e2 + 1]));
-              o[e2] = Act<__half>::pack2(v0, v1);
+            for (int v4 = 0; v4 < 4; ++v4) {
+              const float4 cs = lds_f4(s_cs + 256 * s + 4 * (col0 + 4 * v4));
+              const float csv[4] = {cs.x, cs.y, cs.z, cs.w};
+              float v[4];
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int e = 4 * v4 + u;
+                v[u] = fmaf(__fmul_rn((float)(int)ri[cc][e], csv[u]), ga, __uint_as_float(rf[cc][e]));
+              }
+              o[2 * v4] = Act<__half>::pack2(v[0], v[1]);
+              o[2 * v4 + 1] = Act<__half>::pack2(v[2], v[3]);
             }
           }
           sts128(pa, make_uint4(o[0], o[1], o[2], o[3]));
           sts128(pb, make_uint4(o[4], o[5], o[6], o[7]));
         }
+        }
       }
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the output tile -> visible to the TMA store
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the output rows -> visible to the TMA store
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");  // accumulator reads done before the stage is reused
-      const bool all_ok = worker_and(ok);
-      if (all_ok && tid == 0) mbar_arrive(bar(OUT_READY, s));
-      return all_ok;
+      __syncwarp();
+      if (ok && lane == 0) mbar_arrive(bar(OUT_READY, s));
+      return ok;
     };
 
     uint4 nxt[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
@@ -378,16 +394,16 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
       const int8_t* cb0 = p.cb + (((size_t)b * NC + c) * p.G + grp) * (size_t)C * C + (size_t)r * C + 16 * qt;
       auto fetch = [&](int ti) {  // ti is a compile-time constant at every call; two tiles are kept in flight
         const int mb = ti < 2 ? 0 : 1, kb = ti < 2 ? ti : ti - 2;
-        if (64 * kb + 16 * qt <= 128 * mb + r) nxt[ti & 1] = __ldg(reinterpret_cast<const uint4*>(cb0 + (size_t)mb * 128 * C + 64 * kb));
+        if (64 * kb + 16 * qt <= 128 * mb + r) nxt[ti & 1] = __ldg(reinterpret_cast<const uint4*>(cb0 + mb * 128 * C + 64 * kb));
       };
       fetch(0);
       fetch(1);
-      if (j >= 1 && !epilogue(j - 1, ok)) { failed = true; break; }
+      if (j >= 1) ok = epilogue(j - 1, ok);
       if (tid < P) {
         sts_f(s_cs + 256 * s + 4 * tid, cs_v);
         sts_f(s_D + 256 * s + 4 * tid, D_v);
       }
-      ok = warp_wait(bar(FULL_IN, s), (uint32_t)((j >> 1) & 1));
+      ok = warp_wait(bar(FULL_IN, s), (uint32_t)((j >> 1) & 1)) && ok;  // (the epilogue above returned the warp's verdict so far)
       const uint32_t st = s_stage0 + s * kStageBytes;
       const uint32_t dAs = st + kOffDa;
       if (tid < C) sts_f(s_dts + 4 * tid, __fmul_rn(Scb, lds_f(st + kOffDt + 4 * tid)));
@@ -411,30 +427,34 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
         const int i = tid - (kWorkers - 256);
         sts_h(s_dvec + 2 * i, __float2half_rn((i >> 4) == (i & 15) ? D_v : 0.f));
       }
-      if (tid < C) {  // the row's own 16-token group, masked to k <= t
-        const int t = tid, kq = t & ~15;
+      // Two threads per token (C = 256) share its two table rows evenly. The row's own 16-token group, masked to k <= t:
+      // eight weights each. The below-group weights of the token as a source, for every later group, as a running product
+      // over g: the first thread takes the first half of the groups, the second starts from its own exponential.
+      for (int i = tid; i < 2 * C; i += kWorkers) {
+        const int t = i >> 1, hf = i & 1, kq = t & ~15;
         const float dAt = lds_f(dAs + 4 * t);
-        uint32_t hw[8];
+        {
+          uint32_t hw[4];
 #pragma unroll
-        for (int v4 = 0; v4 < 4; ++v4) {
-          const float4 d = lds_f4(dAs + 4 * (kq + 4 * v4)), ws = lds_f4(s_dts + 4 * (kq + 4 * v4));
-          const int k = kq + 4 * v4;
-          const float v0 = (k <= t) ? __fmul_rn(exp_decay(__fsub_rn(dAt, d.x)), ws.x) : 0.f;
-          const float v1 = (k + 1 <= t) ? __fmul_rn(exp_decay(__fsub_rn(dAt, d.y)), ws.y) : 0.f;
-          const float v2 = (k + 2 <= t) ? __fmul_rn(exp_decay(__fsub_rn(dAt, d.z)), ws.z) : 0.f;
-          const float v3 = (k + 3 <= t) ? __fmul_rn(exp_decay(__fsub_rn(dAt, d.w)), ws.w) : 0.f;
-          hw[2 * v4] = Act<__half>::pack2(v0, v1);
-          hw[2 * v4 + 1] = Act<__half>::pack2(v2, v3);
+          for (int v4 = 0; v4 < 2; ++v4) {
+            const int k = kq + 8 * hf + 4 * v4;
+            const float4 d = lds_f4(dAs + 4 * k), ws = lds_f4(s_dts + 4 * k);
+            const float v0 = (k <= t) ? __fmul_rn(exp_decay(__fsub_rn(dAt, d.x)), ws.x) : 0.f;
+            const float v1 = (k + 1 <= t) ? __fmul_rn(exp_decay(__fsub_rn(dAt, d.y)), ws.y) : 0.f;
+            const float v2 = (k + 2 <= t) ? __fmul_rn(exp_decay(__fsub_rn(dAt, d.z)), ws.z) : 0.f;
+            const float v3 = (k + 3 <= t) ? __fmul_rn(exp_decay(__fsub_rn(dAt, d.w)), ws.w) : 0.f;
+            hw[2 * v4] = Act<__half>::pack2(v0, v1);
+            hw[2 * v4 + 1] = Act<__half>::pack2(v2, v3);
+          }
+          sts128(s_dg + 32 * t + 16 * hf, make_uint4(hw[0], hw[1], hw[2], hw[3]));
         }
-        sts128(s_dg + 32 * t, make_uint4(hw[0], hw[1], hw[2], hw[3]));
-        sts128(s_dg + 32 * t + 16, make_uint4(hw[4], hw[5], hw[6], hw[7]));
-      } else if (tid < 2 * C) {  // below-group weights of source token k for every later group: a running product over g
-        const int k = tid - C, g0 = (k >> 4) + 1;
-        if (g0 < (C >> 4)) {
-          float v = __fmul_rn(exp_decay(__fsub_rn(lds_f(dAs + 64 * g0), lds_f(dAs + 4 * k))), lds_f(s_dts + 4 * k));
-          uint32_t a = s_tab + 2 * (g0 * C + k);
+        const int g0 = (t >> 4) + 1, n = (C >> 4) - g0, n0 = (n + 1) >> 1;  // groups g0 .. C/16 - 1 read this token from below
+        const int gs = hf ? g0 + n0 : g0, ge = hf ? (C >> 4) : g0 + n0;
+        if (gs < ge) {
+          float v = __fmul_rn(exp_decay(__fsub_rn(lds_f(dAs + 64 * gs), dAt)), lds_f(s_dts + 4 * t));
+          uint32_t a = s_tab + 2 * (gs * C + t);
           sts_h(a, __float2half_rn(v));
-          for (int gq = g0 + 1; gq < (C >> 4); ++gq) {
+          for (int gq = gs + 1; gq < ge; ++gq) {
             v = __fmul_rn(v, lds_f(s_ratio + 4 * gq));
             a += 2 * C;
             sts_h(a, __float2half_rn(v));
@@ -452,15 +472,16 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
       worker_and(true);  // tables complete
       // ---- the tiles of M: (row block mb, source block kb); block 0 takes source blocks 0..1, block 1 takes 0..3.
       // No block barrier here: each warp posts its share of a tile on the slot's mbarrier (one arrival per warp), and a
-      // slot is rewritten only after the product that read it has completed, so a warp runs at most two tiles ahead. A
+      // slot is rewritten only after the product that read it has completed, so a warp runs at most kRing tiles ahead. A
       // wait that runs out is remembered in `ok` and acted on by all workers together at the next item's barrier.
 #pragma unroll
       for (int ti = 0; ti < NT; ++ti, ++g) {
-        const int mb = ti < 2 ? 0 : 1, kb = ti < 2 ? ti : ti - 2, slot = g & 1;
+        const int mb = ti < 2 ? 0 : 1, kb = ti < 2 ? ti : ti - 2;
+        if (NT % kRing == 0) { slot = ti % kRing; rph = (uint32_t)((ti / kRing) & 1); }
         const int t = 128 * mb + r, g0 = t & ~15;
         const uint4 cq = nxt[ti & 1];
         if (ti + 2 < NT) fetch(ti + 2);
-        if (g >= 2) ok = warp_wait(bar(RING_EMPTY, slot), (uint32_t)(((g >> 1) - 1) & 1)) && ok;
+        if (g >= kRing) ok = warp_wait(bar(RING_EMPTY, slot), rph ^ 1u) && ok;
         const uint32_t srow = s_ring + slot * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
         const int kq = 64 * kb + 16 * qt;
         // weights of this 16-token group for this row: zeros above the diagonal, the row's own masked weights on it, the
@@ -492,10 +513,11 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(RING_FULL, slot));
+        if (++slot == kRing) { slot = 0; rph ^= 1u; }
       }
     }
     if (!failed && n_mine > 0 && !epilogue(n_mine - 1, ok)) failed = true;
-    if (failed && tid == 0 && status != nullptr) atomicExch(status, 1);
+    if (failed && lane == 0 && status != nullptr) atomicExch(status, 1);
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
@@ -562,7 +584,7 @@ int run_chunk_scan_tc(const lq_ssd_problem* p, int* status, cudaStream_t st) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const size_t smem = 2 * (size_t)scantc::kStageBytes + 32768 + 2 * 8192 + 1024 + 64 + 64 + 512 + 512 + 512 + 80 + 16 + 1024;
+  const size_t smem = 2 * (size_t)scantc::kStageBytes + scantc::kRing * 16384 + 2 * 8192 + 1024 + 64 + 64 + 512 + 512 + 512 + 96 + 16 + 1024;
   const int grid = (int)(items < sms ? items : sms);
   cudaError_t e;
   if (p->x_dtype == LQ_F16) e = C == 256 ? launch_scan_tc<__half, 2>(grid, smem, st, tq, ts, tx, to, p, status, (int)items)
