@@ -40,10 +40,11 @@ M2 = dict(layers=64, B=8, L=16384, H=80, P=64, N=128, G=1, C=256)
 WORKLOAD = ("mamba2_2.7b_ssd_stack 64 layers x (B=8 L=16384 H=80 P=64 N=128 G=1 chunk=256) bf16 x/B/C, 1% heavy channels x20, "
             "INT8 operands + INT8 states, value-side absorption")
 
-# DRAM bytes (read + write) per launch of the Mamba-2 layer kernels from an ncu capture (dram__bytes_read.sum +
-# dram__bytes_write.sum) of one layer at B=2, scaled by the batch ratio (traffic of these kernels grows in proportion
-# to the (batch, chunk, head) items). None = not captured for the kernels of this build.
-NCU_DRAM_BYTES_PER_LAUNCH_B2 = {"chunk_scan": None, "chunk_state": None}
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per head-token of the two largest Mamba-2 layer kernels, from
+# one ncu capture of each at B=2, L=8192 (1 310 720 head-tokens per launch: 354.78 MB and 206.56 MB). The traffic of these
+# kernels grows in proportion to the (batch, chunk, head) items they walk, so a launch of the bench moves this figure
+# times its head-tokens.
+NCU_DRAM_BYTES_PER_HEAD_TOKEN = {"chunk_scan": 354.78e6 / 1310720, "chunk_state": 206.56e6 / 1310720}
 
 
 def measured_peak():
@@ -404,7 +405,7 @@ def run_ours(args):
     dom = max(per_layer_us, key=per_layer_us.get)
     achieved = ab[dom] * ht_rank / (per_layer_us[dom] * 1e-6) / 1e9
     path_gbs = ab["path"] * ht_rank * n_layers / (ms / args.steps * 1e-3) / 1e9
-    traffic = NCU_DRAM_BYTES_PER_LAUNCH_B2.get(dom)
+    traffic = NCU_DRAM_BYTES_PER_HEAD_TOKEN.get(dom)
     kernels = {}
     for k, us in per_layer_us.items():
         rec = {"us_per_layer": round(us, 1), "hbm_frac": round(ab[k] * ht_rank / (us * 1e-6) / 1e9 / peak, 3)}
@@ -426,7 +427,7 @@ def run_ours(args):
                 "host_buffers": "pinned ring of 2 layer inputs and 2 layer outputs per rank"},
         "gpu_launches": 7 * n_layers * args.steps,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": peak_kind, "traffic": None if traffic is None else traffic * len(bids) / 2,
+                     "peak_kind": peak_kind, "traffic": None if traffic is None else traffic * ht_rank,
                      "algorithmic_bytes": ab[dom] * ht_rank, "kernels": kernels,
                      "stage_sum_ms_per_step": round(sum(stage_ms.values()), 3),
                      "path_achieved": path_gbs, "path_frac": path_gbs / peak,

@@ -266,3 +266,46 @@ def test_config4_layer_slice_every_sub_op_and_combined():
     print("\nconfiguration 4 layer slice: fraction of codes off by one step "
           + ", ".join(f"{n} {v:.2e}" for n, v in fr.items()) + "; output rel-L2 " + ", ".join(f"{n} {v:.2e}" for n, v in errs.items()))
     assert all(e <= 2e-3 for e in errs.values()), errs
+
+
+@pytest.mark.gpu
+def test_config4_full_size_layer_properties():
+    """One layer at the full size of configuration 4 (B=8, L=16384, H=80, P=64, N=128, chunk 256, bf16), where the CPU
+    restatement would take hours: properties that do not depend on the size instead. (i) the forward is deterministic;
+    (ii) a batch element evaluated alone equals its rows of the full call bit for bit (no exchange across the batch);
+    (iii) the sequence evaluated as four chained segments, the INT32 carry handed from one to the next, equals the
+    single call bit for bit; (iv) no device-side wait ran out. The persistent chunk scan walks 40 960 items here."""
+    from linquant_b200 import check_status
+    from linquant_b200.kernels.mamba2 import ssd_combined as sc
+    from linquant_b200.kernels.mamba2.calibration import SsdObservers
+    from linquant_b200.seqpar import ssd_segmented_on_one_device
+
+    B, L, H, P, G, N, C = 8, 16384, 80, 64, 1, 128, 256
+    obs = SsdObservers()
+    for s in (601, 602):
+        k = mamba2_layer_case(1, 1024, H, P, G, N, C, s)
+        obs.observe(k["x"], k["dt_raw"], k["A_log"], k["Bm"], k["Cm"], C)
+    S = {n: (v.to(DEV) if torch.is_tensor(v) else v) for n, v in obs.scales().items()}
+    g = torch.Generator(device=DEV).manual_seed(600)
+    x = torch.randn(B, L, H, P, generator=g, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+    x[..., 7] *= 20.0
+    qB = torch.randint(-127, 128, (B, L, G, N), generator=g, device=DEV, dtype=torch.int32).to(torch.int8)
+    qC = torch.randint(-127, 128, (B, L, G, N), generator=g, device=DEV, dtype=torch.int32).to(torch.int8)
+    dt_raw = torch.randn(B, L, H, generator=g, device=DEV) * 0.5 - 2.0
+    A_log = torch.rand(H, generator=g, device=DEV) * math.log(16.0)
+    D = torch.randn(H, generator=g, device=DEV)
+    kw = dict(dt_softplus=True, static_state_scale=S["state_scale"], static_cb_scale=S["cb_scale"], alpha_hp=S["alpha_hp"],
+              bscale_g=S["B_scale"])
+
+    def fwd(sl=slice(None)):
+        o, _ = sc._quant_mamba_chunk_scan_combined_fwd(x[sl], dt_raw[sl], 1.0, A_log, 1.0, qB[sl], S["B_scale"], qC[sl], S["C_scale"],
+                                                       C, D, 1.0, **kw)
+        return o
+
+    full = fwd()
+    assert full.shape == (B, L, H, P) and bool(torch.isfinite(full.float()).all())
+    assert torch.equal(fwd(), full), "two runs of the same call differ"
+    assert torch.equal(fwd(slice(5, 6)), full[5:6]), "a batch element alone differs from its rows of the full call"
+    seg = ssd_segmented_on_one_device(4, x, dt_raw, 1.0, A_log, 1.0, qB, S["B_scale"], qC, S["C_scale"], C, D, 1.0, **kw)
+    assert torch.equal(seg, full), "four chained segments differ from the single call"
+    check_status(DEV)
