@@ -99,67 +99,70 @@ __global__ void __launch_bounds__(256) zoo_prologue_delta_kernel(DeltaPrepArgs d
   }
   __syncthreads();
 
-  const int mt = warp & 3, nh = warp >> 2;
-  // ---- Gram matrix (strictly lower triangle)
-  {
+  // Work split of the three triangular products. Row tile mt (16 tokens) of G, W and U contracts over 2 mt + 2 steps
+  // of eight tokens, so the cost grows 1 : 2 : 3 : 4 with mt: every warp takes the row tiles pr and 3 - pr (five steps on
+  // average instead of up to eight) and one quarter of the columns.
+  const int pr = warp & 1, qd = warp >> 1;
+  // ---- Gram matrix (strictly lower triangle): 8-column tiles nt <= 2 mt + 1 of row tile mt, ten per pair of row tiles,
+  // dealt round-robin to the pair's four warps. Tiles above the diagonal blocks are never read and stay unwritten.
+  for (int u = qd; u < 10; u += 4) {
+    const int lo = 2 * pr + 2;  // tiles of the lighter row tile of the pair
+    const int mt = u < lo ? pr : 3 - pr, nt = u < lo ? u : u - lo;
     const int ia = 16 * mt + g, ib = ia + 8;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int kk = 0; kk < K / 8; ++kk) {
+      const int c0 = 8 * kk + j;
+      mma_tf32(acc, __float_as_uint(s_kf[ia * LDK + c0]), __float_as_uint(s_kf[ib * LDK + c0]),
+               __float_as_uint(s_kf[ia * LDK + c0 + 4]), __float_as_uint(s_kf[ib * LDK + c0 + 4]),
+               __float_as_uint(s_kf[(8 * nt + g) * LDK + c0]), __float_as_uint(s_kf[(8 * nt + g) * LDK + c0 + 4]));
+    }
 #pragma unroll
-    for (int n4 = 0; n4 < 4; ++n4) {
-      const int nt = 4 * nh + n4;
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
-      if (8 * nt <= 16 * mt + 15) {
-        for (int kk = 0; kk < K / 8; ++kk) {
-          const int c0 = 8 * kk + j;
-          mma_tf32(acc, __float_as_uint(s_kf[ia * LDK + c0]), __float_as_uint(s_kf[ib * LDK + c0]),
-                   __float_as_uint(s_kf[ia * LDK + c0 + 4]), __float_as_uint(s_kf[ib * LDK + c0 + 4]),
-                   __float_as_uint(s_kf[(8 * nt + g) * LDK + c0]), __float_as_uint(s_kf[(8 * nt + g) * LDK + c0 + 4]));
-        }
-      }
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int jj = 8 * nt + 2 * j + e;
-        s_G[ia * 68 + jj] = (ia > jj) ? s_bs[ia] * s_b1[jj] * acc[e] * expf(s_gc[ia] - s_gc[jj]) : 0.f;
-        s_G[ib * 68 + jj] = (ib > jj) ? s_bs[ib] * s_b1[jj] * acc[2 + e] * expf(s_gc[ib] - s_gc[jj]) : 0.f;
-      }
+    for (int e = 0; e < 2; ++e) {
+      const int jj = 8 * nt + 2 * j + e;
+      s_G[ia * 68 + jj] = (ia > jj) ? s_bs[ia] * s_b1[jj] * acc[e] * expf(s_gc[ia] - s_gc[jj]) : 0.f;
+      s_G[ib * 68 + jj] = (ib > jj) ? s_bs[ib] * s_b1[jj] * acc[2 + e] * expf(s_gc[ib] - s_gc[jj]) : 0.f;
     }
   }
   __syncthreads();
   wy_solve(s_G, s_T);
   __syncthreads();
-  // ---- W = T diag(beta^sigma exp(gc)) k  -> w_read codes
-  {
-    constexpr int NTW = K / 16;
-    float acc[NTW][4];
+  const float inv_sw = 1.0f / d.sw[h];
+  T* up = reinterpret_cast<T*>(d.u);
 #pragma unroll
-    for (int nt = 0; nt < NTW; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-    const int n0 = nh * (K / 2);
-    wy_product<NTW>(acc, s_T, s_cwW, s_kf, LDK, mt, n0, g, j);
-    const float inv_sw = 1.0f / d.sw[h];
+  for (int half = 0; half < 2; ++half) {
+    const int mt = half == 0 ? pr : 3 - pr;
     const int ia = 16 * mt + g, ib = ia + 8;
+    // ---- W = T diag(beta^sigma exp(gc)) k  -> w_read codes
+    {
+      constexpr int NTW = K / 32;
+      float acc[NTW][4];
 #pragma unroll
-    for (int nt = 0; nt < NTW; ++nt) {
-      const int col = n0 + 8 * nt + 2 * j;
-      const int a0 = q8(Act<T>::round(acc[nt][0]), inv_sw, a.qmax), a1 = q8(Act<T>::round(acc[nt][1]), inv_sw, a.qmax);
-      const int b0 = q8(Act<T>::round(acc[nt][2]), inv_sw, a.qmax), b1 = q8(Act<T>::round(acc[nt][3]), inv_sw, a.qmax);
-      *reinterpret_cast<uint16_t*>(d.wq + (tile * C + ia) * K + col) = (uint16_t)((a0 & 0xff) | ((a1 & 0xff) << 8));
-      *reinterpret_cast<uint16_t*>(d.wq + (tile * C + ib) * K + col) = (uint16_t)((b0 & 0xff) | ((b1 & 0xff) << 8));
+      for (int nt = 0; nt < NTW; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+      const int n0 = qd * (K / 4);
+      wy_product<NTW>(acc, s_T, s_cwW, s_kf, LDK, mt, n0, g, j);
+#pragma unroll
+      for (int nt = 0; nt < NTW; ++nt) {
+        const int col = n0 + 8 * nt + 2 * j;
+        const int a0 = q8(Act<T>::round(acc[nt][0]), inv_sw, a.qmax), a1 = q8(Act<T>::round(acc[nt][1]), inv_sw, a.qmax);
+        const int b0 = q8(Act<T>::round(acc[nt][2]), inv_sw, a.qmax), b1 = q8(Act<T>::round(acc[nt][3]), inv_sw, a.qmax);
+        *reinterpret_cast<uint16_t*>(d.wq + (tile * C + ia) * K + col) = (uint16_t)((a0 & 0xff) | ((a1 & 0xff) << 8));
+        *reinterpret_cast<uint16_t*>(d.wq + (tile * C + ib) * K + col) = (uint16_t)((b0 & 0xff) | ((b1 & 0xff) << 8));
+      }
     }
-  }
-  // ---- U = T diag(beta^sigma) v  -> activation dtype
-  {
-    constexpr int NTU = V / 16;
-    float acc[NTU][4];
+    // ---- U = T diag(beta^sigma) v  -> activation dtype
+    {
+      constexpr int NTU = V / 32;
+      float acc[NTU][4];
 #pragma unroll
-    for (int nt = 0; nt < NTU; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-    const int n0 = nh * (V / 2);
-    wy_product<NTU>(acc, s_T, s_bs, s_vf, LDV, mt, n0, g, j);
-    const int ia = 16 * mt + g, ib = ia + 8;
-    T* up = reinterpret_cast<T*>(d.u);
+      for (int nt = 0; nt < NTU; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+      const int n0 = qd * (V / 4);
+      wy_product<NTU>(acc, s_T, s_bs, s_vf, LDV, mt, n0, g, j);
 #pragma unroll
-    for (int nt = 0; nt < NTU; ++nt) {
-      const int col = n0 + 8 * nt + 2 * j;
-      *reinterpret_cast<uint32_t*>(up + (tile * C + ia) * V + col) = Act<T>::pack2(acc[nt][0], acc[nt][1]);
-      *reinterpret_cast<uint32_t*>(up + (tile * C + ib) * V + col) = Act<T>::pack2(acc[nt][2], acc[nt][3]);
+      for (int nt = 0; nt < NTU; ++nt) {
+        const int col = n0 + 8 * nt + 2 * j;
+        *reinterpret_cast<uint32_t*>(up + (tile * C + ia) * V + col) = Act<T>::pack2(acc[nt][0], acc[nt][1]);
+        *reinterpret_cast<uint32_t*>(up + (tile * C + ib) * V + col) = Act<T>::pack2(acc[nt][2], acc[nt][3]);
+      }
     }
   }
   uint32_t* kw_out = reinterpret_cast<uint32_t*>(a.kwT + tile * (size_t)(K * C));

@@ -644,16 +644,20 @@ __global__ void __launch_bounds__(256) zoo_kda_wy_kernel(DiagArgs a) {
       *reinterpret_cast<float4*>(s_vf + t * LDV + 8 * seg + 4) = make_float4(x[4], x[5], x[6], x[7]);
     }
   }
-  const int mt = warp & 3, nh = warp >> 2;
+  // Row tile mt of W and U contracts over 2 mt + 2 steps of eight tokens: every warp takes the row tiles pr and 3 - pr
+  // (five steps on average instead of up to eight) and one quarter of the columns.
+  const int pr = warp & 1, qd = warp >> 1;
+  const float inv_sw = 1.0f / a.sw[h];
   // ---- W = T diag(beta^sigma) (k exp(gc))  -> w_read codes
-  {
-    constexpr int NTW = K / 16;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int mt = half == 0 ? pr : 3 - pr;
+    constexpr int NTW = K / 32;
     float acc[NTW][4];
 #pragma unroll
     for (int nt = 0; nt < NTW; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-    const int n0 = nh * (K / 2);
+    const int n0 = qd * (K / 4);
     wy_product_split<NTW>(acc, s_T, s_bs, s_x, LD, mt, n0, g, j4);
-    const float inv_sw = 1.0f / a.sw[h];
     const int ia = 16 * mt + g, ib = ia + 8;
 #pragma unroll
     for (int nt = 0; nt < NTW; ++nt) {
@@ -666,15 +670,17 @@ __global__ void __launch_bounds__(256) zoo_kda_wy_kernel(DiagArgs a) {
   }
   __syncthreads();  // v staged by all threads
   // ---- U = T diag(beta^sigma) v (v is exact in TF32)
-  {
-    constexpr int NTU = V / 16;
+  T* up = reinterpret_cast<T*>(a.u);
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int mt = half == 0 ? pr : 3 - pr;
+    constexpr int NTU = V / 32;
     float acc[NTU][4];
 #pragma unroll
     for (int nt = 0; nt < NTU; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-    const int n0 = nh * (V / 2);
+    const int n0 = qd * (V / 4);
     wy_product<NTU>(acc, s_T, s_bs, s_vf, LDV, mt, n0, g, j4);
     const int ia = 16 * mt + g, ib = ia + 8;
-    T* up = reinterpret_cast<T*>(a.u);
 #pragma unroll
     for (int nt = 0; nt < NTU; ++nt) {
       const int col = n0 + 8 * nt + 2 * j4;
