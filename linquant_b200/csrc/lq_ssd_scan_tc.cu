@@ -111,8 +111,13 @@ __device__ __forceinline__ bool mbar_wait_suspending(uint32_t bar, uint32_t pari
   }
   return false;
 }
-// by every lane (each needs its own acquire of the barrier's phase), warp-uniform result
+// by every lane (each needs its own acquire of the barrier's phase), warp-uniform result. Most waits of the workers find
+// their phase complete already: one non-suspending probe first.
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  if (__all_sync(0xffffffffu, done != 0u)) return true;
   return __all_sync(0xffffffffu, mbar_wait_suspending(bar, parity) ? 1 : 0) != 0;
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory"); }
@@ -155,7 +160,7 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
   using namespace scantc;
   constexpr int P = 64, N = 128, C = 128 * MB, NT = MB == 2 ? 6 : 2;
   constexpr bool XBF16 = !std::is_same<T, __half>::value;
-  const int NC = p.L / C;
+  const int NC = p.L / C, hpg = p.H / p.G;
   extern __shared__ uint8_t smem_dyn[];
   const uint32_t s_stage0 = (smem_u32(smem_dyn) + 1023u) & ~1023u;  // two input stages
   const uint32_t s_ring = s_stage0 + 2 * kStageBytes;             // kRing M-tile slots of 16 KB
@@ -222,7 +227,7 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
       if (j < n_mine) {
         if (lane == 0) {
           const int b = ld.b, c = ld.c, h = ld.h;
-          const int grp = h / (p.H / p.G);
+          const int grp = p.G == 1 ? 0 : h / hpg;
           const uint32_t st = s_stage0 + s * kStageBytes, fb = bar(FULL_IN, s);
           mbar_expect(fb, (uint32_t)(C * 128 + MB * 16384 + 8192 + 2 * C * 4));
 #pragma unroll
@@ -383,7 +388,7 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
     for (int j = 0; j < n_mine && !failed; ++j, w.next()) {
       const int s = j & 1;
       const int b = w.b, c = w.c, h = w.h;
-      const int grp = h / (p.H / p.G);
+      const int grp = p.G == 1 ? 0 : h / hpg;  // (no division on the common single-group path: its latency opens every item)
       // per-head constants of this item (global loads issued before the epilogue below, used after it)
       float cs_v = 0.f, D_v = 0.f;
       if (tid < P) cs_v = __fmul_rn(p.C_scale[grp], p.state_scale[h * P + tid]);
