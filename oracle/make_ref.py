@@ -7,7 +7,9 @@ output, like a compiled ``.so``) so that machines without the reference checkout
 ``bench.py --impl reference`` and its ``cpu_baseline`` leg time ``oracle/_ref`` when it exists and fall back to the
 restatement in ``oracle/zoo_oracle.py`` otherwise. Nothing on the product path imports either.
 
-    python oracle/make_ref.py [path-to-reference-checkout]     (default: /root/reference)
+    python oracle/make_ref.py [path-to-reference-checkout]
+
+(default: ``$LINQUANT_REFERENCE_ROOT``, else the directory ``reference`` beside this repository)
 """
 
 import os
@@ -18,8 +20,12 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 FILES = ("reference.py", "invariances.py")
 
 
-def build(ref_root="/root/reference"):
-    src = os.path.join(ref_root, "linquant")
+def default_root():
+    return os.environ.get("LINQUANT_REFERENCE_ROOT") or os.path.normpath(os.path.join(HERE, "..", "..", "reference"))
+
+
+def build(ref_root=None):
+    src = os.path.join(ref_root or default_root(), "linquant")
     if not all(os.path.exists(os.path.join(src, f)) for f in FILES):
         return None
     dst = os.path.join(HERE, "_ref", "linquant")
@@ -45,5 +51,5 @@ def load():
 
 
 if __name__ == "__main__":
-    out = build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    out = build(sys.argv[1] if len(sys.argv) > 1 else None)
     print(out or "reference checkout not found: nothing built")
