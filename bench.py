@@ -277,6 +277,34 @@ def dist_env():
     return int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
 
 
+_ALL_CORES = None  # the affinity the process started with (the CPU baseline takes every core back)
+
+
+def pin_host_threads(local, world):
+    """Pins this rank's host threads to the CPU cores NVML reports as local to its GPU (its share of them when the ranks
+    of the box report the same set), before any pinned host buffer is allocated. Returns a one-line record."""
+    global _ALL_CORES
+    try:
+        import pynvml
+
+        _ALL_CORES = os.sched_getaffinity(0)
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(local).uuid)
+        h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cores = [64 * i + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1]
+        allowed = sorted(set(cores) & os.sched_getaffinity(0))
+        if not allowed:
+            return "unchanged (NVML reports no usable local cores)"
+        per = len(allowed) // world
+        mine = allowed[local * per:(local + 1) * per] if per >= 2 else allowed
+        os.sched_setaffinity(0, mine)
+        torch.set_num_threads(max(1, min(len(mine), 8)))
+        return f"cores {mine[0]}-{mine[-1]} ({len(mine)} of the {len(allowed)} NVML-local cores)"
+    except Exception as e:  # no NVML, no permission: leave the affinity as it is
+        return f"unchanged ({type(e).__name__})"
+
+
 def run_ours(args):
     import torch.distributed as dist
 
@@ -288,6 +316,7 @@ def run_ours(args):
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    affinity = pin_host_threads(local, world)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     _cabi.lib()  # fail loudly when the CUDA library is missing
@@ -424,7 +453,7 @@ def run_ours(args):
                    "calibration": "absmax observers on 4 further seeded batches per layer", "warmup_steps_run": warm},
         "e2e": {"value": tokens * e2e_steps / (e2e_ms * 1e-3) / 1e6, "unit": "Mtokens/s", "h2d_bytes_per_step": h2d * world,
                 "d2h_bytes_per_step": d2h * world, "steps": e2e_steps, "h2d_gbs_per_rank": h2d * e2e_steps / (e2e_ms * 1e-3) / 1e9,
-                "host_buffers": "pinned ring of 2 layer inputs and 2 layer outputs per rank"},
+                "host_buffers": "pinned ring of 2 layer inputs and 2 layer outputs per rank", "host_affinity_rank0": affinity},
         "gpu_launches": 7 * n_layers * args.steps,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": peak_kind, "traffic": None if traffic is None else traffic * ht_rank,
@@ -690,6 +719,8 @@ CPU_SAMPLE = "1 of 64 layers x 1 of 8 batch elements x 2048 of 16384 tokens, all
 
 
 def cpu_baseline(reps):
+    if _ALL_CORES:
+        os.sched_setaffinity(0, _ALL_CORES)
     threads = os.cpu_count() or 1
     run, tokens, kind = cpu_sample(threads)
     run()
