@@ -1009,7 +1009,9 @@ template <typename T, bool QUANT>
 static int launch_rotate(const T* x, long long sb, long long stt, long long ob, long long oc, int B, int T_len, int G, int N,
                          int gy, const float* signs, const float* ib, const float* ic, const float* db, const float* dc,
                          int8_t* qb, int8_t* qc, T* y, cudaStream_t st) {
-  const int rows_per_cta = 256;
+  // 256 rows per CTA amortise the per-thread constants; a problem too small to fill the GPU that way takes 128 or 64
+  int rows_per_cta = 256;
+  while (rows_per_cta > 64 && (long long)((T_len + rows_per_cta - 1) / rows_per_cta) * gy * B < 592) rows_per_cta >>= 1;
   dim3 grid((T_len + rows_per_cta - 1) / rows_per_cta, gy, B);
   if (N == 128) ssd_rotate_rows_kernel<T, 128, QUANT><<<grid, 256, 0, st>>>(x, sb, stt, ob, oc, T_len, G, signs, ib, ic, db, dc, qb, qc, y, rows_per_cta);
   else if (N == 64) ssd_rotate_rows_kernel<T, 64, QUANT><<<grid, 256, 0, st>>>(x, sb, stt, ob, oc, T_len, G, signs, ib, ic, db, dc, qb, qc, y, rows_per_cta);
