@@ -738,7 +738,8 @@ def run_reference(args):
         return
     threads = os.cpu_count() or 1
     run, tokens, kind = cpu_sample(threads)
-    for _ in range(min(args.warmup, 3)):
+    warm = max(args.warmup, 3)  # the same count the measured arm reports
+    for _ in range(warm):
         run()
     t = time.perf_counter()
     for _ in range(args.steps):
@@ -747,7 +748,7 @@ def run_reference(args):
     val = tokens * args.steps / (dt * M2["layers"]) / 1e6
     print(json.dumps({
         "impl": "reference", "metric": "INT8 chunk-prefill Mtokens/s", "value": val, "unit": "Mtokens/s",
-        "n_gpus": world, "steps": args.steps, "warmup": min(args.warmup, 3), "ms_per_step": dt / args.steps * 1e3,
+        "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
         "config": {"workload": WORKLOAD},
         "cpu_baseline": {"value": val, "unit": "Mtokens/s", "cores": threads, "kind": kind, "sample": CPU_SAMPLE + " (each step)"},
