@@ -259,3 +259,19 @@ def test_kronecker_hadamard_matches_reference_kernel_golden(name):
     assert got.dtype == y.dtype
     frac = float((got != y).float().mean())
     assert frac <= 1e-3 and float((got.float() - y.float()).abs().max()) <= 0.04, f"{name}: {frac:.2e} of outputs differ"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("chunk", [128, 256])
+def test_bmm_chunk_two_groups_on_the_tensor_core_kernel(chunk):
+    """C.B^T at d_state 128 with two groups (the group picks the 128-byte column block of the INT8 rows that the TMA
+    box starts at) and a ragged number of chunks: codes bit for bit against the CPU restatement."""
+    from linquant_b200.kernels.mamba2 import ssd_combined as sc
+
+    k = make_case(B=2, L=3 * chunk, H=4, G=2, N=128, chunk=chunk, seed=11)
+    ref = so.bmm_chunk(k["qC"], k["sC"], k["qB"], k["sB"], chunk, k["cb_scale"])
+    got = sc._quant_bmm_chunk_fwd(cu(k["qC"]), cu(k["sC"]), cu(k["qB"]), cu(k["sB"]), chunk, cu(k["cb_scale"]))
+    assert got.shape == ref.shape and torch.equal(got.cpu(), ref), "CB codes differ"
+    import linquant_b200
+
+    linquant_b200.check_status("cuda")
