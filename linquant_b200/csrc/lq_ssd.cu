@@ -895,6 +895,8 @@ int run_chunk_state_value_tc(const lq_ssd_problem* p, int* status, cudaStream_t 
 bool chunk_state_value_tc2_applies(const lq_ssd_problem* p);
 int run_chunk_state_value_tc2(const lq_ssd_problem* p, int* status, cudaStream_t st);
 int run_chunk_scan_tc(const lq_ssd_problem* p, int* status, cudaStream_t st);
+bool chunk_state_key_tc_applies(const lq_ssd_problem* p);
+int run_chunk_state_key_tc(const lq_ssd_problem* p, int* status, cudaStream_t st);
 bool bmm_tc_applies(const lq_ssd_problem* p);
 int run_bmm_tc(const lq_ssd_problem* p, int* status, cudaStream_t st);
 }
@@ -908,6 +910,8 @@ static int ssd_chunk_state(const lq_ssd_problem* p, bool keyside, lq_stream stre
   dim3 grid(p->L / p->chunk, p->H, p->B);
   if (keyside) {
     if (!p->b_fp || !p->x_scale_hp || !p->b_gate_scale) return fail(LQ_ERR_NULL, "%s: b_fp, x_scale_hp, b_gate_scale required", what);
+    // d_state 128 with chunks of 128 / 256 tokens: tcgen05, two heads per CTA; else the warp-level MMA kernel
+    if (chunk_state_key_tc_applies(p)) return run_chunk_state_key_tc(p, p->status, st);
     launch_chunk_state<true>(p, grid, st);
   } else {
     if (!p->q_B || !p->alpha_hp || !p->bscale_g) return fail(LQ_ERR_NULL, "%s: q_B, alpha_hp, bscale_g required", what);
