@@ -897,8 +897,8 @@ int run_chunk_state_value_tc2(const lq_ssd_problem* p, int* status, cudaStream_t
 int run_chunk_scan_tc(const lq_ssd_problem* p, int* status, cudaStream_t st);
 bool chunk_state_key_tc_applies(const lq_ssd_problem* p);
 int run_chunk_state_key_tc(const lq_ssd_problem* p, int* status, cudaStream_t st);
-bool bmm_tc_applies(const lq_ssd_problem* p);
-int run_bmm_tc(const lq_ssd_problem* p, int* status, cudaStream_t st);
+bool bmm_tc_applies(const lq_ssd_problem* p, bool b_is_fp);
+int run_bmm_tc(const lq_ssd_problem* p, bool b_is_fp, int* status, cudaStream_t st);
 }
 // with_qbt: take the path that goes through the transposed copy of q_B even where the transposition-free kernel applies
 static int ssd_chunk_state(const lq_ssd_problem* p, bool keyside, lq_stream stream, bool with_qbt = false) {
@@ -982,8 +982,8 @@ extern "C" int lq_ssd_bmm_chunk(const lq_ssd_problem* p, int b_is_fp, lq_stream 
   const int tiles = p->chunk / 64;
   dim3 grid(tiles * tiles, (p->L / p->chunk) * p->G, p->B);
   cudaStream_t st = (cudaStream_t)stream;
-  // INT8 B at d_state 128 and chunks of 128 / 256 tokens: tcgen05 + TMA, one CTA per chunk; else the warp-level MMA kernel
-  if (!b_is_fp && bmm_tc_applies(p)) return run_bmm_tc(p, p->status, st);
+  // d_state 128 and chunks of 128 / 256 tokens: tcgen05 + TMA, one CTA per chunk; else the warp-level MMA kernel
+  if (bmm_tc_applies(p, b_is_fp != 0)) return run_bmm_tc(p, b_is_fp != 0, p->status, st);
   if (b_is_fp) launch_bmm<true>(p, grid, st);
   else launch_bmm<false>(p, grid, st);
   return check_launch("ssd_bmm_kernel");
