@@ -486,7 +486,10 @@ __global__ void __launch_bounds__(576, 1) ssd_chunk_scan_tc_kernel(const __grid_
         const int t = 128 * mb + r, g0 = t & ~15;
         const uint4 cq = nxt[ti & 1];
         if (ti + 2 < NT) fetch(ti + 2);
-        if (g >= kRing) ok = warp_wait(bar(RING_EMPTY, slot), rph ^ 1u) && ok;
+        // A slot is rewritten only after the product that read it has completed. When an item is a whole number of laps of
+        // the ring, its first lap needs no wait: this warp has seen the previous item's accumulators complete (epilogue
+        // above), and with them every product that read the ring.
+        if (NT % kRing == 0 ? ti >= kRing : g >= kRing) ok = warp_wait(bar(RING_EMPTY, slot), rph ^ 1u) && ok;
         const uint32_t srow = s_ring + slot * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
         const int kq = 64 * kb + 16 * qt;
         // weights of this 16-token group for this row: zeros above the diagonal, the row's own masked weights on it, the
