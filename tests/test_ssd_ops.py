@@ -275,3 +275,26 @@ def test_bmm_chunk_two_groups_on_the_tensor_core_kernel(chunk):
     import linquant_b200
 
     linquant_b200.check_status("cuda")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("chunk,dtype", [(128, torch.float16), (256, torch.bfloat16)])
+def test_chunk_states_two_groups_on_the_tensor_core_kernels(chunk, dtype):
+    """Value- and key-side chunk states at d_state 128 with two groups of two heads (the head pair of a CTA picks its
+    group's B lanes): INT8 state codes against the CPU restatement, and the key side's C.B^T from the unquantised B."""
+    from linquant_b200.kernels.mamba2 import ssd_combined as sc
+
+    k = make_case(B=2, L=2 * chunk, H=4, G=2, N=128, chunk=chunk, dtype=dtype, seed=12)
+    dtd, dAd = cu(k["dt"]), cu(k["dA"])
+    st_ref = so.chunk_state_value(k["x"], k["qB"], k["dt"], k["dA"], k["alpha"], k["sB"], k["state_scale"])
+    st = sc._quant_chunk_state_fwd_xfp_static_int8(cu(k["x"]), cu(k["qB"]), dtd, dAd, cu(k["alpha"]), cu(k["sB"]), cu(k["state_scale"]))
+    code_mismatch(st, st_ref, "value-side chunk states, two groups")
+    stk_ref = so.chunk_state_key(k["x"], k["x_scale"], k["Bm"], k["dt"], k["dA"], k["state_scale"], k["b_gate"])
+    stk = sc._chunk_state_keyside_fwd(cu(k["x"]), cu(k["x_scale"]), cu(k["Bm"]), dtd, dAd, cu(k["state_scale"]), cu(k["b_gate"]))
+    code_mismatch(stk, stk_ref, "key-side chunk states, two groups")
+    cbk_ref = so.bmm_chunk(k["qC"], k["sC"], k["Bm"], k["sB"], chunk, k["cb_scale"], b_is_fp=True)
+    cbk = sc._quant_bmm_chunk_fwd(cu(k["qC"]), cu(k["sC"]), cu(k["Bm"]), cu(k["sB"]), chunk, cu(k["cb_scale"]), b_is_fp=True)
+    code_mismatch(cbk, cbk_ref, "key-side CB codes, two groups")
+    import linquant_b200
+
+    linquant_b200.check_status("cuda")
