@@ -114,20 +114,27 @@ __global__ void __launch_bounds__(256) zoo_diag_rows_kernel(DiagArgs a) {
       uint32_t kwp[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) kwp[j] = 0u;
+      // the eight row loads of the group are in flight before the first is used
+      uint4 rq[4], rk[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const size_t row = (((size_t)b * a.T + (size_t)c * C + 4 * tg + i) * a.H + h) * K + 8 * r;
+        rq[i] = __ldg(reinterpret_cast<const uint4*>(qp + row));
+        rk[i] = __ldg(reinterpret_cast<const uint4*>(kp + row));
+      }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int t = 4 * tg + i;
-        const size_t row = (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K + 8 * r;
         float x[8], gv[8];
         int cd[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) gv[j] = s_gc[t * LD + 8 * r + j];
-        Act<T>::unpack8(*reinterpret_cast<const uint4*>(qp + row), x);
+        Act<T>::unpack8(rq[i], x);
 #pragma unroll
         for (int j = 0; j < 8; ++j) cd[j] = q8(__fmul_rn(__fmul_rn(x[j], __expf(gv[j])), a.scale), inv_sq, a.qmax);
         *reinterpret_cast<uint2*>(a.qq + (tile * C + t) * K + 8 * r) =
             make_uint2(pack4(cd[0], cd[1], cd[2], cd[3]), pack4(cd[4], cd[5], cd[6], cd[7]));
-        Act<T>::unpack8(*reinterpret_cast<const uint4*>(kp + row), x);
+        Act<T>::unpack8(rk[i], x);
         if (DELTA && e_hw != 0.f) {
           const float hw = s_hw[t];
 #pragma unroll
