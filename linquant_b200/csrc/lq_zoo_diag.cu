@@ -447,13 +447,26 @@ __device__ __forceinline__ void kda_scaled_rows(const DiagArgs& a, int b, int c,
                                                 int anchor_row, int first_row, int nrows, int dst_row, bool toward_anchor) {
   // rows [first_row, first_row + nrows) of k, times exp(gc[row] - gc[anchor]) (toward_anchor) or exp(gc[anchor] - gc[row]),
   // or times exp(gc[row]) when anchor_row < 0; written as fp32 to s_x rows dst_row ...
-  constexpr int C = 64, LD = K + 4, LPR = K / 8;
+  constexpr int C = 64, LD = K + 4, LPR = K / 8, MAXIT = C * LPR / 256;
   const T* kp = reinterpret_cast<const T*>(a.k);
-  for (int i = threadIdx.x; i < nrows * LPR; i += 256) {
+  // every row piece of the thread is requested before the first is used (at most MAXIT of them: nrows <= 64)
+  uint4 raw[MAXIT];
+#pragma unroll
+  for (int it = 0; it < MAXIT; ++it) {
+    const int i = threadIdx.x + 256 * it;
+    if (i < nrows * LPR) {
+      const int rr = i / LPR, seg = i % LPR;
+      raw[it] = __ldg(reinterpret_cast<const uint4*>(kp + (((size_t)b * a.T + (size_t)c * C + first_row + rr) * a.H + h) * K + 8 * seg));
+    }
+  }
+#pragma unroll
+  for (int it = 0; it < MAXIT; ++it) {
+    const int i = threadIdx.x + 256 * it;
+    if (i >= nrows * LPR) break;
     const int rr = i / LPR, seg = i % LPR;
     const int t = first_row + rr;
     float x[8];
-    Act<T>::unpack8(__ldg(reinterpret_cast<const uint4*>(kp + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K + 8 * seg)), x);
+    Act<T>::unpack8(raw[it], x);
     const float4 g0 = *reinterpret_cast<const float4*>(s_gc + t * LD + 8 * seg);
     const float4 g1 = *reinterpret_cast<const float4*>(s_gc + t * LD + 8 * seg + 4);
     float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
@@ -494,10 +507,18 @@ __global__ void __launch_bounds__(256) zoo_kda_wy_kernel(DiagArgs a) {
   load_gc_tile<K>(a.gc + tile * (size_t)(C * K), s_gc);
   {
     const T* kp = reinterpret_cast<const T*>(a.k);
-    for (int i = tid; i < C * (K / 8); i += 256) {
-      const int t = i / (K / 8), seg = i % (K / 8);
+    constexpr int NIT = C * (K / 8) / 256;
+    uint4 raw[NIT];
+#pragma unroll
+    for (int it = 0; it < NIT; ++it) {
+      const int i = tid + 256 * it, t = i / (K / 8), seg = i % (K / 8);
+      raw[it] = __ldg(reinterpret_cast<const uint4*>(kp + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K + 8 * seg));
+    }
+#pragma unroll
+    for (int it = 0; it < NIT; ++it) {
+      const int i = tid + 256 * it, t = i / (K / 8), seg = i % (K / 8);
       float x[8];
-      Act<T>::unpack8(__ldg(reinterpret_cast<const uint4*>(kp + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K + 8 * seg)), x);
+      Act<T>::unpack8(raw[it], x);
       *reinterpret_cast<float4*>(s_x + t * LD + 8 * seg) = make_float4(x[0], x[1], x[2], x[3]);
       *reinterpret_cast<float4*>(s_x + t * LD + 8 * seg + 4) = make_float4(x[4], x[5], x[6], x[7]);
     }
@@ -643,10 +664,18 @@ __global__ void __launch_bounds__(256) zoo_kda_wy_kernel(DiagArgs a) {
   __syncthreads();
   {
     const T* vp = reinterpret_cast<const T*>(a.v);
-    for (int i = tid; i < C * (V / 8); i += 256) {
-      const int t = i / (V / 8), seg = i % (V / 8);
+    constexpr int NIT = C * (V / 8) / 256;
+    uint4 raw[NIT];
+#pragma unroll
+    for (int it = 0; it < NIT; ++it) {
+      const int i = tid + 256 * it, t = i / (V / 8), seg = i % (V / 8);
+      raw[it] = __ldg(reinterpret_cast<const uint4*>(vp + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * V + 8 * seg));
+    }
+#pragma unroll
+    for (int it = 0; it < NIT; ++it) {
+      const int i = tid + 256 * it, t = i / (V / 8), seg = i % (V / 8);
       float x[8];
-      Act<T>::unpack8(__ldg(reinterpret_cast<const uint4*>(vp + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * V + 8 * seg)), x);
+      Act<T>::unpack8(raw[it], x);
       *reinterpret_cast<float4*>(s_vf + t * LDV + 8 * seg) = make_float4(x[0], x[1], x[2], x[3]);
       *reinterpret_cast<float4*>(s_vf + t * LDV + 8 * seg + 4) = make_float4(x[4], x[5], x[6], x[7]);
     }
