@@ -165,11 +165,15 @@ __global__ void __launch_bounds__(256) zoo_diag_rows_kernel(DiagArgs a) {
       uint32_t vlp[8], vwp[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) vlp[j] = vwp[j] = 0u;
+      uint4 rv[4];  // the four row loads of the group are in flight before the first is used
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        rv[i] = __ldg(reinterpret_cast<const uint4*>(vp + (((size_t)b * a.T + (size_t)c * C + 4 * tg + i) * a.H + h) * V + 8 * r));
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int t = 4 * tg + i;
         float x[8];
-        Act<T>::unpack8(*reinterpret_cast<const uint4*>(vp + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * V + 8 * r), x);
+        Act<T>::unpack8(rv[i], x);
         const float fv = expf(a.eta * s_le[t]);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
