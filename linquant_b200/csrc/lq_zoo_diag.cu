@@ -405,28 +405,48 @@ __global__ void __launch_bounds__(256) zoo_diag_amat_kernel(DiagArgs a) {
                       __fmul_rn(s8_to_float<2>(kw), __expf(an.z - gt.z)), __fmul_rn(s8_to_float<3>(kw), __expf(an.w - gt.w)));
     }
     __syncthreads();
-    {  // 16 x 16 x K product: eight lanes per (i, j) pair as above would leave half the block idle; here one (i, j)
-       // per thread pair-of-halves: thread = (i, j, half of K), two partial sums joined by one shuffle
-      const int pr = tid >> 1, hf = tid & 1;
-      const int i = pr >> 3, j2 = (pr & 7) * 2;  // this thread: row i, columns j2 and j2 + 1
-      const float* qr = s_qd + i * LD + hf * (K / 2);
-      const float* k0 = s_kd + j2 * LD + hf * (K / 2);
-      const float* k1 = k0 + LD;
-      float s0 = 0.f, s1 = 0.f;
-      if (j2 <= i) {
-#pragma unroll 4
-        for (int n = 0; n < K / 2; n += 4) {
-          const float4 qv = *reinterpret_cast<const float4*>(qr + n);
-          const float4 ka = *reinterpret_cast<const float4*>(k0 + n), kb = *reinterpret_cast<const float4*>(k1 + n);
-          s0 = fmaf(qv.x, ka.x, s0); s0 = fmaf(qv.y, ka.y, s0); s0 = fmaf(qv.z, ka.z, s0); s0 = fmaf(qv.w, ka.w, s0);
-          s1 = fmaf(qv.x, kb.x, s1); s1 = fmaf(qv.y, kb.y, s1); s1 = fmaf(qv.z, kb.z, s1); s1 = fmaf(qv.w, kb.w, s1);
+    {  // 16 x 16 x K product on the tensor cores, 3xTF32 (both factors split into a TF32 part and a TF32 remainder: the
+       // products are good to about 2^-21). Warp w contracts the channels [K/8 w, K/8 (w + 1)); the eight partial blocks
+       // are parked behind the scaled rows and summed in a fixed order.
+      float* s_part = s_kd + SUB * LD;  // [8 warps][16][16]
+      float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int kk = 0; kk < K / 64; ++kk) {
+        const int c0 = (K / 8) * warp + 8 * kk + j4, c1 = c0 + 4;
+        const float xa[4] = {s_qd[g * LD + c0], s_qd[(g + 8) * LD + c0], s_qd[g * LD + c1], s_qd[(g + 8) * LD + c1]};
+        uint32_t ab[4], as_[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          ab[e] = tf32_rna(xa[e]);
+          as_[e] = tf32_rna(xa[e] - __uint_as_float(ab[e]));
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const float y0 = s_kd[(8 * nt + g) * LD + c0], y1 = s_kd[(8 * nt + g) * LD + c1];
+          const uint32_t b0 = tf32_rna(y0), b1 = tf32_rna(y1);
+          const uint32_t s0 = tf32_rna(y0 - __uint_as_float(b0)), s1 = tf32_rna(y1 - __uint_as_float(b1));
+          mma_tf32(acc[nt], as_[0], as_[1], as_[2], as_[3], b0, b1);
+          mma_tf32(acc[nt], ab[0], ab[1], ab[2], ab[3], s0, s1);
+          mma_tf32(acc[nt], ab[0], ab[1], ab[2], ab[3], b0, b1);
         }
       }
-      s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
-      s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
-      if (hf == 0 && j2 <= i) {
-        s_A[(SUB * I + i) * 65 + SUB * I + j2] = __fmul_rn(s0, sqk);
-        if (j2 + 1 <= i) s_A[(SUB * I + i) * 65 + SUB * I + j2 + 1] = __fmul_rn(s1, sqk);
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        float* pw = s_part + warp * 256;
+        pw[g * 16 + 8 * nt + 2 * j4] = acc[nt][0];
+        pw[g * 16 + 8 * nt + 2 * j4 + 1] = acc[nt][1];
+        pw[(g + 8) * 16 + 8 * nt + 2 * j4] = acc[nt][2];
+        pw[(g + 8) * 16 + 8 * nt + 2 * j4 + 1] = acc[nt][3];
+      }
+      __syncthreads();
+      {
+        const int i = tid >> 4, jj = tid & 15;
+        if (jj <= i) {
+          float sum = 0.f;
+#pragma unroll
+          for (int w = 0; w < 8; ++w) sum += s_part[w * 256 + tid];
+          s_A[(SUB * I + i) * 65 + SUB * I + jj] = __fmul_rn(sum, sqk);
+        }
       }
     }
     __syncthreads();
@@ -760,7 +780,7 @@ static int run_diag_T(const lq_zoo_problem* p, const DiagArgs& a, bool delta, in
     return launch_big_smem(zoo_diag_rows_kernel<T, K, V, false>, "zoo_diag_rows_kernel", grid, smem, a, st);
   }
   if (stage == 1) {
-    const size_t smem = sizeof(float) * (64 * (K + 4) + 64 * 65 + 64 + 2 * 16 * (K + 4)) + (size_t)(64 * K * 2 + 16 * K + 48 * K);
+    const size_t smem = sizeof(float) * (64 * (K + 4) + 64 * 65 + 64 + 2 * 16 * (K + 4) + 8 * 256) + (size_t)(64 * K * 2 + 16 * K + 48 * K);
     return launch_big_smem(zoo_diag_amat_kernel<T, K>, "zoo_diag_amat_kernel", grid, smem, a, st);
   }
   const size_t smem = sizeof(float) * (64 * ((K + 4) > (V + 8) ? (K + 4) : (V + 8)) + 64 * (K + 4) + 2 * 64 * 68 + 128);
