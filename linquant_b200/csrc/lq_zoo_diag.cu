@@ -520,6 +520,7 @@ __global__ void __launch_bounds__(256) zoo_kda_wy_kernel(DiagArgs a) {
   float* s_T = s_G + C * 68;
   float* s_bs = s_T + C * 68;
   float* s_b1 = s_bs + C;
+  float* s_part = s_b1 + C;  // [8 warps][16][16] partial diagonal blocks
   float* s_vf = s_gc;
 
   const int c = blockIdx.x, bh = blockIdx.y;
@@ -614,28 +615,45 @@ __global__ void __launch_bounds__(256) zoo_kda_wy_kernel(DiagArgs a) {
                                                                      __fmul_rn(xv.z, __expf(an.z - gt.z)), __fmul_rn(xv.w, __expf(an.w - gt.w)));
       }
       __syncthreads();
-      {  // thread = (row i, columns j2 and j2 + 1, half of K); the two halves are joined by one shuffle
-        const int pr = tid >> 1, hf = tid & 1;
-        const int i = pr >> 3, j2 = (pr & 7) * 2;
-        const float* qr = s_kq + i * LD + hf * (K / 2);
-        const float* k0 = s_kk + j2 * LD + hf * (K / 2);
-        const float* k1 = k0 + LD;
-        float s0 = 0.f, s1 = 0.f;
-        if (j2 < i) {
-#pragma unroll 4
-          for (int n = 0; n < K / 2; n += 4) {
-            const float4 qv = *reinterpret_cast<const float4*>(qr + n);
-            const float4 ka = *reinterpret_cast<const float4*>(k0 + n), kb = *reinterpret_cast<const float4*>(k1 + n);
-            s0 = fmaf(qv.x, ka.x, s0); s0 = fmaf(qv.y, ka.y, s0); s0 = fmaf(qv.z, ka.z, s0); s0 = fmaf(qv.w, ka.w, s0);
-            s1 = fmaf(qv.x, kb.x, s1); s1 = fmaf(qv.y, kb.y, s1); s1 = fmaf(qv.z, kb.z, s1); s1 = fmaf(qv.w, kb.w, s1);
+      {  // 16 x 16 x K product on the tensor cores, 3xTF32, as in the A matrix: warp w contracts the channels
+         // [K/8 w, K/8 (w + 1)), the eight partial blocks are summed in a fixed order
+        float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int kk = 0; kk < K / 64; ++kk) {
+          const int c0 = (K / 8) * warp + 8 * kk + j4, c1 = c0 + 4;
+          const float xa[4] = {s_kq[g * LD + c0], s_kq[(g + 8) * LD + c0], s_kq[g * LD + c1], s_kq[(g + 8) * LD + c1]};
+          uint32_t ab[4], as_[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            ab[e] = tf32_rna(xa[e]);
+            as_[e] = tf32_rna(xa[e] - __uint_as_float(ab[e]));
+          }
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            const float y0 = s_kk[(8 * nt + g) * LD + c0], y1 = s_kk[(8 * nt + g) * LD + c1];
+            const uint32_t b0 = tf32_rna(y0), b1 = tf32_rna(y1);
+            const uint32_t s0 = tf32_rna(y0 - __uint_as_float(b0)), s1 = tf32_rna(y1 - __uint_as_float(b1));
+            mma_tf32(acc[nt], as_[0], as_[1], as_[2], as_[3], b0, b1);
+            mma_tf32(acc[nt], ab[0], ab[1], ab[2], ab[3], s0, s1);
+            mma_tf32(acc[nt], ab[0], ab[1], ab[2], ab[3], b0, b1);
           }
         }
-        s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
-        s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
-        const int ti = SUB * I + i;
-        if (hf == 0 && j2 < i) {
-          s_G[ti * 68 + SUB * I + j2] = s_bs[ti] * s_b1[SUB * I + j2] * s0;
-          if (j2 + 1 < i) s_G[ti * 68 + SUB * I + j2 + 1] = s_bs[ti] * s_b1[SUB * I + j2 + 1] * s1;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          float* pw = s_part + warp * 256;
+          pw[g * 16 + 8 * nt + 2 * j4] = acc[nt][0];
+          pw[g * 16 + 8 * nt + 2 * j4 + 1] = acc[nt][1];
+          pw[(g + 8) * 16 + 8 * nt + 2 * j4] = acc[nt][2];
+          pw[(g + 8) * 16 + 8 * nt + 2 * j4 + 1] = acc[nt][3];
+        }
+        __syncthreads();
+        const int i = tid >> 4, jj = tid & 15;
+        if (jj < i) {
+          float sum = 0.f;
+#pragma unroll
+          for (int w = 0; w < 8; ++w) sum += s_part[w * 256 + tid];
+          const int ti = SUB * I + i;
+          s_G[ti * 68 + SUB * I + jj] = s_bs[ti] * s_b1[SUB * I + jj] * sum;
         }
       }
       __syncthreads();
@@ -783,7 +801,7 @@ static int run_diag_T(const lq_zoo_problem* p, const DiagArgs& a, bool delta, in
     const size_t smem = sizeof(float) * (64 * (K + 4) + 64 * 65 + 64 + 2 * 16 * (K + 4) + 8 * 256) + (size_t)(64 * K * 2 + 16 * K + 48 * K);
     return launch_big_smem(zoo_diag_amat_kernel<T, K>, "zoo_diag_amat_kernel", grid, smem, a, st);
   }
-  const size_t smem = sizeof(float) * (64 * ((K + 4) > (V + 8) ? (K + 4) : (V + 8)) + 64 * (K + 4) + 2 * 64 * 68 + 128);
+  const size_t smem = sizeof(float) * (64 * ((K + 4) > (V + 8) ? (K + 4) : (V + 8)) + 64 * (K + 4) + 2 * 64 * 68 + 128 + 8 * 256);
   return launch_big_smem(zoo_kda_wy_kernel<T, K, V>, "zoo_kda_wy_kernel", grid, smem, a, st);
 }
 
