@@ -665,14 +665,18 @@ __global__ void __launch_bounds__(256) zoo_kda_wy_kernel(DiagArgs a) {
     kda_scaled_rows<T, K>(a, b, c, h, s_gc, s_x, SUB * I, 0, SUB * I, 0, false);        // ke -> rows 0 .. 16I-1
     kda_scaled_rows<T, K>(a, b, c, h, s_gc, s_x, SUB * I, SUB * I, SUB, 48, true);      // kd -> rows 48 .. 63
     __syncthreads();
-    if (warp < 2 * I) {
+    // 2 I column tiles of eight tokens x four quarters of the channels = 8 I units of work, dealt to the eight warps
+    // (one column tile per warp would leave 8 - 2 I warps idle); the quarter sums are parked in the space of T, which is
+    // not needed before the solve, and added in a fixed order.
+    for (int u = warp; u < 8 * I; u += 8) {
+      const int nt = u >> 2, kq = u & 3;
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
       const float* ra = s_x + (48 + g) * LD;
       const float* rb = s_x + (56 + g) * LD;
-      const float* rn = s_x + (8 * warp + g) * LD;
-#pragma unroll 4
-      for (int kk = 0; kk < K / 8; ++kk) {
-        const int c0 = 8 * kk + j4, c1 = c0 + 4;
+      const float* rn = s_x + (8 * nt + g) * LD;
+#pragma unroll
+      for (int ks = 0; ks < K / 32; ++ks) {
+        const int c0 = 8 * (kq * (K / 32) + ks) + j4, c1 = c0 + 4;
         const float xa[4] = {ra[c0], rb[c0], ra[c1], rb[c1]};
         const float xb[2] = {rn[c0], rn[c1]};
         uint32_t ab[4], as_[4], bb[2], bs_[2];
@@ -690,13 +694,20 @@ __global__ void __launch_bounds__(256) zoo_kda_wy_kernel(DiagArgs a) {
         mma_tf32(acc, ab[0], ab[1], ab[2], ab[3], bs_[0], bs_[1]);
         mma_tf32(acc, ab[0], ab[1], ab[2], ab[3], bb[0], bb[1]);
       }
-      const int ia = SUB * I + g, ib = ia + 8;
+      float* pp = s_T + u * 128;  // [16 rows][8 columns]
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        const int jj = 8 * warp + 2 * j4 + e;
-        s_G[ia * 68 + jj] = s_bs[ia] * s_b1[jj] * acc[e];
-        s_G[ib * 68 + jj] = s_bs[ib] * s_b1[jj] * acc[2 + e];
+        pp[g * 8 + 2 * j4 + e] = acc[e];
+        pp[(g + 8) * 8 + 2 * j4 + e] = acc[2 + e];
       }
+    }
+    __syncthreads();
+    for (int el = tid; el < 256 * I; el += 256) {
+      const int i = el / (16 * I), jj = el - i * (16 * I);
+      const float* pp = s_T + (4 * (jj >> 3)) * 128 + i * 8 + (jj & 7);
+      const float sum = ((pp[0] + pp[128]) + pp[256]) + pp[384];
+      const int ia = SUB * I + i;
+      s_G[ia * 68 + jj] = s_bs[ia] * s_b1[jj] * sum;
     }
     __syncthreads();
   }
