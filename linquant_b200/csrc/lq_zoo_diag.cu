@@ -29,12 +29,21 @@ struct DiagArgs {
   float scale, eta, sigma, tau, qmax;
 };
 
-template <int K>
-__device__ __forceinline__ void load_gc_tile(const float* gc_tile, float* s_gc) {
-  for (int i = threadIdx.x; i < 64 * K / 4; i += blockDim.x) {
-    const int t = i / (K / 4), c4 = i % (K / 4);
-    const float4 v = reinterpret_cast<const float4*>(gc_tile)[i];
-    *reinterpret_cast<float4*>(s_gc + t * (K + 4) + 4 * c4) = v;
+template <int K, int BATCH = 64 * K / 4 / 256>
+__device__ __forceinline__ void load_gc_tile(const float* gc_tile, float* s_gc) {  // 256 threads
+  // BATCH 16-byte loads of the thread are requested before the first of them is stored (one or two trips to memory
+  // instead of one per load)
+  constexpr int NIT = 64 * K / 4 / 256;
+#pragma unroll
+  for (int b0 = 0; b0 < NIT; b0 += BATCH) {
+    float4 v[BATCH];
+#pragma unroll
+    for (int it = 0; it < BATCH; ++it) v[it] = __ldg(reinterpret_cast<const float4*>(gc_tile) + threadIdx.x + 256 * (b0 + it));
+#pragma unroll
+    for (int it = 0; it < BATCH; ++it) {
+      const int i = threadIdx.x + 256 * (b0 + it), t = i / (K / 4), c4 = i % (K / 4);
+      *reinterpret_cast<float4*>(s_gc + t * (K + 4) + 4 * c4) = v[it];
+    }
   }
 }
 
@@ -57,10 +66,19 @@ __global__ void __launch_bounds__(256) zoo_diag_rows_kernel(DiagArgs a) {
   const float e_hw = (1.f - a.sigma) * a.tau;
 
   // stage the raw log-decays of the chunk (coalesced), then one thread per channel scans them in double
-  for (int i = tid; i < C * (K / 4); i += 256) {
-    const int t = i / (K / 4), c4 = i % (K / 4);
-    *reinterpret_cast<float4*>(s_gc + t * LD + 4 * c4) =
-        __ldg(reinterpret_cast<const float4*>(a.g + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K) + c4);
+  {
+    constexpr int NIT = C * (K / 4) / 256;
+    float4 v[NIT];
+#pragma unroll
+    for (int it = 0; it < NIT; ++it) {
+      const int i = tid + 256 * it, t = i / (K / 4), c4 = i % (K / 4);
+      v[it] = __ldg(reinterpret_cast<const float4*>(a.g + (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K) + c4);
+    }
+#pragma unroll
+    for (int it = 0; it < NIT; ++it) {
+      const int i = tid + 256 * it, t = i / (K / 4), c4 = i % (K / 4);
+      *reinterpret_cast<float4*>(s_gc + t * LD + 4 * c4) = v[it];
+    }
   }
   if (DELTA && tid >= 128 && tid < 128 + C) {
     const int t = tid - 128;
@@ -223,7 +241,7 @@ __global__ void __launch_bounds__(256) zoo_diag_amat_kernel(DiagArgs a) {
   const bool use_hw = a.beta != nullptr && e_hw != 0.f;
   const bool rot = a.signs != nullptr;
 
-  load_gc_tile<K>(a.gc + tile * (size_t)(C * K), s_gc);
+  load_gc_tile<K, K / 32>(a.gc + tile * (size_t)(C * K), s_gc);
   for (int i = tid; i < C * 65; i += 256) s_A[i] = 0.f;
   if (tid < C) {
     s_hw[tid] = use_hw ? pow_exact01(a.beta[((size_t)b * a.T + (size_t)c * C + tid) * a.H + h], e_hw) : 1.f;
