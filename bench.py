@@ -316,7 +316,7 @@ def run_ours(args):
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    affinity = pin_host_threads(local, world)
+    affinity = "unchanged (--no-pin)" if args.no_pin else pin_host_threads(local, world)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     _cabi.lib()  # fail loudly when the CUDA library is missing
@@ -793,6 +793,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-side", action="store_true", help="skip the per_config side records")
+    ap.add_argument("--no-pin", action="store_true", help="leave the host threads' CPU affinity as it is")
     ap.add_argument("--eager", action="store_true", help="launch the step kernel by kernel from Python instead of replaying a CUDA graph")
     ap.add_argument("--layers", type=int, default=M2["layers"], help="fewer layers: a reduced run for profiling, not a bench value")
     ap.add_argument("--batch", type=int, default=M2["B"], help="smaller batch: a reduced run for profiling, not a bench value")
