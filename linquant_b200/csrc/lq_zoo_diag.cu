@@ -241,22 +241,14 @@ __global__ void __launch_bounds__(256) zoo_diag_amat_kernel(DiagArgs a) {
   const bool use_hw = a.beta != nullptr && e_hw != 0.f;
   const bool rot = a.signs != nullptr;
 
-  load_gc_tile<K, K / 32>(a.gc + tile * (size_t)(C * K), s_gc);
-  for (int i = tid; i < C * 65; i += 256) s_A[i] = 0.f;
-  if (tid < C) {
-    s_hw[tid] = use_hw ? pow_exact01(a.beta[((size_t)b * a.T + (size_t)c * C + tid) * a.H + h], e_hw) : 1.f;
-  }
-  __syncthreads();
-
   constexpr int LPR = K / 8, G = 32 / LPR;
   const int r = lane % LPR, grp = lane / LPR;
-  const float inv_sq = 1.0f / a.sq[h], inv_sk = 1.0f / a.sk[h];
-  const float sqk = __fmul_rn(a.sq[h], a.sk[h]);
   const T* qp = reinterpret_cast<const T*>(a.q);
   const T* kp = reinterpret_cast<const T*>(a.k);
   auto grow = [&](int t) { return (((size_t)b * a.T + (size_t)c * C + t) * a.H + h) * K + 8 * r; };
 
-  // codes of the bare operands (diagonal blocks); every row load of the thread is issued before the first is used
+  // The rows of the bare operands (diagonal blocks) are requested first of all, so that their trip to memory runs
+  // beside that of the log-decay tile; every row load of the thread is issued before the first is used.
   constexpr int NIT = C / (8 * G);
   uint4 rq0[NIT], rk0[NIT];
 #pragma unroll
@@ -265,6 +257,15 @@ __global__ void __launch_bounds__(256) zoo_diag_amat_kernel(DiagArgs a) {
     rq0[u] = __ldg(reinterpret_cast<const uint4*>(qp + grow(t)));
     rk0[u] = __ldg(reinterpret_cast<const uint4*>(kp + grow(t)));
   }
+  load_gc_tile<K, K / 32>(a.gc + tile * (size_t)(C * K), s_gc);
+  for (int i = tid; i < C * 65; i += 256) s_A[i] = 0.f;
+  if (tid < C) {
+    s_hw[tid] = use_hw ? pow_exact01(a.beta[((size_t)b * a.T + (size_t)c * C + tid) * a.H + h], e_hw) : 1.f;
+  }
+  __syncthreads();
+
+  const float inv_sq = 1.0f / a.sq[h], inv_sk = 1.0f / a.sk[h];
+  const float sqk = __fmul_rn(a.sq[h], a.sk[h]);
 #pragma unroll
   for (int u = 0; u < NIT; ++u) {
     const int t = warp * G + grp + 8 * G * u;
